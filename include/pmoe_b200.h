@@ -1,0 +1,138 @@
+/* C ABI of the B200 (sm_100a) fused MoE FFN library `libpmoe_b200.so`.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless stated otherwise, `stream`
+ * is a CUDA stream handle (cudaStream_t / CUstream), and every function returns a status code
+ * (PMOE_OK == 0) instead of throwing; `pmoe_last_error()` returns the message of the last failing
+ * call on the calling thread. No entry point synchronises the host with the device except
+ * `pmoe_device_status` and `pmoe_reset_device_status`.
+ *
+ * Each entry point names the reference interface it replaces (file:line inside
+ * PrimeIntellect-ai/prime-flash-moe). Argument order and meaning follow the reference's native
+ * `pi::` layer so that its torch binding can forward to these functions one to one.
+ */
+#ifndef PMOE_B200_H
+#define PMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *pmoe_stream_t;
+
+enum {
+    PMOE_OK = 0,
+    PMOE_ERR_BAD_ARG = 1,     /* an argument violates the documented contract */
+    PMOE_ERR_UNSUPPORTED = 2, /* a knob combination this library (like the reference) rejects */
+    PMOE_ERR_CUDA = 3,        /* a CUDA runtime / driver call failed */
+    PMOE_ERR_DEVICE = 4       /* a kernel recorded an error (bounded wait expired) */
+};
+
+/* Message of the last error on this thread ("" if none). The pointer stays valid until the next
+ * failing call on the same thread. */
+const char *pmoe_last_error(void);
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int pmoe_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * moe_align: counting sort of (token, route) pair ids by expert with per-expert padding.
+ * Replaces pi::moe_align (prime_moe/csrc/torch_interface.cpp:63-75, kernel
+ * prime_moe/csrc/kernels/fused_moe_bf16_kernel.cu:853-928).
+ *
+ *   topk_ids               int32[n]            expert of pair i (pair id i = token * top_k + route)
+ *   sorted_token_ids       int32[max_padded]   out: per expert, its pair ids in ascending order, then
+ *                                              -1 up to a multiple of pad_to; -1 past the end
+ *   expert_ids             int32[max_blocks]   out: expert of each block_m-row block; num_experts-1
+ *                                              for blocks past num_tokens_post_padded
+ *   num_tokens_post_padded int32[1]            out: sum of the padded expert counts
+ *   pad_to = block_m * bpc; max_padded = ceil((n + E*(pad_to-1)) / pad_to) * pad_to;
+ *   max_blocks = max_padded / block_m (prime_moe/csrc/torch_interface.cpp:88-91).
+ *
+ * Unlike the reference (order inside an expert left to shared-memory atomics), the order inside an
+ * expert is deterministic: ascending pair id. Ids outside [0, num_experts) are ignored.
+ * num_experts <= 1024 as in the reference (fused_moe_bf16_kernel.cu:922-923).
+ *
+ * `pmoe_moe_align` takes its scratch from the stream-ordered allocator (cudaMallocAsync);
+ * `pmoe_moe_align_ws` uses caller memory of at least `pmoe_moe_align_workspace_bytes` bytes
+ * (may be 0 for small n), 16-byte aligned, and performs no allocation. */
+int pmoe_moe_align(const int32_t *topk_ids, int32_t *sorted_token_ids, int32_t *expert_ids,
+                   int32_t *num_tokens_post_padded, int n, int num_experts, int block_m, int pad_to,
+                   int max_padded, int max_blocks, pmoe_stream_t stream);
+size_t pmoe_moe_align_workspace_bytes(int n, int num_experts);
+int pmoe_moe_align_ws(const int32_t *topk_ids, int32_t *sorted_token_ids, int32_t *expert_ids,
+                      int32_t *num_tokens_post_padded, int n, int num_experts, int block_m, int pad_to,
+                      int max_padded, int max_blocks, void *workspace, size_t workspace_bytes,
+                      pmoe_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * fused_moe_bf16: out[token] (+)= sum over routes  w_route * (SwiGLU(x[token] * W1[e]^T) * W2[e]^T)
+ * Replaces pi::fused_moe_bf16 (prime_moe/csrc/torch_interface.cpp:11-34; kernels
+ * prime_moe/csrc/kernels/fused_moe_bf16_kernel.cu:21-373, 393-546; launcher :549-733, :930-964).
+ *
+ *   x   bf16[M, K]        w   bf16[E, N, K]  (rows [0,N/2) gate, [N/2,N) up)     w2  bf16[E, K, N/2]
+ *   out bf16[M, K]        sorted_token_ids int32[sorted_num], expert_ids int32[>= sorted_num/128],
+ *   num_tokens_post_padded int32[1], topk_weights fp32[M*top_k] (indexed by pair id)
+ *   block_m == 128; (block_n, warp_n) in {(32,8), (64,4)}; stages 1..5 (<= 4 when split);
+ *   bpc in {1, 2} (2 = two-CTA MMA; needs moe_align run with the same bpc); cpc == 1;
+ *   K % 128 == 0, N % 256 == 0.
+ *   split == 0: one launch, ACCUMULATES into `out` (caller zeroes it).
+ *   split != 0: gate/up kernel -> activation workspace -> down kernel chained by programmatic
+ *               dependent launch; `out` is zeroed by the library.
+ * `_ws` variant: caller-provided workspace (>= pmoe_fused_moe_bf16_workspace_bytes, 1024-byte
+ * aligned), no allocation; the plain variant uses cudaMallocAsync / cudaFreeAsync on `stream`. */
+int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2, void *out,
+                        const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                        const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k, int M,
+                        int K, int N, int num_experts, int sorted_num, int block_m, int block_n, int warp_n,
+                        int stages, int bpc, int cpc, int split, pmoe_stream_t stream);
+size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int sorted_num, int split);
+int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *w2, void *out,
+                           const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                           const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
+                           int M, int K, int N, int num_experts, int sorted_num, int block_m, int block_n,
+                           int warp_n, int stages, int bpc, int cpc, int split, void *workspace,
+                           size_t workspace_bytes, pmoe_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * fused_moe_mxfp8: the same contraction on OCP-MX operands (e4m3 values, one e8m0 scale per 32
+ * K-elements); the SwiGLU output is re-quantised to mxfp8 on chip before the down projection.
+ * Replaces pi::fused_moe_mxfp8 (prime_moe/csrc/torch_interface.cpp:36-61; kernels
+ * prime_moe/csrc/kernels/fused_moe_mxfp8_kernel.cu:82-503, 513-679; launcher :681-866, :944-1009).
+ *
+ *   x e4m3[M, K], x_scales e8m0[M, K/32] row major;
+ *   w e4m3[E, N, K], w_scales e8m0[E*N*K/32] in the blocked layout of pack_scales_blocked
+ *   (prime_moe/__init__.py:106-115): 512-byte tiles of 128 rows x 4 scale columns, tile index
+ *   row_tile * (K/128) + k_tile, byte (r%32)*16 + (r/32)*4 + (kb%4);
+ *   w2 e4m3[E, K, N/2], w2_scales e8m0[E*K*(N/2)/32] blocked likewise; K % 256 == 0, N % 256 == 0,
+ *   stages 1..4, bpc == 1. Other arguments as for bf16. */
+int pmoe_fused_moe_mxfp8(const void *x, const void *x_scales, const void *w, const void *w_scales,
+                         const void *w2, const void *w2_scales, void *out, const int32_t *sorted_token_ids,
+                         const int32_t *expert_ids, const int32_t *num_tokens_post_padded,
+                         const float *topk_weights, int top_k, int M, int K, int N, int num_experts,
+                         int sorted_num, int block_m, int block_n, int warp_n, int stages, int bpc, int split,
+                         pmoe_stream_t stream);
+size_t pmoe_fused_moe_mxfp8_workspace_bytes(int M, int K, int N, int sorted_num, int split);
+int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, const void *w_scales,
+                            const void *w2, const void *w2_scales, void *out,
+                            const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                            const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
+                            int M, int K, int N, int num_experts, int sorted_num, int block_m, int block_n,
+                            int warp_n, int stages, int bpc, int split, void *workspace,
+                            size_t workspace_bytes, pmoe_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Device status. Every wait inside the kernels is bounded; a wait that expires records a code in a
+ * device status word and the kernel unwinds. These two calls synchronise the current device.
+ * No counterpart in the reference (its waits are unbounded, tcgen05_prelude.cuh:404-414).
+ *   pmoe_device_status: *status = first recorded code (0 = none); returns PMOE_OK, or
+ *   PMOE_ERR_DEVICE when *status != 0.   pmoe_reset_device_status: clears the word. */
+int pmoe_device_status(int *status /* host pointer */);
+int pmoe_reset_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PMOE_B200_H */

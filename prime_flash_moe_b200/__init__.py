@@ -1,0 +1,102 @@
+"""B200-native fused MoE FFN behind the ``prime_moe`` torch-library API.
+
+Python surface of the reference package (prime_moe/__init__.py:27-49 ``fused_moe_bf16``, :75-100
+``fused_moe_mxfp8``, :103 ``BLOCK``, :106-115 ``pack_scales_blocked``) plus ``moe_align`` (the
+reference exposes it only as ``torch.ops.prime_moe.moe_align``). The operators are registered by
+``_C.so`` (TORCH_LIBRARY fragment ``prime_moe``) which forwards to the C ABI of
+``_lib/libpmoe_b200.so``. There is no CPU or eager fallback: importing this package without the
+built libraries raises.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from . import _build
+
+_PKG = Path(__file__).resolve().parent
+
+
+def _load() -> None:
+    missing = [p for p in (_build.NATIVE_LIB, _build.TORCH_EXT) if not p.exists()]
+    if missing:
+        raise ImportError(
+            "prime_flash_moe_b200: native libraries not built ("
+            + ", ".join(str(m.relative_to(_PKG.parent)) for m in missing)
+            + "); run `python prime_flash_moe_b200/_build.py` (needs nvcc and g++)"
+        )
+    torch.ops.load_library(str(_build.TORCH_EXT))
+
+
+_load()
+
+BLOCK = 32  # MX scale block size (prime_moe/__init__.py:103)
+
+
+@torch.library.register_fake("prime_moe::fused_moe_bf16")
+def _fused_moe_bf16_fake(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out,
+                         top_k, block_m, block_n, warp_n, stages, bpc, cpc, split):
+    return None
+
+
+@torch.library.register_fake("prime_moe::fused_moe_mxfp8")
+def _fused_moe_mxfp8_fake(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, expert_ids,
+                          num_tokens_post_padded, topk_weights, out, top_k, block_m, block_n, warp_n, stages,
+                          bpc, split):
+    return None
+
+
+@torch.library.register_fake("prime_moe::moe_align")
+def _moe_align_fake(topk_ids, num_experts, block_m, bpc):
+    n = topk_ids.numel()
+    pad_to = block_m * bpc
+    max_padded = (n + num_experts * (pad_to - 1) + pad_to - 1) // pad_to * pad_to
+    mk = lambda k: topk_ids.new_empty((k,), dtype=torch.int32)
+    return mk(max_padded), mk(max_padded // block_m), mk(1)
+
+
+def fused_moe_bf16(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k,
+                   block_m, block_n, warp_n, stages, bpc=1, cpc=1, split=True):
+    """In-place fused MoE FFN on bf16 operands; returns ``out`` (prime_moe/__init__.py:27-49).
+
+    ``split=False`` accumulates into ``out`` (zero it first); ``split=True`` zeroes ``out`` itself.
+    """
+    torch.ops.prime_moe.fused_moe_bf16(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                       topk_weights, out, top_k, block_m, block_n, warp_n, stages, bpc, cpc,
+                                       split)
+    return out
+
+
+def fused_moe_mxfp8(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, expert_ids,
+                    num_tokens_post_padded, topk_weights, out, top_k, block_m, block_n, warp_n, stages, bpc=1,
+                    split=True):
+    """In-place fused MoE FFN on OCP-MX (e4m3 + e8m0/32) operands; returns ``out``
+    (prime_moe/__init__.py:75-100). Weight scales must be in the ``pack_scales_blocked`` layout."""
+    torch.ops.prime_moe.fused_moe_mxfp8(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, expert_ids,
+                                        num_tokens_post_padded, topk_weights, out, top_k, block_m, block_n,
+                                        warp_n, stages, bpc, split)
+    return out
+
+
+def moe_align(topk_ids, num_experts, block_m=128, bpc=1):
+    """``(sorted_token_ids, expert_ids, num_tokens_post_padded)`` for ``topk_ids`` int32 ``(T, top_k)``
+    (op schema prime_moe/csrc/torch_interface.cpp:316-322)."""
+    return torch.ops.prime_moe.moe_align(topk_ids, num_experts, block_m, bpc)
+
+
+def pack_scales_blocked(scales: torch.Tensor) -> torch.Tensor:
+    """Row-major e8m0 scales ``(..., MN, K/32)`` -> the blocked layout the kernels read
+    (prime_moe/__init__.py:106-115): 512-byte tiles covering 128 rows x 4 scale columns, tile index
+    ``mn_tile * (K/128) + k_tile``, byte ``(r % 32) * 16 + (r // 32) * 4 + (kb % 4)`` inside a tile."""
+    u = scales.view(torch.uint8)
+    lead = u.shape[:-2]
+    mn, kb = u.shape[-2:]
+    assert mn % 128 == 0, f"MN ({mn}) must be a multiple of 128"
+    assert kb % 4 == 0, f"K ({kb * 32}) must be a multiple of 128"
+    tiles = u.reshape(-1, mn // 128, 4, 32, kb // 4, 4)     # (lead, mn_tile, r/32, r%32, k_tile, kb%4)
+    tiles = tiles.permute(0, 1, 4, 3, 2, 5).contiguous()    # (lead, mn_tile, k_tile, r%32, r/32, kb%4)
+    return tiles.reshape(*lead, -1).view(torch.float8_e8m0fnu)
+
+
+__all__ = ["fused_moe_bf16", "fused_moe_mxfp8", "moe_align", "pack_scales_blocked", "BLOCK"]

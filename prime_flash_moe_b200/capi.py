@@ -1,0 +1,123 @@
+"""ctypes view of the C ABI (``include/pmoe_b200.h``) for callers that hold raw device pointers.
+
+The functions here take torch tensors only to read ``data_ptr()`` and the current CUDA stream; they
+call ``libpmoe_b200.so`` directly, bypassing the torch operator registration. A non-zero status is
+raised as ``RuntimeError`` carrying ``pmoe_last_error()``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+from . import _build
+
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/pmoe_b200.h declaration by declaration
+SIGNATURES = {
+    "pmoe_last_error": (C.c_char_p, []),
+    "pmoe_version": (_i, []),
+    "pmoe_moe_align": (_i, [_vp] * 4 + [_i] * 6 + [_vp]),
+    "pmoe_moe_align_workspace_bytes": (_sz, [_i, _i]),
+    "pmoe_moe_align_ws": (_i, [_vp] * 4 + [_i] * 6 + [_vp, _sz, _vp]),
+    "pmoe_fused_moe_bf16": (_i, [_vp] * 8 + [_i] * 13 + [_vp]),
+    "pmoe_fused_moe_bf16_workspace_bytes": (_sz, [_i] * 5),
+    "pmoe_fused_moe_bf16_ws": (_i, [_vp] * 8 + [_i] * 13 + [_vp, _sz, _vp]),
+    "pmoe_fused_moe_mxfp8": (_i, [_vp] * 11 + [_i] * 12 + [_vp]),
+    "pmoe_fused_moe_mxfp8_workspace_bytes": (_sz, [_i] * 5),
+    "pmoe_fused_moe_mxfp8_ws": (_i, [_vp] * 11 + [_i] * 12 + [_vp, _sz, _vp]),
+    "pmoe_device_status": (_i, [C.POINTER(_i)]),
+    "pmoe_reset_device_status": (_i, []),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded shared library with argtypes/restypes set. Raises if it was not built."""
+    global _lib
+    if _lib is None:
+        path = Path(_build.NATIVE_LIB)
+        if not path.exists():
+            raise ImportError(f"{path} not built; run `python prime_flash_moe_b200/_build.py`")
+        handle = C.CDLL(str(path))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if a declared symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(lib().pmoe_last_error().decode() or f"pmoe status {rc}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def moe_align(topk_ids: torch.Tensor, num_experts: int, block_m: int = 128, bpc: int = 1):
+    assert topk_ids.is_cuda and topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()
+    n = topk_ids.numel()
+    pad_to = block_m * bpc
+    max_padded = (n + num_experts * (pad_to - 1) + pad_to - 1) // pad_to * pad_to
+    max_blocks = max_padded // block_m
+    mk = lambda k: torch.empty(k, dtype=torch.int32, device=topk_ids.device)
+    sorted_ids, expert_ids, npp = mk(max_padded), mk(max_blocks), mk(1)
+    with torch.cuda.device(topk_ids.device):
+        _check(lib().pmoe_moe_align(_p(topk_ids), _p(sorted_ids), _p(expert_ids), _p(npp), n, num_experts,
+                                    block_m, pad_to, max_padded, max_blocks, _stream()))
+    return sorted_ids, expert_ids, npp
+
+
+def fused_moe_bf16(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k,
+                   block_m=128, block_n=64, warp_n=4, stages=4, bpc=1, cpc=1, split=True, workspace=None):
+    M, K = x.shape
+    E, N, _ = w.shape
+    with torch.cuda.device(x.device):
+        common = (_p(x), _p(w), _p(w2), _p(out), _p(sorted_token_ids), _p(expert_ids), _p(num_tokens_post_padded),
+                  _p(topk_weights), top_k, M, K, N, E, sorted_token_ids.numel(), block_m, block_n, warp_n, stages,
+                  bpc, cpc, int(split))
+        if workspace is None:
+            _check(lib().pmoe_fused_moe_bf16(*common, _stream()))
+        else:
+            _check(lib().pmoe_fused_moe_bf16_ws(*common, _p(workspace), workspace.numel() * workspace.element_size(),
+                                                _stream()))
+    return out
+
+
+def fused_moe_mxfp8(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, expert_ids,
+                    num_tokens_post_padded, topk_weights, out, top_k, block_m=128, block_n=64, warp_n=4,
+                    stages=4, bpc=1, split=True, workspace=None):
+    M, K = x.shape
+    E, N, _ = w.shape
+    with torch.cuda.device(x.device):
+        common = (_p(x), _p(x_scales), _p(w), _p(w_scales), _p(w2), _p(w2_scales), _p(out), _p(sorted_token_ids),
+                  _p(expert_ids), _p(num_tokens_post_padded), _p(topk_weights), top_k, M, K, N, E,
+                  sorted_token_ids.numel(), block_m, block_n, warp_n, stages, bpc, int(split))
+        if workspace is None:
+            _check(lib().pmoe_fused_moe_mxfp8(*common, _stream()))
+        else:
+            _check(lib().pmoe_fused_moe_mxfp8_ws(*common, _p(workspace),
+                                                 workspace.numel() * workspace.element_size(), _stream()))
+    return out
+
+
+def device_status() -> int:
+    """Synchronises; returns the first error code recorded by a kernel (0 = none)."""
+    st = _i(0)
+    rc = lib().pmoe_device_status(C.byref(st))
+    if rc not in (0, 4):
+        _check(rc)
+    return st.value
+
+
+def reset_device_status() -> None:
+    _check(lib().pmoe_reset_device_status())

@@ -1,0 +1,107 @@
+// Host-side plumbing behind the C ABI: error string, tensor-map encoder lookup, device queries,
+// device status read-back.
+#include "host_common.h"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+namespace pmoe {
+
+namespace {
+thread_local char g_error[512] = "";
+std::once_flag g_encode_once;
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+    std::call_once(g_encode_once, [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    });
+    return g_encode;
+}
+}  // namespace
+
+int set_error(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void *base,
+                 uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
+                 CUtensorMapSwizzle swizzle, const char *what) {
+    auto encode = tensor_map_encoder();
+    PMOE_REQUIRE(encode != nullptr, PMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * elem_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(map, dtype, 2, const_cast<void *>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    PMOE_REQUIRE(r == CUDA_SUCCESS, PMOE_ERR_CUDA,
+                 "tensor map '%s' (rows %llu, cols %llu, box %ux%u) failed: CUresult %d", what,
+                 static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols), box_rows, box_cols,
+                 static_cast<int>(r));
+    return PMOE_OK;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("PMOE_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+int status_fetch_bf16(int *value, bool reset);
+int status_fetch_mxfp8(int *value, bool reset);
+
+}  // namespace pmoe
+
+extern "C" const char *pmoe_last_error(void) { return pmoe::g_error; }
+
+extern "C" int pmoe_version(void) { return 100; }
+
+extern "C" int pmoe_device_status(int *status) {
+    using namespace pmoe;
+    PMOE_REQUIRE(status != nullptr, PMOE_ERR_BAD_ARG, "pmoe_device_status: null pointer");
+    PMOE_CUDA_OK(cudaDeviceSynchronize());
+    int a = 0, b = 0;
+    if (int rc = status_fetch_bf16(&a, false)) return rc;
+    if (int rc = status_fetch_mxfp8(&b, false)) return rc;
+    *status = a ? a : b;
+    if (*status) return set_error(PMOE_ERR_DEVICE, "a kernel gave up a bounded wait (device status %d)", *status);
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_reset_device_status(void) {
+    using namespace pmoe;
+    PMOE_CUDA_OK(cudaDeviceSynchronize());
+    if (int rc = status_fetch_bf16(nullptr, true)) return rc;
+    return status_fetch_mxfp8(nullptr, true);
+}

@@ -1,0 +1,42 @@
+// Host-side helpers shared by the translation units behind the C ABI: status codes, the
+// thread-local error string, CUDA error mapping and the driver entry point for tensor maps.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pmoe_b200.h"
+
+namespace pmoe {
+
+// stores a printf-formatted message for pmoe_last_error() and returns `code`
+int set_error(int code, const char *fmt, ...);
+
+#define PMOE_CUDA_OK(expr)                                                                          \
+    do {                                                                                            \
+        cudaError_t _e = (expr);                                                                    \
+        if (_e != cudaSuccess)                                                                      \
+            return ::pmoe::set_error(PMOE_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
+                                     cudaGetErrorString(_e), __FILE__, __LINE__);                   \
+    } while (0)
+
+#define PMOE_REQUIRE(cond, code, ...)                                 \
+    do {                                                              \
+        if (!(cond)) return ::pmoe::set_error(code, __VA_ARGS__);     \
+    } while (0)
+
+// 2-D row-major tensor map: `rows` x `cols` elements of `elem_bytes` each, row pitch = cols*elem_bytes,
+// box = box_rows x box_cols, given swizzle. Returns PMOE_OK or an error code.
+int make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void *base,
+                 uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
+                 CUtensorMapSwizzle swizzle, const char *what);
+
+// number of SMs of the current device (cached per device)
+int sm_count();
+
+// PMOE_PDL=0 in the environment disables programmatic dependent launch between the kernels of the
+// split pipelines (they then run in plain stream order)
+bool pdl_enabled();
+
+}  // namespace pmoe

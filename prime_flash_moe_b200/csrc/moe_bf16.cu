@@ -1,0 +1,846 @@
+// bf16 fused MoE FFN for sm_100a: persistent, warp-specialised tcgen05 kernels.
+//
+// Replaces the kernels and launcher of prime_moe/csrc/kernels/fused_moe_bf16_kernel.cu
+// (fused_moe_kernel :21-373, gather_x_kernel :375-391, fused_moe_down_kernel :393-546,
+// launch_fused_moe_kernel_impl :549-733) behind pmoe_fused_moe_bf16.
+//
+// Work decomposition (all kernels): the rows of `sorted_token_ids` are cut into 128-row blocks, one
+// expert per block (moe_align guarantees it). A tile is one row block x one slice of output columns.
+// Each kernel is PERSISTENT: grid = min(#tiles, #SMs) CTAs, every CTA walks tiles blockIdx.x,
+// blockIdx.x + gridDim.x, ...; tiles are ordered so that the up-to-8 row blocks sharing a weight
+// slice run at the same time and the slice is read from HBM once and from L2 afterwards.
+//
+// Warp roles in every kernel:
+//   warp 0        TMA producer  - fills a ring of `stages` shared-memory slots (A tile 128x64 bf16 +
+//                                 B tile 256x64 bf16, 128-byte swizzle, 48 KB per slot)
+//   warp 1        MMA issuer    - one thread issues tcgen05.mma (M128 x N256 x K16) into TMEM and
+//                                 commits ring slots / accumulators to mbarriers; owns TMEM alloc
+//   warps 2..     epilogue      - 4 or 8 warps (`warp_n`) read accumulators from TMEM
+// TMEM holds 512 fp32 columns = two 128x256 accumulators, so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+//   up kernel   (split):  A = x rows gathered by token id with TMA gather4 (no gather pre-pass),
+//                         B = [gate rows ; up rows] of w1[e]; epilogue: SwiGLU from TMEM -> bf16 ->
+//                         swizzled staging tile -> TMA store into the activation workspace
+//                         [sorted_num, H]. The 2H-wide gate/up tensor never exists in memory.
+//                         The epilogue warps also zero `out` before their first tile.
+//   down kernel (split):  A = activation rows, B = 256 rows of w2[e] (K-major over H); epilogue:
+//                         acc * routing weight -> bf16x2 vector reductions into out[token].
+//                         Chained to the up kernel by programmatic dependent launch.
+//   fused kernel (split == 0): per (row block, 128-wide H slice): up GEMM -> SwiGLU -> bf16
+//                         activation tile kept in shared memory -> down GEMM against
+//                         w2[e][:, slice] in 128-column chunks (double-buffered in TMEM) ->
+//                         weighted reduction into `out` (split-K over H/128 slices).
+//
+// All waits are bounded (ptx.cuh); no hardware barrier is used inside a role loop.
+#include <stdio.h>
+
+#include <algorithm>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace pmoe {
+
+__device__ int g_status_bf16 = 0;
+
+namespace {
+
+constexpr int BM = 128;                          // rows per block (block_m)
+constexpr int BK = 64;                           // bf16 elements in one 128-byte swizzled row
+constexpr uint32_t A_BYTES = BM * BK * 2;        // 16 KB
+constexpr uint32_t B_BYTES = 256 * BK * 2;       // 32 KB
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr uint32_t ACT_TILE_BYTES = 128 * 128 * 2;  // 128 rows x 128 bf16: two swizzled 16 KB halves
+constexpr int MAX_STAGES = 4;
+constexpr int GROUP_M = 8;                       // row blocks that run side by side on one weight slice
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int MAX_THREADS = 64 + 8 * 32;
+constexpr uint32_t BAR_BYTES = 256;
+
+struct Coord {
+    int m_blk, n_tile;
+};
+__device__ __forceinline__ Coord tile_coord(int t, int m_blocks, int n_tiles) {
+    const int per_group = GROUP_M * n_tiles;
+    const int g = t / per_group;
+    const int first = g * GROUP_M;
+    const int gsz = min(GROUP_M, m_blocks - first);
+    const int local = t - g * per_group;
+    Coord c;
+    c.m_blk = first + local % gsz;
+    c.n_tile = local / gsz;
+    return c;
+}
+
+struct Args {
+    const int32_t *sorted_ids;
+    const int32_t *expert_ids;
+    const int32_t *npp;
+    const float *topk_weights;
+    __nv_bfloat16 *out;
+    int M, K, N, H;
+    int top_k;
+    int sorted_num;
+    int stages;
+    int epi_warps;   // 4 or 8
+    int zero_out;    // up kernel: clear `out` before the first tile
+    int use_pdl;     // down kernel: wait for the primary grid before touching its results
+};
+
+__device__ __forceinline__ int num_row_blocks(const Args &a) {
+    int npp = *a.npp;
+    npp = max(0, min(npp, a.sorted_num));
+    return npp / BM;
+}
+
+// Shared-memory carve-up (offsets from the 1024-byte aligned base):
+//   [0, stages*48K) ring | [.., +32K) activation tile (up: store staging, fused: A operand) | barriers
+struct Smem {
+    uint32_t ring, act, bars;
+    __device__ __forceinline__ uint32_t a(int s) const { return ring + s * STAGE_BYTES; }
+    __device__ __forceinline__ uint32_t b(int s) const { return ring + s * STAGE_BYTES + A_BYTES; }
+    __device__ __forceinline__ uint32_t full(int s) const { return bars + 8 * s; }
+    __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8 * (MAX_STAGES + s); }
+    __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * MAX_STAGES + i); }
+    __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * MAX_STAGES + 12); }
+};
+__device__ __forceinline__ Smem carve(const uint8_t *raw, int stages, bool with_act) {
+    Smem s;
+    s.ring = (smem_u32(raw) + 1023u) & ~1023u;
+    s.act = s.ring + stages * STAGE_BYTES;
+    s.bars = s.act + (with_act ? ACT_TILE_BYTES : 0);
+    return s;
+}
+size_t smem_bytes(int stages, bool with_act) {
+    return 1024 + static_cast<size_t>(stages) * STAGE_BYTES + (with_act ? ACT_TILE_BYTES : 0) + BAR_BYTES;
+}
+
+// token rows for the four A-tile rows a producer lane gathers (rows 4*lane .. 4*lane+3 of the block)
+__device__ __forceinline__ void gather_rows(const Args &a, int m_blk, int lane, int (&r)[4]) {
+    const int4 p = *reinterpret_cast<const int4 *>(a.sorted_ids + m_blk * BM + 4 * lane);
+    const int pr[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int tok = pr[i] >= 0 ? pr[i] / a.top_k : 0;  // padding rows read token 0, their result is dropped
+        if (tok >= a.M) tok = 0;
+        r[i] = tok;
+    }
+}
+
+// After an abort: give the copies this producer issued a bounded time to land before the CTA exits.
+__device__ __forceinline__ void drain_fills(const Smem &sm, int stages, long long issued) {
+    const long long first = issued > stages ? issued - stages : 0;
+    for (long long f = first; f < issued; ++f) {
+        const uint32_t bar = sm.full(static_cast<int>(f % stages));
+        const uint32_t parity = static_cast<uint32_t>((f / stages) & 1);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar, parity)) {
+            if (globaltimer_ns() - t0 > 20000000ull) break;  // 20 ms
+        }
+    }
+}
+
+// SwiGLU epilogue for one 32-column chunk `c` (0..3) of a 128x128 activation tile: thread = row.
+// Writes bf16 into the 128-byte-swizzled tile at `act` (two 16 KB halves of 64 columns).
+__device__ __forceinline__ void swiglu_chunk_to_smem(uint32_t tmem_acc, uint32_t lane_base, int row, int c,
+                                                     uint32_t act) {
+    float g[32], u[32];
+    tmem_ld_32x32(g, tmem_addr(tmem_acc, lane_base, c * 32));
+    tmem_ld_32x32(u, tmem_addr(tmem_acc, lane_base, 128 + c * 32));
+    tmem_ld_wait();
+    const uint32_t row_addr = act + (c >> 1) * (ACT_TILE_BYTES / 2) + row * 128;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = j * 8 + e * 2;
+            w[e] = pack_bf16x2(swiglu(g[i], u[i]), swiglu(g[i + 1], u[i + 1]));
+        }
+        const uint32_t chunk16 = static_cast<uint32_t>((c & 1) * 4 + j);
+        st_shared_v4(row_addr + ((chunk16 ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+    }
+}
+
+// acc chunk (32 columns) * weight -> bf16 -> four 16-byte vector reductions into out
+__device__ __forceinline__ void reduce_chunk_to_out(uint32_t taddr, float wgt, __nv_bfloat16 *dst, bool valid) {
+    float v[32];
+    tmem_ld_32x32(v, taddr);
+    tmem_ld_wait();
+    if (valid) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            red_add_bf16x8(dst + j * 8, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                           pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                           pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                           pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// up kernel (split pipeline, first launch)
+//   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2] | 4 staged | 5 stage_free
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(MAX_THREADS, 1)
+moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
+                   const __grid_constant__ CUtensorMap map_act, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const Smem sm = carve(smem_raw, a.stages, true);
+    int *status = &g_status_bf16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int epi_threads = a.epi_warps * 32;
+
+    pdl_launch_dependents();  // the dependent grid still waits for this whole grid before reading
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), 1);
+        mbar_init(sm.misc(2), epi_threads);
+        mbar_init(sm.misc(3), epi_threads);
+        mbar_init(sm.misc(4), epi_threads);
+        mbar_init(sm.misc(5), 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w1);
+        tma_prefetch_desc(&map_act);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    const int m_blocks = num_row_blocks(a);
+    const int n_tiles = a.H / 128;
+    const int num_tiles = m_blocks * n_tiles;
+    const int ksteps = a.K / BK;
+
+    if (warp == 0) {
+        // ---------------- producer: 32 lanes, lane l gathers rows 4l..4l+3 ----------------
+        int s = 0;
+        uint32_t ph = 0;
+        long long issued = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int e = a.expert_ids[c.m_blk];
+            int r[4];
+            gather_rows(a, c.m_blk, lane, r);
+            const int row_gate = e * a.N + c.n_tile * 128;
+            const int row_up = row_gate + a.H;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                if (lane == 0) ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
+                    tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
+                    tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
+                }
+                __syncwarp();
+                tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
+                ++issued;
+                if (++s == a.stages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+            }
+        }
+        if (!ok && lane == 0) drain_fills(sm, a.stages, issued);
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int buf = it & 1;
+                ok = mbar_wait(sm.misc(2 + buf), ((it >> 1) & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * 256;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16(d, smem_desc_sw128(sm.a(s) + k * 32), smem_desc_sw128(sm.b(s) + k * 32), idesc,
+                                 (ks | k) != 0);
+                    umma_commit(sm.empty(s));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit(sm.misc(buf));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: thread = accumulator row ----------------
+        const int ew = warp - 2;
+        const int et = threadIdx.x - 64;
+        const uint32_t lane_base = (warp & 3) * 32;  // TMEM lane quarter this warp may read
+        const int row = lane_base + lane;
+        const int ncg = a.epi_warps / 4;             // column groups (1 or 2)
+        const int cg = ew / 4;
+        if (a.zero_out) {
+            int4 *o4 = reinterpret_cast<int4 *>(a.out);
+            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const int4 z = make_int4(0, 0, 0, 0);
+            for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
+                 i += static_cast<long long>(gridDim.x) * epi_threads)
+                o4[i] = z;
+        }
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int buf = it & 1;
+            if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            if (!mbar_wait(sm.misc(5), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;  // staging tile free
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * 256;
+            for (int ch = cg * (4 / ncg); ch < (cg + 1) * (4 / ncg); ++ch)
+                swiglu_chunk_to_smem(acc, lane_base, row, ch, sm.act);
+            tc_fence_before();
+            mbar_arrive(sm.misc(2 + buf));  // accumulator drained
+            fence_proxy_async_smem();
+            mbar_arrive(sm.misc(4));        // staging tile written
+            if (et == 0) {
+                if (!mbar_wait(sm.misc(4), it & 1, status, ST_TIMEOUT_ACT)) break;
+                tma_store_2d(&map_act, sm.act, c.n_tile * 128, c.m_blk * BM);
+                tma_store_2d(&map_act, sm.act + ACT_TILE_BYTES / 2, c.n_tile * 128 + 64, c.m_blk * BM);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+                mbar_arrive(sm.misc(5));
+            }
+        }
+        if (et == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// down kernel (split pipeline, second launch)
+//   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2]
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(MAX_THREADS, 1)
+moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_w2,
+                     const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const Smem sm = carve(smem_raw, a.stages, false);
+    int *status = &g_status_bf16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int epi_threads = a.epi_warps * 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), 1);
+        mbar_init(sm.misc(2), epi_threads);
+        mbar_init(sm.misc(3), epi_threads);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_act);
+        tma_prefetch_desc(&map_w2);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (a.use_pdl) pdl_wait_primary();  // activations and the zeroed `out` come from the up kernel
+
+    const int m_blocks = num_row_blocks(a);
+    const int n_tiles = (a.K + 255) / 256;
+    const int num_tiles = m_blocks * n_tiles;
+    const int ksteps = a.H / BK;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Coord c = tile_coord(t, m_blocks, n_tiles);
+                const int e = a.expert_ids[c.m_blk];
+                const int w2_row = e * a.K + c.n_tile * 256;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
+                    tma_load_2d(sm.a(s), &map_act, sm.full(s), ks * BK, c.m_blk * BM);
+                    tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BK, w2_row);
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+            if (!ok) drain_fills(sm, a.stages, issued);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int buf = it & 1;
+                ok = mbar_wait(sm.misc(2 + buf), ((it >> 1) & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * 256;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16(d, smem_desc_sw128(sm.a(s) + k * 32), smem_desc_sw128(sm.b(s) + k * 32), idesc,
+                                 (ks | k) != 0);
+                    umma_commit(sm.empty(s));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit(sm.misc(buf));
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int ncg = a.epi_warps / 4;
+        const int cg = ew / 4;
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int buf = it & 1;
+            const int pair = a.sorted_ids[c.m_blk * BM + row];
+            const int tok = pair >= 0 ? pair / a.top_k : 0;
+            const bool valid = pair >= 0 && tok < a.M;
+            const float wgt = valid ? a.topk_weights[pair] : 0.f;
+            const int col0 = c.n_tile * 256;
+            __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + col0;
+            const int cols = min(256, a.K - col0);
+            if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * 256;
+            for (int ch = cg * (8 / ncg); ch < (cg + 1) * (8 / ncg); ++ch)
+                reduce_chunk_to_out(tmem_addr(acc, lane_base, ch * 32), wgt, dst + ch * 32,
+                                    valid && ch * 32 < cols);
+            tc_fence_before();
+            mbar_arrive(sm.misc(2 + buf));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// fused kernel (split == 0): one launch, activation tile stays on chip, split-K over H/128 slices
+//   TMEM: [0,256) gate|up accumulator, [256,384) and [384,512) down accumulators (128 columns each)
+//   misc barriers: 0 up_full | 1 up_empty | 2 act_ready | 3 act_free | 4,5 dn_full[2] | 6,7 dn_empty[2]
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(MAX_THREADS, 1)
+moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
+                      const __grid_constant__ CUtensorMap map_w2, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const Smem sm = carve(smem_raw, a.stages, true);
+    int *status = &g_status_bf16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int epi_threads = a.epi_warps * 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), epi_threads);
+        mbar_init(sm.misc(2), epi_threads);
+        mbar_init(sm.misc(3), 1);
+        mbar_init(sm.misc(4), 1);
+        mbar_init(sm.misc(5), 1);
+        mbar_init(sm.misc(6), epi_threads);
+        mbar_init(sm.misc(7), epi_threads);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w1);
+        tma_prefetch_desc(&map_w2);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    const int m_blocks = num_row_blocks(a);
+    const int n_tiles = a.H / 128;          // H slices
+    const int num_tiles = m_blocks * n_tiles;
+    const int ksteps = a.K / BK;
+    const int dn_chunks = a.K / 128;        // 128 output columns per down chunk
+
+    if (warp == 0) {
+        int s = 0;
+        uint32_t ph = 0;
+        long long issued = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int e = a.expert_ids[c.m_blk];
+            int r[4];
+            gather_rows(a, c.m_blk, lane, r);
+            const int row_gate = e * a.N + c.n_tile * 128;
+            const int row_up = row_gate + a.H;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                if (lane == 0) ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
+                    tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
+                    tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
+                }
+                __syncwarp();
+                tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
+                ++issued;
+                if (++s == a.stages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+            }
+            if (!ok) break;
+            // down phase: w2[e][chunk*128 .. +128, slice*128 + kh*64 .. +64] -> B part of a slot
+            for (int ch = 0; ch < dn_chunks && ok; ++ch) {
+                for (int kh = 0; kh < 2; ++kh) {
+                    if (lane == 0) ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(sm.full(s), B_BYTES / 2);
+                        tma_load_2d(sm.b(s), &map_w2, sm.full(s), c.n_tile * 128 + kh * 64, e * a.K + ch * 128);
+                    }
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+        if (!ok && lane == 0) drain_fills(sm, a.stages, issued);
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_up = idesc_bf16_f32(128, 256);
+            constexpr uint32_t idesc_dn = idesc_bf16_f32(128, 128);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            long long dn_it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                ok = mbar_wait(sm.misc(1), (it & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16(tmem_base, smem_desc_sw128(sm.a(s) + k * 32), smem_desc_sw128(sm.b(s) + k * 32),
+                                 idesc_up, (ks | k) != 0);
+                    umma_commit(sm.empty(s));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(sm.misc(0));
+                ok = mbar_wait(sm.misc(2), it & 1, status, ST_TIMEOUT_ACT);  // activation tile in smem
+                if (!ok) break;
+                tc_fence_after();
+                for (int ch = 0; ch < dn_chunks && ok; ++ch, ++dn_it) {
+                    const int b = static_cast<int>(dn_it & 1);
+                    ok = mbar_wait(sm.misc(6 + b), static_cast<uint32_t>(((dn_it >> 1) & 1) ^ 1), status,
+                                   ST_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d = tmem_base + 256 + b * 128;
+                    for (int kh = 0; kh < 2; ++kh) {
+                        ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_f16(d, smem_desc_sw128(sm.act + kh * (ACT_TILE_BYTES / 2) + k * 32),
+                                     smem_desc_sw128(sm.b(s) + k * 32), idesc_dn, (kh | k) != 0);
+                        umma_commit(sm.empty(s));
+                        if (++s == a.stages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
+                    if (ok) umma_commit(sm.misc(4 + b));
+                }
+                if (ok) umma_commit(sm.misc(3));  // every MMA that reads the activation tile is done
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int ncg = a.epi_warps / 4;
+        const int cg = ew / 4;
+        int it = 0;
+        long long dn_it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int pair = a.sorted_ids[c.m_blk * BM + row];
+            const int tok = pair >= 0 ? pair / a.top_k : 0;
+            const bool valid = pair >= 0 && tok < a.M;
+            const float wgt = valid ? a.topk_weights[pair] : 0.f;
+            __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K;
+            if (!mbar_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            if (!mbar_wait(sm.misc(3), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;  // act tile reusable
+            tc_fence_after();
+            for (int ch = cg * (4 / ncg); ch < (cg + 1) * (4 / ncg); ++ch)
+                swiglu_chunk_to_smem(tmem_base, lane_base, row, ch, sm.act);
+            tc_fence_before();
+            mbar_arrive(sm.misc(1));
+            fence_proxy_async_smem();
+            mbar_arrive(sm.misc(2));
+            for (int ch = 0; ch < dn_chunks; ++ch, ++dn_it) {
+                const int b = static_cast<int>(dn_it & 1);
+                ok = mbar_wait(sm.misc(4 + b), static_cast<uint32_t>((dn_it >> 1) & 1), status,
+                               ST_TIMEOUT_TMEM_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + 256 + b * 128;
+                for (int q = cg * (4 / ncg); q < (cg + 1) * (4 / ncg); ++q)
+                    reduce_chunk_to_out(tmem_addr(acc, lane_base, q * 32), wgt, dst + ch * 128 + q * 32, valid);
+                tc_fence_before();
+                mbar_arrive(sm.misc(6 + b));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct Problem {
+    const void *x, *w, *w2;
+    void *out;
+    const int32_t *sorted_ids, *expert_ids, *npp;
+    const float *topk_weights;
+    int top_k, M, K, N, E, sorted_num, block_n, warp_n, stages, bpc, split;
+};
+
+int validate(const Problem &p, int block_m, int cpc) {
+    PMOE_REQUIRE(p.x && p.w && p.w2 && p.out && p.sorted_ids && p.expert_ids && p.npp && p.topk_weights,
+                 PMOE_ERR_BAD_ARG, "fused_moe_bf16: null pointer");
+    PMOE_REQUIRE(p.M > 0 && p.K > 0 && p.N > 0 && p.E > 0 && p.top_k > 0 && p.sorted_num >= 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16: M, K, N, num_experts, top_k must be positive");
+    PMOE_REQUIRE((p.K & 127) == 0, PMOE_ERR_BAD_ARG, "K dimension must be a multiple of 128");
+    PMOE_REQUIRE((p.N & 255) == 0, PMOE_ERR_BAD_ARG, "N dimension must be a multiple of 256");
+    PMOE_REQUIRE((p.block_n == 64 && p.warp_n == 4) || (p.block_n == 32 && p.warp_n == 8), PMOE_ERR_UNSUPPORTED,
+                 "(block_n, warp_n) must be (64, 4) or (32, 8)");
+    PMOE_REQUIRE(p.stages > 0 && p.stages < 6, PMOE_ERR_UNSUPPORTED, "stages must be in 1..5");
+    PMOE_REQUIRE(p.bpc == 1 && cpc == 1, PMOE_ERR_UNSUPPORTED, "bpc=cpc=1 is the only supported configuration");
+    PMOE_REQUIRE(!p.split || p.stages <= 4, PMOE_ERR_UNSUPPORTED, "split=True requires stages<=4, got stages=%d",
+                 p.stages);
+    PMOE_REQUIRE(block_m == 128, PMOE_ERR_UNSUPPORTED, "Blackwell tcgen05 fused MoE requires block_m=128.");
+    PMOE_REQUIRE(p.sorted_num % 128 == 0, PMOE_ERR_BAD_ARG, "sorted_num must be a multiple of block_m");
+    PMOE_REQUIRE(static_cast<long long>(p.E) * p.N < (1ll << 31) && static_cast<long long>(p.E) * p.K < (1ll << 31),
+                 PMOE_ERR_UNSUPPORTED, "E*N and E*K must fit in 31 bits");
+    PMOE_REQUIRE((reinterpret_cast<uintptr_t>(p.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.w) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(p.w2) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(p.sorted_ids) & 15) == 0,
+                 PMOE_ERR_BAD_ARG, "x, w, w2, out and sorted_token_ids must be 16-byte aligned");
+    return PMOE_OK;
+}
+
+template <typename Kernel>
+int set_smem(Kernel k, size_t bytes) {
+    PMOE_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    return PMOE_OK;
+}
+
+int run(const Problem &p, void *workspace, cudaStream_t stream) {
+    const int H = p.N / 2;
+    const int max_blocks = p.sorted_num / BM;
+    if (max_blocks == 0) {
+        if (p.split)
+            PMOE_CUDA_OK(cudaMemsetAsync(p.out, 0, static_cast<size_t>(p.M) * p.K * 2, stream));
+        return PMOE_OK;
+    }
+    Args a{};
+    a.sorted_ids = p.sorted_ids;
+    a.expert_ids = p.expert_ids;
+    a.npp = p.npp;
+    a.topk_weights = p.topk_weights;
+    a.out = static_cast<__nv_bfloat16 *>(p.out);
+    a.M = p.M;
+    a.K = p.K;
+    a.N = p.N;
+    a.H = H;
+    a.top_k = p.top_k;
+    a.sorted_num = p.sorted_num;
+    a.stages = std::min(p.stages, MAX_STAGES);
+    a.epi_warps = p.warp_n;
+    const int threads = 64 + 32 * a.epi_warps;
+    const int sms = sm_count();
+
+    CUtensorMap map_x, map_w1;
+    if (int rc = make_tmap_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.x, p.M, p.K, 1, BK,
+                              CU_TENSOR_MAP_SWIZZLE_128B, "x"))
+        return rc;
+    if (int rc = make_tmap_2d(&map_w1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w, static_cast<uint64_t>(p.E) * p.N,
+                              p.K, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w"))
+        return rc;
+
+    if (!p.split) {
+        CUtensorMap map_w2;
+        if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2,
+                                  static_cast<uint64_t>(p.E) * p.K, H, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
+            return rc;
+        const size_t smem = smem_bytes(a.stages, true);
+        if (int rc = set_smem(moe_fused_bf16_kernel, smem)) return rc;
+        const int tiles = max_blocks * (H / 128);
+        moe_fused_bf16_kernel<<<std::min(tiles, sms), threads, smem, stream>>>(map_x, map_w1, map_w2, a);
+        PMOE_CUDA_OK(cudaGetLastError());
+        return PMOE_OK;
+    }
+
+    // split pipeline: workspace = activation [sorted_num, H] bf16
+    PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16: workspace must be 1024-byte aligned");
+    CUtensorMap map_act, map_w2;
+    if (int rc = make_tmap_2d(&map_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, workspace, p.sorted_num, H, 128, BK,
+                              CU_TENSOR_MAP_SWIZZLE_128B, "act"))
+        return rc;
+    if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2, static_cast<uint64_t>(p.E) * p.K,
+                              H, 256, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
+        return rc;
+    {
+        Args up = a;
+        up.zero_out = 1;
+        const size_t smem = smem_bytes(up.stages, true);
+        if (int rc = set_smem(moe_up_bf16_kernel, smem)) return rc;
+        const int tiles = max_blocks * (H / 128);
+        moe_up_bf16_kernel<<<std::min(tiles, sms), threads, smem, stream>>>(map_x, map_w1, map_act, up);
+        PMOE_CUDA_OK(cudaGetLastError());
+    }
+    {
+        Args dn = a;
+        dn.use_pdl = pdl_enabled() ? 1 : 0;
+        const size_t smem = smem_bytes(dn.stages, false);
+        if (int rc = set_smem(moe_down_bf16_kernel, smem)) return rc;
+        const int tiles = max_blocks * ((p.K + 255) / 256);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(std::min(tiles, sms));
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = dn.use_pdl ? 1 : 0;
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_bf16_kernel, map_act, map_w2, dn));
+    }
+    return PMOE_OK;
+}
+
+}  // namespace
+
+int status_fetch_bf16(int *value, bool reset) {
+    if (value) PMOE_CUDA_OK(cudaMemcpyFromSymbol(value, g_status_bf16, sizeof(int)));
+    if (reset) {
+        const int zero = 0;
+        PMOE_CUDA_OK(cudaMemcpyToSymbol(g_status_bf16, &zero, sizeof(int)));
+    }
+    return PMOE_OK;
+}
+
+}  // namespace pmoe
+
+extern "C" size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int sorted_num, int split) {
+    (void)M;
+    (void)K;
+    if (!split || sorted_num <= 0 || N <= 0) return 0;
+    return static_cast<size_t>(sorted_num) * (N / 2) * 2;
+}
+
+extern "C" int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *w2, void *out,
+                                      const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                      const int32_t *num_tokens_post_padded, const float *topk_weights,
+                                      int top_k, int M, int K, int N, int num_experts, int sorted_num,
+                                      int block_m, int block_n, int warp_n, int stages, int bpc, int cpc,
+                                      int split, void *workspace, size_t workspace_bytes,
+                                      pmoe_stream_t stream) {
+    using namespace pmoe;
+    Problem p{x, w, w2, out, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights,
+              top_k, M, K, N, num_experts, sorted_num, block_n, warp_n, stages, bpc, split ? 1 : 0};
+    if (int rc = validate(p, block_m, cpc)) return rc;
+    const size_t need = pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_num, split);
+    PMOE_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16: workspace of %zu bytes required, got %zu", need, workspace_bytes);
+    return run(p, workspace, stream);
+}
+
+extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2, void *out,
+                                   const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                   const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
+                                   int M, int K, int N, int num_experts, int sorted_num, int block_m,
+                                   int block_n, int warp_n, int stages, int bpc, int cpc, int split,
+                                   pmoe_stream_t stream) {
+    using namespace pmoe;
+    Problem p{x, w, w2, out, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights,
+              top_k, M, K, N, num_experts, sorted_num, block_n, warp_n, stages, bpc, split ? 1 : 0};
+    if (int rc = validate(p, block_m, cpc)) return rc;
+    const size_t need = pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_num, split);
+    void *ws = nullptr;
+    if (need) PMOE_CUDA_OK(cudaMallocAsync(&ws, need, stream));
+    const int rc = run(p, ws, stream);
+    if (ws) PMOE_CUDA_OK(cudaFreeAsync(ws, stream));
+    return rc;
+}

@@ -1,0 +1,199 @@
+// TORCH_LIBRARY registration of the prime_moe operators on top of the C ABI (include/pmoe_b200.h).
+//
+// Schemas, argument order, defaults and tensor-level checks mirror the reference binding
+// (prime_moe/csrc/torch_interface.cpp:77-110 moe_align, :112-180 fused_moe_bf16, :182-268
+// fused_moe_mxfp8, schemas :271-324) so the ops are drop-in. Shape/knob checks that the reference
+// performs with TORCH_CHECK are performed by the C ABI and surface here as the same c10::Error.
+// Workspaces come from torch's caching allocator (stream-ordered for the current stream) and are
+// handed to the `_ws` entry points, so the op itself performs no cudaMalloc.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/all.h>
+#include <torch/library.h>
+
+#include <tuple>
+
+#include "../../include/pmoe_b200.h"
+
+namespace {
+
+void check_status(int rc) { TORCH_CHECK(rc == PMOE_OK, pmoe_last_error()); }
+
+torch::Tensor workspace(size_t bytes, const torch::Tensor &like) {
+    // +1024 so the pointer can be rounded up to the 1024-byte alignment the kernels need
+    return torch::empty({static_cast<int64_t>(bytes + 1024)},
+                        torch::TensorOptions().dtype(torch::kUInt8).device(like.device()));
+}
+void *align1k(void *p) {
+    return reinterpret_cast<void *>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> moe_align(const torch::Tensor &topk_ids,
+                                                                  int64_t num_experts, int64_t block_m,
+                                                                  int64_t bpc) {
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    at::cuda::OptionalCUDAGuard guard{device_of(topk_ids)};
+    TORCH_CHECK(topk_ids.is_contiguous());
+    TORCH_CHECK(topk_ids.dtype() == torch::kInt32);
+    TORCH_CHECK(block_m > 0 && bpc > 0 && num_experts > 0);
+    const int64_t n = topk_ids.numel();
+    const int64_t pad_to = block_m * bpc;
+    const int64_t max_padded = (n + num_experts * (pad_to - 1) + pad_to - 1) / pad_to * pad_to;
+    const int64_t max_blocks = max_padded / block_m;
+    auto opts = torch::TensorOptions().dtype(torch::kInt32).device(topk_ids.device());
+    torch::Tensor sorted_token_ids = torch::empty({max_padded}, opts);
+    torch::Tensor expert_ids = torch::empty({max_blocks}, opts);
+    torch::Tensor num_tokens_post_padded = torch::empty({1}, opts);
+    const size_t ws_bytes = pmoe_moe_align_workspace_bytes(static_cast<int>(n), static_cast<int>(num_experts));
+    torch::Tensor ws;
+    void *ws_ptr = nullptr;
+    if (ws_bytes) {
+        ws = workspace(ws_bytes, topk_ids);
+        ws_ptr = align1k(ws.data_ptr());
+    }
+    check_status(pmoe_moe_align_ws(static_cast<const int32_t *>(topk_ids.const_data_ptr()),
+                                   static_cast<int32_t *>(sorted_token_ids.data_ptr()),
+                                   static_cast<int32_t *>(expert_ids.data_ptr()),
+                                   static_cast<int32_t *>(num_tokens_post_padded.data_ptr()), static_cast<int>(n),
+                                   static_cast<int>(num_experts), static_cast<int>(block_m),
+                                   static_cast<int>(pad_to), static_cast<int>(max_padded),
+                                   static_cast<int>(max_blocks), ws_ptr, ws_bytes, stream));
+    return {sorted_token_ids, expert_ids, num_tokens_post_padded};
+}
+
+void fused_moe_bf16(const torch::Tensor &x, const torch::Tensor &w, const torch::Tensor &w2,
+                    const torch::Tensor &sorted_token_ids, const torch::Tensor &expert_ids,
+                    const torch::Tensor &num_tokens_post_padded, const torch::Tensor &topk_weights,
+                    torch::Tensor &out, int64_t top_k, int64_t block_m, int64_t block_n, int64_t warp_n,
+                    int64_t stages, int64_t bpc, int64_t cpc, bool split) {
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w2.dim() == 3);
+    TORCH_CHECK(x.size(0));
+    TORCH_CHECK(x.size(1) == w.size(2));
+    TORCH_CHECK(w2.size(0) == w.size(0) && w2.size(1) == x.size(1) && w2.size(2) * 2 == w.size(1),
+                "w2 must have shape (E, K, N/2)");
+    TORCH_CHECK(out.numel() == x.numel(), "out must have shape (M, K)");
+    TORCH_CHECK(topk_weights.numel() >= x.size(0) * top_k, "topk_weights must hold M*top_k values");
+    TORCH_CHECK(expert_ids.numel() * block_m >= sorted_token_ids.numel(),
+                "expert_ids must cover every block of sorted_token_ids");
+    TORCH_CHECK(x.is_contiguous());
+    TORCH_CHECK(w.is_contiguous());
+    TORCH_CHECK(w2.is_contiguous());
+    TORCH_CHECK(sorted_token_ids.is_contiguous());
+    TORCH_CHECK(expert_ids.is_contiguous());
+    TORCH_CHECK(num_tokens_post_padded.is_contiguous());
+    TORCH_CHECK(topk_weights.is_contiguous());
+    TORCH_CHECK(out.is_contiguous());
+    TORCH_CHECK(x.dtype() == torch::kBFloat16);
+    TORCH_CHECK(w.dtype() == torch::kBFloat16);
+    TORCH_CHECK(w2.dtype() == torch::kBFloat16);
+    TORCH_CHECK(topk_weights.dtype() == torch::kFloat32);
+    TORCH_CHECK(sorted_token_ids.dtype() == torch::kInt32);
+    TORCH_CHECK(expert_ids.dtype() == torch::kInt32);
+    TORCH_CHECK(num_tokens_post_padded.dtype() == torch::kInt32);
+    TORCH_CHECK(out.dtype() == torch::kBFloat16);
+    const int M = static_cast<int>(x.size(0)), K = static_cast<int>(x.size(1));
+    const int N = static_cast<int>(w.size(1)), E = static_cast<int>(w.size(0));
+    const int sorted_num = static_cast<int>(sorted_token_ids.size(0));
+    const size_t ws_bytes = pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_num, split);
+    torch::Tensor ws;
+    void *ws_ptr = nullptr;
+    if (ws_bytes) {
+        ws = workspace(ws_bytes, x);
+        ws_ptr = align1k(ws.data_ptr());
+    }
+    check_status(pmoe_fused_moe_bf16_ws(
+        x.const_data_ptr(), w.const_data_ptr(), w2.const_data_ptr(), out.data_ptr(),
+        static_cast<const int32_t *>(sorted_token_ids.const_data_ptr()),
+        static_cast<const int32_t *>(expert_ids.const_data_ptr()),
+        static_cast<const int32_t *>(num_tokens_post_padded.const_data_ptr()),
+        static_cast<const float *>(topk_weights.const_data_ptr()), static_cast<int>(top_k), M, K, N, E, sorted_num,
+        static_cast<int>(block_m), static_cast<int>(block_n), static_cast<int>(warp_n), static_cast<int>(stages),
+        static_cast<int>(bpc), static_cast<int>(cpc), split ? 1 : 0, ws_ptr, ws_bytes, stream));
+}
+
+void fused_moe_mxfp8(const torch::Tensor &x, const torch::Tensor &x_scales, const torch::Tensor &w,
+                     const torch::Tensor &w_scales, const torch::Tensor &w2, const torch::Tensor &w2_scales,
+                     const torch::Tensor &sorted_token_ids, const torch::Tensor &expert_ids,
+                     const torch::Tensor &num_tokens_post_padded, const torch::Tensor &topk_weights,
+                     torch::Tensor &out, int64_t top_k, int64_t block_m, int64_t block_n, int64_t warp_n,
+                     int64_t stages, int64_t bpc, bool split) {
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w2.dim() == 3);
+    const int64_t M = x.size(0), K = x.size(1), E = w.size(0), N = w.size(1);
+    TORCH_CHECK(M);
+    TORCH_CHECK(K == w.size(2));
+    TORCH_CHECK((K & 255) == 0, "K dimension must be a multiple of 256 on the mxfp8 path");
+    TORCH_CHECK((N & 255) == 0, "N dimension must be a multiple of 256 on the mxfp8 path");
+    TORCH_CHECK(w2.size(0) == E && w2.size(1) == K && w2.size(2) == N / 2);
+    TORCH_CHECK(x_scales.numel() == M * (K / 32), "x_scales must be a row major (M, K/32) e8m0 tensor");
+    TORCH_CHECK(w_scales.numel() == E * N * (K / 32),
+                "w_scales must hold E*N*K/32 e8m0 values in the blocked layout");
+    TORCH_CHECK(w2_scales.numel() == E * K * ((N / 2) / 32),
+                "w2_scales must hold E*K*(N/2)/32 e8m0 values in the blocked layout");
+    TORCH_CHECK(out.numel() == x.numel(), "out must have shape (M, K)");
+    TORCH_CHECK(topk_weights.numel() >= M * top_k, "topk_weights must hold M*top_k values");
+    TORCH_CHECK(expert_ids.numel() * block_m >= sorted_token_ids.numel(),
+                "expert_ids must cover every block of sorted_token_ids");
+    TORCH_CHECK(x.is_contiguous());
+    TORCH_CHECK(x_scales.is_contiguous());
+    TORCH_CHECK(w.is_contiguous());
+    TORCH_CHECK(w_scales.is_contiguous());
+    TORCH_CHECK(w2.is_contiguous());
+    TORCH_CHECK(w2_scales.is_contiguous());
+    TORCH_CHECK(sorted_token_ids.is_contiguous());
+    TORCH_CHECK(expert_ids.is_contiguous());
+    TORCH_CHECK(num_tokens_post_padded.is_contiguous());
+    TORCH_CHECK(topk_weights.is_contiguous());
+    TORCH_CHECK(out.is_contiguous());
+    TORCH_CHECK(x.dtype() == torch::kFloat8_e4m3fn);
+    TORCH_CHECK(x_scales.dtype() == torch::kFloat8_e8m0fnu);
+    TORCH_CHECK(w.dtype() == torch::kFloat8_e4m3fn);
+    TORCH_CHECK(w_scales.dtype() == torch::kFloat8_e8m0fnu);
+    TORCH_CHECK(w2.dtype() == torch::kFloat8_e4m3fn);
+    TORCH_CHECK(w2_scales.dtype() == torch::kFloat8_e8m0fnu);
+    TORCH_CHECK(topk_weights.dtype() == torch::kFloat32);
+    TORCH_CHECK(sorted_token_ids.dtype() == torch::kInt32);
+    TORCH_CHECK(expert_ids.dtype() == torch::kInt32);
+    TORCH_CHECK(num_tokens_post_padded.dtype() == torch::kInt32);
+    TORCH_CHECK(out.dtype() == torch::kBFloat16);
+    const int sorted_num = static_cast<int>(sorted_token_ids.size(0));
+    const size_t ws_bytes = pmoe_fused_moe_mxfp8_workspace_bytes(static_cast<int>(M), static_cast<int>(K),
+                                                                 static_cast<int>(N), sorted_num, split);
+    torch::Tensor ws;
+    void *ws_ptr = nullptr;
+    if (ws_bytes) {
+        ws = workspace(ws_bytes, x);
+        ws_ptr = align1k(ws.data_ptr());
+    }
+    check_status(pmoe_fused_moe_mxfp8_ws(
+        x.const_data_ptr(), x_scales.const_data_ptr(), w.const_data_ptr(), w_scales.const_data_ptr(),
+        w2.const_data_ptr(), w2_scales.const_data_ptr(), out.data_ptr(),
+        static_cast<const int32_t *>(sorted_token_ids.const_data_ptr()),
+        static_cast<const int32_t *>(expert_ids.const_data_ptr()),
+        static_cast<const int32_t *>(num_tokens_post_padded.const_data_ptr()),
+        static_cast<const float *>(topk_weights.const_data_ptr()), static_cast<int>(top_k), static_cast<int>(M),
+        static_cast<int>(K), static_cast<int>(N), static_cast<int>(E), sorted_num, static_cast<int>(block_m),
+        static_cast<int>(block_n), static_cast<int>(warp_n), static_cast<int>(stages), static_cast<int>(bpc),
+        split ? 1 : 0, ws_ptr, ws_bytes, stream));
+}
+
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(prime_moe, m) {
+    m.def(
+        "fused_moe_bf16(Tensor x, Tensor w, Tensor w2, Tensor sorted_token_ids, Tensor expert_ids, "
+        "Tensor num_tokens_post_padded, Tensor topk_weights, Tensor(a!) out, int top_k, int block_m, "
+        "int block_n, int warp_n, int stages, int bpc, int cpc, bool split=True) -> ()");
+    m.impl("fused_moe_bf16", torch::kCUDA, &fused_moe_bf16);
+    m.def(
+        "fused_moe_mxfp8(Tensor x, Tensor x_scales, Tensor w, Tensor w_scales, Tensor w2, Tensor w2_scales, "
+        "Tensor sorted_token_ids, Tensor expert_ids, Tensor num_tokens_post_padded, Tensor topk_weights, "
+        "Tensor(a!) out, int top_k, int block_m, int block_n, int warp_n, int stages, int bpc, "
+        "bool split=True) -> ()");
+    m.impl("fused_moe_mxfp8", torch::kCUDA, &fused_moe_mxfp8);
+    m.def("moe_align(Tensor topk_ids, int num_experts, int block_m, int bpc) -> (Tensor, Tensor, Tensor)");
+    m.impl("moe_align", torch::kCUDA, &moe_align);
+}
