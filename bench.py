@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Benchmark of the fused MoE FFN hot path (moe_align -> gate/up GEMM -> SwiGLU -> down GEMM -> top-k reduce).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c1] [--dtype bf16] [--impl ours|reference|cpu]
+
+Prints ONE JSON line (rank 0). A step = one pass of the hot path over one synthetic batch:
+`torch.ops.prime_moe.moe_align` + `torch.ops.prime_moe.fused_moe_*`. `value` is whole-job TFLOP/s with
+the inputs resident in HBM (algorithmic FLOPs 3*P*K*N, P = T*top_k; padding rows do not count);
+`e2e` is the same metric with the step's activations, routing ids and routing weights copied from pinned
+host memory and `out` copied back inside the timed region (weights stay resident, as in a model).
+
+`--impl reference` times the UNMODIFIED reference (pip-installed into baseline/_ref from the reference
+checkout) through its own public API on the same workload, its best accepted knob setting chosen during
+warm-up. The reference has no CPU implementation of this path - its product is sm_100a kernels - so that
+arm runs on the GPU too; the reference's only CPU code for the path, the PyTorch MoE of its tests, is
+timed as `cpu_baseline` (and alone with `--impl cpu`).
+
+N > 1 (torchrun): every rank runs its own batch on its own GPU against a full replica of the experts
+(no collective on the data path, weak scaling), or the expert-parallel mode with `--parallel ep`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+
+CONFIGS = {
+    # name: (T, K, E, N, top_k, routing)
+    "c0": (256, 4096, 8, 512, 4, "uniform"),
+    "c1": (4096, 4096, 8, 28672, 2, "uniform"),            # Mixtral-8x7B layer: the headline workload
+    "c2": (8192, 2048, 128, 1536, 8, "uniform"),           # Qwen3-30B-A3B layer (T overridable with --tokens)
+    "c3": (16384, 7168, 256, 4096, 8, "uniform"),          # DeepSeek-V3 layer
+    "c4": (65536, 4096, 128, 3072, 8, "zipf"),             # skewed routing stress
+    "refbench": (16384, 2048, 32, 2048, 4, "uniform"),     # the reference benchmark's default shape
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "cpu"])
+    ap.add_argument("--config", default="c1", choices=sorted(CONFIGS))
+    ap.add_argument("--tokens", type=int, default=0, help="override T of the configuration")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "mxfp8"])
+    ap.add_argument("--split", type=int, default=1)
+    ap.add_argument("--stages", type=int, default=4)
+    ap.add_argument("--bpc", type=int, default=1)
+    ap.add_argument("--parallel", default="replica", choices=["replica", "ep"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def dist_setup(args):
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo")
+    return world, rank, local
+
+
+def barrier_sync(world):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, world: int, device) -> float:
+    if world == 1:
+        return ms
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def make_inputs(cfg, seed, device):
+    """Seeded synthetic batch: x ~ N(0,1) bf16, w1 ~ N(0,1/K), w2 ~ N(0,1/H) bf16 generated on the device;
+    routing (distinct experts per token, uniform or Zipf s=1.2) and softmax weights from the CPU oracle's
+    generator so that every arm sees identical routing."""
+    import torch
+    sys.path.insert(0, str(ROOT))
+    from oracle import moe_oracle as O
+    T, K, E, N, k, routing = cfg
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(T, K, device=device, generator=g).to(torch.bfloat16)
+    w1 = torch.randn(E, N, K, device=device, generator=g, dtype=torch.bfloat16) * K ** -0.5
+    w2 = torch.randn(E, K, N // 2, device=device, generator=g, dtype=torch.bfloat16) * (N // 2) ** -0.5
+    ids, wts = O.make_routing(T, E, k, seed + 1, routing)
+    return x, w1, w2, ids, wts
+
+
+def time_cpu_oracle(x, w1, w2, ids, wts, sample_tokens):
+    """The reference's PyTorch MoE (restated in oracle/) on the host cores, on the first
+    `sample_tokens` tokens of the batch. Returns (TFLOP/s, seconds, threads)."""
+    import torch
+    from oracle import moe_oracle as O
+    T = min(sample_tokens, x.shape[0])
+    K = x.shape[1]
+    N = w1.shape[1]
+    xs, ids_s, wts_s = x[:T].cpu(), ids[:T].cpu(), wts[:T].cpu()
+    w1c, w2c = w1.cpu(), w2.cpu()
+    O.moe_ref_grouped_mm(xs[:8], w1c, w2c, ids_s[:8], wts_s[:8])   # warm-up (thread pool, allocator)
+    t0 = time.perf_counter()
+    O.moe_ref_grouped_mm(xs, w1c, w2c, ids_s, wts_s)
+    dt = time.perf_counter() - t0
+    flops = 3.0 * T * ids.shape[1] * K * N
+    return flops / dt / 1e12, dt, torch.get_num_threads()
+
+
+# ------------------------------------------------------------------------------------------------
+# arms
+# ------------------------------------------------------------------------------------------------
+def run_gpu_arm(args, impl):
+    import torch
+    world, rank, local = dist_setup(args)
+    if impl == "reference" and rank != 0:
+        return                     # the reference arm is single-GPU: rank 0 alone runs and prints
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    cfg = list(CONFIGS[args.config])
+    if args.tokens:
+        cfg[0] = args.tokens
+    T, K, E, N, k, routing = cfg
+    if args.dtype != "bf16":
+        raise SystemExit("mxfp8 benchmarking: use --dtype bf16 until the mxfp8 arm is wired in")
+    x, w1, w2, ids_cpu, wts_cpu = make_inputs(cfg, 1234 + rank, device)
+    ids, wts = ids_cpu.to(device), wts_cpu.to(device)
+    out = torch.zeros(T, K, dtype=torch.bfloat16, device=device)
+    flops = 3.0 * T * k * K * N
+    pad_note = ""
+
+    if impl == "ours":
+        sys.path.insert(0, str(ROOT))
+        import prime_flash_moe_b200  # noqa: F401
+        from prime_flash_moe_b200 import capi
+        ops = torch.ops.prime_moe
+        bn, wn, stages, split, bpc = 64, 4, args.stages, bool(args.split), args.bpc
+        launches_per_step = (3 if T * k > 4096 else 1) + (3 if split else 1)
+
+        def step(x_, ids_, wts_, out_):
+            s, e, n = ops.moe_align(ids_, E, 128, bpc)
+            if not split:
+                out_.zero_()
+            ops.fused_moe_bf16(x_, w1, w2, s, e, n, wts_, out_, k, 128, bn, wn, stages, bpc, 1, split)
+        knobs = {"block_n": bn, "warp_n": wn, "stages": stages, "split": split, "bpc": bpc}
+    else:
+        ref_dir = ROOT / "baseline" / "_ref"
+        if not (ref_dir / "prime_moe").exists():
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/prime_moe is not installed"}))
+            return
+        sys.path.insert(0, str(ref_dir))           # ahead of the repo root, which holds a shim of the same name
+        import prime_moe as ref_pkg
+        assert str(ref_dir) in str(Path(ref_pkg.__file__).resolve()), "wrong prime_moe imported"
+        ops = torch.ops.prime_moe
+        launches_per_step = None
+        best = None
+        for split in (True, False):
+            for bn, wn in ((64, 4), (32, 8)):
+                for stages in (1, 2, 3, 4):
+                    def cand(x_, ids_, wts_, out_, split=split, bn=bn, wn=wn, stages=stages):
+                        s, e, n = ops.moe_align(ids_, E, 128, 1)
+                        if not split:
+                            out_.zero_()
+                        ref_pkg.fused_moe_bf16(x_, w1, w2, s, e, n, wts_, out_, k, 128, bn, wn, stages, 1, 1, split)
+                    try:
+                        for _ in range(2):
+                            cand(x, ids, wts, out)
+                        torch.cuda.synchronize()
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record()
+                        for _ in range(3):
+                            cand(x, ids, wts, out)
+                        b.record()
+                        torch.cuda.synchronize()
+                        ms = a.elapsed_time(b) / 3
+                    except Exception:
+                        continue
+                    if best is None or ms < best[0]:
+                        best = (ms, cand, {"block_n": bn, "warp_n": wn, "stages": stages, "split": split, "bpc": 1})
+        if best is None:
+            print(json.dumps({"impl": "reference", "unavailable": "every knob setting of the reference failed"}))
+            return
+        _, step, knobs = best
+
+    ref_world = 1 if impl == "reference" else world
+    # ---- device-resident timing ----
+    for _ in range(max(args.warmup, 3)):
+        step(x, ids, wts, out)
+    barrier_sync(ref_world)
+    with ClockSampler(local) as clocks:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            step(x, ids, wts, out)
+        b.record()
+        barrier_sync(ref_world)
+        ms_total = max_over_ranks(a.elapsed_time(b), ref_world, device)
+    ms_step = ms_total / args.steps
+    value = ref_world * flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: host buffers, copies inside the timed region ----
+    hx = x.cpu().pin_memory()
+    hids, hwts = ids_cpu.pin_memory(), wts_cpu.pin_memory()
+    hout = torch.empty(T, K, dtype=torch.bfloat16).pin_memory()
+    dx, dids, dwts = torch.empty_like(x), torch.empty_like(ids), torch.empty_like(wts)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        dids.copy_(hids, non_blocking=True)
+        dwts.copy_(hwts, non_blocking=True)
+        step(dx, dids, dwts, out)
+        hout.copy_(out, non_blocking=True)
+    e2e_steps = max(5, min(args.steps, 50))
+    for _ in range(3):
+        e2e_step()
+    barrier_sync(ref_world)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    barrier_sync(ref_world)
+    e2e_ms = max_over_ranks(a.elapsed_time(b), ref_world, device) / e2e_steps
+    h2d = hx.numel() * 2 + hids.numel() * 4 + hwts.numel() * 4
+    d2h = hout.numel() * 2
+    e2e = {"value": ref_world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    peaks = measured_peaks()
+    roofline = None
+    if impl == "ours" and args.split:
+        # dominant kernel = the gate/up GEMM (2/3 of the FLOPs); timed alone through the profiling hook
+        lib = capi.lib()
+        step(x, ids, wts, out)                      # fills the workspace-independent state
+        s, e, n = ops.moe_align(ids, E, 128, args.bpc)
+        nbytes = lib.pmoe_fused_moe_bf16_workspace_bytes(T, K, N, s.numel(), 1)
+        ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        off = (-ws.data_ptr()) % 1024
+        ws = ws[off:off + nbytes]
+        call = lambda: capi.fused_moe_bf16(x, w1, w2, s, e, n, wts, out, k, 128, 64, 4, args.stages, args.bpc, 1, True,
+                                           workspace=ws)
+        call()
+        per_kernel = {}
+        for name, mask in (("gather_rows", 1), ("moe_up_bf16", 2), ("moe_down_bf16", 4)):
+            lib.pmoe_debug_set_phase_mask(mask)
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 20
+            a.record()
+            for _ in range(reps):
+                call()
+            b.record()
+            torch.cuda.synchronize()
+            per_kernel[name] = a.elapsed_time(b) / reps
+        lib.pmoe_debug_set_phase_mask(7)
+        call()
+        torch.cuda.synchronize()
+        up_flops = 2.0 * T * k * K * N
+        achieved = up_flops / (per_kernel["moe_up_bf16"] * 1e-3) / 1e12
+        roofline = {"kernel": "moe_up_bf16_kernel", "bound": "tensor", "achieved": achieved,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
+                    "traffic": None, "kernel_ms": per_kernel,
+                    "whole_op_frac": value / world / peaks["bf16_tflops"]}
+        assert capi.device_status() == 0, "a kernel recorded an error status"
+
+    cpu_baseline = None
+    if rank == 0 and not args.no_cpu_baseline:
+        sample = 256 if T >= 256 else T
+        tf, secs, threads = time_cpu_oracle(x, w1, w2, ids_cpu, wts_cpu, sample)
+        cpu_baseline = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                        "sample": f"first {sample} of {T} tokens of the same batch, torch CPU grouped_mm oracle, "
+                                  f"{secs:.2f} s", "host_cpus": os.cpu_count()}
+
+    if rank == 0:
+        line = {
+            "metric": "moe_ffn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": ref_world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "tokens_per_s": ref_world * T / (ms_step * 1e-3),
+            "config": {"workload": f"{args.config}: T={T} K={K} E={E} N={N} top_k={k} routing={routing} "
+                                   f"(per GPU), moe_align + fused_moe_bf16",
+                       "knobs": knobs, "parallelism": f"{args.parallel}{ref_world}",
+                       "l2": "weights (>= 1 GB) exceed the 126 MB L2, no flush between steps" if
+                             E * N * K * 3 > 256e6 else "inputs smaller than L2; steps are back to back"},
+            "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": (launches_per_step or 0) * args.steps,
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
+        }
+        if impl == "reference":
+            line["impl"] = "reference"
+            line["gpu_launches"] = None
+        print(json.dumps(line))
+
+
+def run_cpu_arm(args):
+    """`--impl cpu`: the reference's PyTorch MoE (oracle port) on the host cores, bounded sample."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sys.path.insert(0, str(ROOT))
+    cfg = list(CONFIGS[args.config])
+    if args.tokens:
+        cfg[0] = args.tokens
+    T, K, E, N, k, routing = cfg
+    dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    x, w1, w2, ids, wts = make_inputs(cfg, 1234, dev)
+    sample = min(T, 256)
+    vals = []
+    for _ in range(max(1, min(args.steps, 3))):
+        tf, secs, threads = time_cpu_oracle(x, w1, w2, ids, wts, sample)
+        vals.append((tf, secs))
+    tf, secs = max(vals)
+    cpu = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+           "sample": f"first {sample} of {T} tokens, torch CPU grouped_mm oracle"}
+    print(json.dumps({"impl": "cpu", "metric": "moe_ffn_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 0,
+                      "steps": len(vals), "warmup": 1, "ms_per_step": secs * 1e3, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"{args.config}: T={T} K={K} E={E} N={N} top_k={k} (sample {sample} tokens)"},
+                      "cpu_baseline": cpu,
+                      "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def main():
+    args = parse_args()
+    if args.impl == "cpu":
+        run_cpu_arm(args)
+    else:
+        run_gpu_arm(args, args.impl)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -132,6 +132,12 @@ int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, 
 int pmoe_device_status(int *status /* host pointer */);
 int pmoe_reset_device_status(void);
 
+/* Profiling hook, process-wide, not thread-safe: restrict the split pipelines to a subset of their
+ * launches so that each kernel can be timed alone with CUDA events (1 = row gather, 2 = gate/up
+ * kernel, 4 = down kernel; default 7 = all). A partial run leaves `out` undefined. Returns the
+ * previous mask. No counterpart in the reference. */
+int pmoe_debug_set_phase_mask(int mask);
+
 #ifdef __cplusplus
 }
 #endif

@@ -70,9 +70,50 @@ int sm_count() {
     return cached[dev];
 }
 
+// One private stream-ordered memory pool per device, created on first use, with the release threshold
+// raised so that freed scratch stays cached in the pool instead of going back to the driver at every
+// synchronisation (the default pool's threshold is 0, which makes each malloc cost ~0.2 ms).
+int scratch_alloc(void **ptr, size_t bytes, cudaStream_t stream) {
+    static cudaMemPool_t pools[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    PMOE_CUDA_OK(cudaGetDevice(&dev));
+    PMOE_REQUIRE(dev >= 0 && dev < 64, PMOE_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!pools[dev]) {
+            cudaMemPoolProps props = {};
+            props.allocType = cudaMemAllocationTypePinned;
+            props.location.type = cudaMemLocationTypeDevice;
+            props.location.id = dev;
+            PMOE_CUDA_OK(cudaMemPoolCreate(&pools[dev], &props));
+            unsigned long long keep = ~0ull;
+            PMOE_CUDA_OK(cudaMemPoolSetAttribute(pools[dev], cudaMemPoolAttrReleaseThreshold, &keep));
+        }
+    }
+    PMOE_CUDA_OK(cudaMallocFromPoolAsync(ptr, bytes, pools[dev], stream));
+    return PMOE_OK;
+}
+
+int scratch_free(void *ptr, cudaStream_t stream) {
+    PMOE_CUDA_OK(cudaFreeAsync(ptr, stream));
+    return PMOE_OK;
+}
+
 bool pdl_enabled() {
     static const bool on = [] {
         const char *e = getenv("PMOE_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+static int g_phase_mask = 7;
+int phase_mask() { return g_phase_mask; }
+
+bool pregather_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("PMOE_PREGATHER");
         return !(e && e[0] == '0');
     }();
     return on;
@@ -86,6 +127,12 @@ int status_fetch_mxfp8(int *value, bool reset);
 extern "C" const char *pmoe_last_error(void) { return pmoe::g_error; }
 
 extern "C" int pmoe_version(void) { return 100; }
+
+extern "C" int pmoe_debug_set_phase_mask(int mask) {
+    const int old = pmoe::g_phase_mask;
+    pmoe::g_phase_mask = mask & 7;
+    return old;
+}
 
 extern "C" int pmoe_device_status(int *status) {
     using namespace pmoe;

@@ -32,11 +32,23 @@ int make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t elem_byte
                  uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
                  CUtensorMapSwizzle swizzle, const char *what);
 
+// stream-ordered scratch from a private per-device pool (used by the entry points without `_ws`)
+int scratch_alloc(void **ptr, size_t bytes, cudaStream_t stream);
+int scratch_free(void *ptr, cudaStream_t stream);
+
 // number of SMs of the current device (cached per device)
 int sm_count();
 
 // PMOE_PDL=0 in the environment disables programmatic dependent launch between the kernels of the
 // split pipelines (they then run in plain stream order)
 bool pdl_enabled();
+
+// Default on: the split pipelines copy the routed rows of x into the workspace first and feed the
+// gate/up GEMM with plain 2-D TMA tiles. PMOE_PREGATHER=0 switches to TMA gather4 straight from x
+// (no pre-pass, smaller workspace, but gather4 issue rate then bounds the gate/up kernel).
+bool pregather_enabled();
+
+// which launches of a split pipeline run (pmoe_debug_set_phase_mask): 1 gather, 2 gate/up, 4 down
+int phase_mask();
 
 }  // namespace pmoe

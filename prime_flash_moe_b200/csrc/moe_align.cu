@@ -335,9 +335,11 @@ extern "C" int pmoe_moe_align(const int32_t *topk_ids, int32_t *sorted_token_ids
         return rc;
     const Plan p = make_plan(n, num_experts);
     int *ws = nullptr;
-    if (p.ws_ints) PMOE_CUDA_OK(cudaMallocAsync(reinterpret_cast<void **>(&ws), p.ws_ints * sizeof(int), stream));
+    if (p.ws_ints)
+        if (int rc = scratch_alloc(reinterpret_cast<void **>(&ws), p.ws_ints * sizeof(int), stream)) return rc;
     const int rc = launch(topk_ids, sorted_token_ids, expert_ids, num_tokens_post_padded, n, num_experts,
                           block_m, pad_to, max_padded, max_blocks, p, ws, stream);
-    if (ws) PMOE_CUDA_OK(cudaFreeAsync(ws, stream));
+    if (ws)
+        if (int rc2 = scratch_free(ws, stream)) return rc2;
     return rc;
 }

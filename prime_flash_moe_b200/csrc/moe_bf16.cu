@@ -86,6 +86,7 @@ struct Args {
     int epi_warps;   // 4 or 8
     int zero_out;    // up kernel: clear `out` before the first tile
     int use_pdl;     // down kernel: wait for the primary grid before touching its results
+    int pregathered; // up kernel: A rows come from a row-gathered copy of x (plain 2-D TMA) instead of gather4
 };
 
 __device__ __forceinline__ int num_row_blocks(const Args &a) {
@@ -180,6 +181,26 @@ __device__ __forceinline__ void reduce_chunk_to_out(uint32_t taddr, float wgt, _
 }
 
 // ---------------------------------------------------------------------------------------------
+// optional pre-pass of the split pipeline: x_sorted[row] = x[token(row)] (one warp per row, 16-byte
+// loads/stores); padding rows copy token 0. Only rows below num_tokens_post_padded are written.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ x_sorted, const Args a) {
+    const int warps_per_cta = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rows = num_row_blocks(a) * BM;
+    const int chunks = a.K / 8;  // 16-byte chunks per row
+    for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
+        const int pair = a.sorted_ids[row];
+        int tok = pair >= 0 ? pair / a.top_k : 0;
+        if (tok >= a.M) tok = 0;
+        const int4 *src = reinterpret_cast<const int4 *>(x + static_cast<size_t>(tok) * a.K);
+        int4 *dst = reinterpret_cast<int4 *>(x_sorted + static_cast<size_t>(row) * a.K);
+        for (int ch = lane; ch < chunks; ch += 32) dst[ch] = __ldg(src + ch);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // up kernel (split pipeline, first launch)
 //   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2] | 4 staged | 5 stage_free
 // ---------------------------------------------------------------------------------------------
@@ -243,9 +264,11 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
+                    if (a.pregathered) tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BK, c.m_blk * BM);
                 }
                 __syncwarp();
-                tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
+                if (!a.pregathered)
+                    tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
                 ++issued;
                 if (++s == a.stages) {
                     s = 0;
@@ -750,9 +773,22 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         return PMOE_OK;
     }
 
-    // split pipeline: workspace = activation [sorted_num, H] bf16
+    // split pipeline: workspace = activation [sorted_num, H] bf16 (+ x_sorted [sorted_num, K] when pre-gathering)
     PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16: workspace must be 1024-byte aligned");
+    const bool pregather = pregather_enabled();
+    const int phases = phase_mask();  // profiling hook: 1 = gather, 2 = gate/up, 4 = down (default all)
+    if (pregather) {
+        __nv_bfloat16 *x_sorted = static_cast<__nv_bfloat16 *>(workspace) + static_cast<size_t>(p.sorted_num) * H;
+        if (phases & 1) {
+            gather_rows_kernel<<<std::min(4 * sms, (p.sorted_num + 7) / 8), 256, 0, stream>>>(
+                static_cast<const __nv_bfloat16 *>(p.x), x_sorted, a);
+            PMOE_CUDA_OK(cudaGetLastError());
+        }
+        if (int rc = make_tmap_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_sorted, p.sorted_num, p.K, 128, BK,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, "x_sorted"))
+            return rc;
+    }
     CUtensorMap map_act, map_w2;
     if (int rc = make_tmap_2d(&map_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, workspace, p.sorted_num, H, 128, BK,
                               CU_TENSOR_MAP_SWIZZLE_128B, "act"))
@@ -760,18 +796,19 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2, static_cast<uint64_t>(p.E) * p.K,
                               H, 256, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
         return rc;
-    {
+    if (phases & 2) {
         Args up = a;
         up.zero_out = 1;
+        up.pregathered = pregather ? 1 : 0;
         const size_t smem = smem_bytes(up.stages, true);
         if (int rc = set_smem(moe_up_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
         moe_up_bf16_kernel<<<std::min(tiles, sms), threads, smem, stream>>>(map_x, map_w1, map_act, up);
         PMOE_CUDA_OK(cudaGetLastError());
     }
-    {
+    if (phases & 4) {
         Args dn = a;
-        dn.use_pdl = pdl_enabled() ? 1 : 0;
+        dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
         const size_t smem = smem_bytes(dn.stages, false);
         if (int rc = set_smem(moe_down_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * ((p.K + 255) / 256);
@@ -805,9 +842,10 @@ int status_fetch_bf16(int *value, bool reset) {
 
 extern "C" size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int sorted_num, int split) {
     (void)M;
-    (void)K;
     if (!split || sorted_num <= 0 || N <= 0) return 0;
-    return static_cast<size_t>(sorted_num) * (N / 2) * 2;
+    size_t bytes = static_cast<size_t>(sorted_num) * (N / 2) * 2;
+    if (pmoe::pregather_enabled()) bytes += static_cast<size_t>(sorted_num) * K * 2;
+    return bytes;
 }
 
 extern "C" int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *w2, void *out,
@@ -839,8 +877,10 @@ extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2,
     if (int rc = validate(p, block_m, cpc)) return rc;
     const size_t need = pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_num, split);
     void *ws = nullptr;
-    if (need) PMOE_CUDA_OK(cudaMallocAsync(&ws, need, stream));
+    if (need)
+        if (int rc = scratch_alloc(&ws, need, stream)) return rc;
     const int rc = run(p, ws, stream);
-    if (ws) PMOE_CUDA_OK(cudaFreeAsync(ws, stream));
+    if (ws)
+        if (int rc2 = scratch_free(ws, stream)) return rc2;
     return rc;
 }
