@@ -30,7 +30,9 @@
 //   fused kernel (split == 0): per (row block, 128-wide H slice): up GEMM -> SwiGLU -> bf16
 //                         activation tile kept in shared memory -> down GEMM against
 //                         w2[e][:, slice] in 128-column chunks (double-buffered in TMEM) ->
-//                         weighted reduction into `out` (split-K over H/128 slices).
+//                         weighted fp32 vector reductions into a zeroed fp32 buffer [M, K] (split-K
+//                         over H/128 slices, no bf16 rounding of partials); a small kernel chained
+//                         by programmatic dependent launch then adds the buffer into `out`.
 //
 // All waits are bounded (ptx.cuh); no hardware barrier is used inside a role loop.
 #include <stdio.h>
@@ -79,6 +81,7 @@ struct Args {
     const int32_t *npp;
     const float *topk_weights;
     __nv_bfloat16 *out;
+    float *acc32;    // fused kernel: fp32 accumulation buffer [M, K] the split-K partials are reduced into
     int M, K, N, H;
     int top_k;
     int sorted_num;
@@ -177,6 +180,39 @@ __device__ __forceinline__ void reduce_chunk_to_out(uint32_t taddr, float wgt, _
                            pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
                            pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
         }
+    }
+}
+
+// acc chunk (32 columns) * weight -> eight 16-byte fp32 vector reductions into the fp32 accumulation buffer
+__device__ __forceinline__ void reduce_chunk_to_acc32(uint32_t taddr, float wgt, float *dst, bool valid) {
+    float v[32];
+    tmem_ld_32x32(v, taddr);
+    tmem_ld_wait();
+    if (valid) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j * 4), "f"(wgt * v[j * 4 + 0]),
+                         "f"(wgt * v[j * 4 + 1]), "f"(wgt * v[j * 4 + 2]), "f"(wgt * v[j * 4 + 3])
+                         : "memory");
+    }
+}
+
+// out[i] += bf16(acc32[i]): last launch of the single-GEMM-launch pipeline (split == 0)
+__global__ void __launch_bounds__(256)
+finalize_acc32_kernel(const float *__restrict__ acc32, __nv_bfloat16 *__restrict__ out, long long n8, int use_pdl) {
+    if (use_pdl) pdl_wait_primary();
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(acc32) + 2 * i);
+        const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(acc32) + 2 * i + 1);
+        uint4 o = reinterpret_cast<const uint4 *>(out)[i];
+        const __nv_bfloat162 *ob = reinterpret_cast<const __nv_bfloat162 *>(&o);
+        uint4 r;
+        r.x = pack_bf16x2(__low2float(ob[0]) + a0.x, __high2float(ob[0]) + a0.y);
+        r.y = pack_bf16x2(__low2float(ob[1]) + a0.z, __high2float(ob[1]) + a0.w);
+        r.z = pack_bf16x2(__low2float(ob[2]) + a1.x, __high2float(ob[2]) + a1.y);
+        r.w = pack_bf16x2(__low2float(ob[3]) + a1.z, __high2float(ob[3]) + a1.w);
+        reinterpret_cast<uint4 *>(out)[i] = r;
     }
 }
 
@@ -501,6 +537,8 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_threads = a.epi_warps * 32;
 
+    pdl_launch_dependents();  // the finalize kernel still waits for this whole grid before reading
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), 1);
@@ -656,7 +694,7 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             const int tok = pair >= 0 ? pair / a.top_k : 0;
             const bool valid = pair >= 0 && tok < a.M;
             const float wgt = valid ? a.topk_weights[pair] : 0.f;
-            __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K;
+            float *dst = a.acc32 + static_cast<size_t>(valid ? tok : 0) * a.K;
             if (!mbar_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
             if (!mbar_wait(sm.misc(3), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;  // act tile reusable
             tc_fence_after();
@@ -674,7 +712,7 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 tc_fence_after();
                 const uint32_t acc = tmem_base + 256 + b * 128;
                 for (int q = cg * (4 / ncg); q < (cg + 1) * (4 / ncg); ++q)
-                    reduce_chunk_to_out(tmem_addr(acc, lane_base, q * 32), wgt, dst + ch * 128 + q * 32, valid);
+                    reduce_chunk_to_acc32(tmem_addr(acc, lane_base, q * 32), wgt, dst + ch * 128 + q * 32, valid);
                 tc_fence_before();
                 mbar_arrive(sm.misc(6 + b));
             }
@@ -765,11 +803,29 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2,
                                   static_cast<uint64_t>(p.E) * p.K, H, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
             return rc;
+        // workspace = fp32 accumulation buffer [M, K]: memset -> fused kernel -> out += bf16(acc32)
+        PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0, PMOE_ERR_BAD_ARG,
+                     "fused_moe_bf16: workspace must be 16-byte aligned");
+        a.acc32 = static_cast<float *>(workspace);
+        const size_t elems = static_cast<size_t>(p.M) * p.K;
+        PMOE_CUDA_OK(cudaMemsetAsync(a.acc32, 0, elems * sizeof(float), stream));
         const size_t smem = smem_bytes(a.stages, true);
         if (int rc = set_smem(moe_fused_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
         moe_fused_bf16_kernel<<<std::min(tiles, sms), threads, smem, stream>>>(map_x, map_w1, map_w2, a);
         PMOE_CUDA_OK(cudaGetLastError());
+        const int use_pdl = pdl_enabled() ? 1 : 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>(4 * sms, (elems / 8 + 255) / 256)));
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_pdl ? 1 : 0;
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, finalize_acc32_kernel, static_cast<const float *>(a.acc32), a.out,
+                                        static_cast<long long>(elems / 8), use_pdl));
         return PMOE_OK;
     }
 
@@ -841,8 +897,8 @@ int status_fetch_bf16(int *value, bool reset) {
 }  // namespace pmoe
 
 extern "C" size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int sorted_num, int split) {
-    (void)M;
-    if (!split || sorted_num <= 0 || N <= 0) return 0;
+    if (sorted_num <= 0 || N <= 0) return 0;
+    if (!split) return static_cast<size_t>(M) * K * sizeof(float);
     size_t bytes = static_cast<size_t>(sorted_num) * (N / 2) * 2;
     if (pmoe::pregather_enabled()) bytes += static_cast<size_t>(sorted_num) * K * 2;
     return bytes;

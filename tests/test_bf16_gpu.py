@@ -154,13 +154,12 @@ def test_full_size_properties_mixtral():
     # CPU oracle on the same 64 tokens (bounded work: 64 tokens x 2 experts each)
     ref = O.moe_ref_fp32(x[:64].cpu(), w1.cpu(), w2.cpu(), ids[:64], wts[:64])
     assert O.max_rel_to_peak(a[:64], ref) <= TOL
-    # The single-launch pipeline adds top_k * H/128 = 224 bf16-rounded partial sums per output element
-    # here (the reference's split=False does the same, prime_moe/csrc/kernels/fused_moe_bf16_kernel.cu
-    # :288-326), so its rounding noise grows with H; at H = 14336 it is held to 6e-2 of the peak.
+    # The single-GEMM-launch pipeline reduces its top_k * H/128 = 224 split-K partials per element in
+    # fp32, so it meets the same gate (the reference's bf16 atomics do not at this H).
     b = run_mine(x, w1, w2, ids, wts, False)
     assert torch.isfinite(b.float()).all()
-    assert O.max_rel_to_peak(b, a) <= 6e-2
-    assert O.max_rel_to_peak(b[:64], ref) <= 6e-2
+    assert O.max_rel_to_peak(b, a) <= TOL
+    assert O.max_rel_to_peak(b[:64], ref) <= TOL
 
 
 @pytest.mark.skipif(not R.available(), reason="oracle/_ref (reference kernels) not built")
@@ -177,6 +176,8 @@ def test_vs_reference_kernels(T, K, E, N, k):
         R.fused_moe_bf16(xd, w1d, w2d, s, e, n, wd, ref_out, k, 128, 64, 4, 2, 1, 1, split)
         torch.cuda.synchronize()
         mine = run_mine(x, w1, w2, ids, wts, split)
-        assert O.max_rel_to_peak(mine, ref_out.cpu()) <= TOL
-        # and this library is at least as close to the fp32 oracle as the gate demands
+        # the reference's own result sits up to ~1.9e-2 from the fp32 oracle on these shapes (bf16
+        # atomics over top_k * H/128 partials), so two correct implementations may differ by more than
+        # one tolerance: bound the distance by 1.5 tolerances, and hold this library to the gate itself
+        assert O.max_rel_to_peak(mine, ref_out.cpu()) <= 1.5 * TOL
         assert O.max_rel_to_peak(mine, ref32) <= TOL
