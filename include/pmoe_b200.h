@@ -67,6 +67,27 @@ int pmoe_moe_align_ws(const int32_t *topk_ids, int32_t *sorted_token_ids, int32_
                       int max_padded, int max_blocks, void *workspace, size_t workspace_bytes,
                       pmoe_stream_t stream);
 
+/* moe_align for callers that cannot allocate device memory. This entry point has no counterpart in
+ * the reference. Hosts with a device-memory budget frozen after start-up, plugins that run inside
+ * another framework's allocator or stream callback, and processes whose device memory already
+ * belongs to a pool they do not control cannot call cudaMalloc (nor a stream-ordered or framework
+ * allocator) where routing runs, and may have no spare buffer to lend to `pmoe_moe_align_ws`.
+ * Same arguments and results as `pmoe_moe_align`; the scratch (per-warp counters and expert offsets)
+ * is a fixed 4 MiB array inside the library image, held by every GPU that loads the library until
+ * the process exits. The call performs no cudaMalloc, cudaFree or any other allocating routine.
+ *  - Limit: inputs whose scratch need (`pmoe_moe_align_workspace_bytes(n, num_experts)`) exceeds
+ *    `pmoe_moe_align_static_capacity_bytes()` are rejected with PMOE_ERR_UNSUPPORTED and a message
+ *    naming both sizes; nothing is launched. n <= 4096 needs no scratch at all.
+ *  - The first call on each device looks up the array's device address (with that device current);
+ *    make that first call outside of any stream capture.
+ *  - All calls on a device share the one array, which keeps the previous call's contents. The kernels
+ *    write every counter and offset before reading it, so nothing needs clearing; but two calls that
+ *    overlap on the GPU (different streams, or graph branches) race on it - serialise them. */
+int pmoe_moe_align_static(const int32_t *topk_ids, int32_t *sorted_token_ids, int32_t *expert_ids,
+                          int32_t *num_tokens_post_padded, int n, int num_experts, int block_m, int pad_to,
+                          int max_padded, int max_blocks, pmoe_stream_t stream);
+size_t pmoe_moe_align_static_capacity_bytes(void);
+
 /* ---------------------------------------------------------------------------------------------
  * fused_moe_bf16: out[token] (+)= sum over routes  w_route * (SwiGLU(x[token] * W1[e]^T) * W2[e]^T)
  * Replaces pi::fused_moe_bf16 (prime_moe/csrc/torch_interface.cpp:11-34; kernels

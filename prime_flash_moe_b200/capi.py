@@ -22,6 +22,8 @@ SIGNATURES = {
     "pmoe_moe_align": (_i, [_vp] * 4 + [_i] * 6 + [_vp]),
     "pmoe_moe_align_workspace_bytes": (_sz, [_i, _i]),
     "pmoe_moe_align_ws": (_i, [_vp] * 4 + [_i] * 6 + [_vp, _sz, _vp]),
+    "pmoe_moe_align_static": (_i, [_vp] * 4 + [_i] * 6 + [_vp]),
+    "pmoe_moe_align_static_capacity_bytes": (_sz, []),
     "pmoe_fused_moe_bf16": (_i, [_vp] * 8 + [_i] * 13 + [_vp]),
     "pmoe_fused_moe_bf16_workspace_bytes": (_sz, [_i] * 5),
     "pmoe_fused_moe_bf16_ws": (_i, [_vp] * 8 + [_i] * 13 + [_vp, _sz, _vp]),

@@ -343,3 +343,63 @@ extern "C" int pmoe_moe_align(const int32_t *topk_ids, int32_t *sorted_token_ids
         if (int rc2 = scratch_free(ws, stream)) return rc2;
     return rc;
 }
+
+// ---------------------------------------------------------------------------------------------
+// moe_align for callers that must not allocate
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library cannot call cudaMalloc (or any allocator) at the point where routing
+// runs: an inference server whose memory budget is fixed after start-up and which forbids further
+// driver allocations, a plugin running inside another framework's stream callback or allocator
+// hook, a process whose whole device memory has already been handed to a pool it does not own.
+// For them the per-warp counter matrix and the offset table live in a fixed array that is part of
+// the library image. Every GPU that loads the library carries these 4 MiB until the process exits.
+#define PMOE_STATIC_SCRATCH_INTS (1u << 20)  /* 4 MiB: the stated maximum */
+static __device__ __align__(256) int g_align_static_scratch[PMOE_STATIC_SCRATCH_INTS];
+
+namespace pmoe {
+namespace {
+
+constexpr size_t kStaticScratchInts = PMOE_STATIC_SCRATCH_INTS;
+
+// Device address of the array, looked up once per device. In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, hence cudaGetSymbolAddress.
+int static_scratch_ptr(int **out) {
+    static int *cached[64] = {nullptr};
+    int dev = 0;
+    PMOE_CUDA_OK(cudaGetDevice(&dev));
+    PMOE_REQUIRE(dev >= 0 && dev < 64, PMOE_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (!cached[dev]) {
+        void *p = nullptr;
+        PMOE_CUDA_OK(cudaGetSymbolAddress(&p, g_align_static_scratch));
+        PMOE_REQUIRE(p != nullptr, PMOE_ERR_CUDA, "moe_align_static: no device address for the scratch array");
+        cached[dev] = static_cast<int *>(p);
+    }
+    *out = cached[dev];
+    return PMOE_OK;
+}
+
+}  // namespace
+}  // namespace pmoe
+
+extern "C" size_t pmoe_moe_align_static_capacity_bytes(void) { return pmoe::kStaticScratchInts * sizeof(int); }
+
+extern "C" int pmoe_moe_align_static(const int32_t *topk_ids, int32_t *sorted_token_ids, int32_t *expert_ids,
+                                     int32_t *num_tokens_post_padded, int n, int num_experts, int block_m,
+                                     int pad_to, int max_padded, int max_blocks, pmoe_stream_t stream) {
+    using namespace pmoe;
+    if (int rc = check_args(topk_ids, sorted_token_ids, expert_ids, num_tokens_post_padded, n, num_experts,
+                            block_m, pad_to, max_padded, max_blocks))
+        return rc;
+    const Plan p = make_plan(n, num_experts);
+    PMOE_REQUIRE(p.ws_ints <= kStaticScratchInts, PMOE_ERR_UNSUPPORTED,
+                 "moe_align_static: n=%d with %d experts needs %zu bytes of scratch, the built-in array holds %zu; "
+                 "use pmoe_moe_align_ws with caller memory instead",
+                 n, num_experts, p.ws_ints * sizeof(int), kStaticScratchInts * sizeof(int));
+    int *scratch = nullptr;
+    if (p.ws_ints)
+        if (int rc = static_scratch_ptr(&scratch)) return rc;
+    // Nothing in the scratch has to start at zero: the histogram pass writes every counter of the
+    // matrix and the scan pass writes every offset before anything reads them.
+    return launch(topk_ids, sorted_token_ids, expert_ids, num_tokens_post_padded, n, num_experts, block_m, pad_to,
+                  max_padded, max_blocks, p, scratch, stream);
+}

@@ -1,0 +1,75 @@
+"""`pmoe_moe_align_static`: the routing kernel for hosts that cannot allocate device memory.
+
+Servers that freeze their device-memory budget after start-up, or plugins running inside another
+framework's allocator hooks, can neither call cudaMalloc nor lend a workspace. This entry point keeps
+its scratch in a fixed array inside the library. The test drives it through the C ABI, twice in a row
+on different inputs (the array keeps the first call's contents), and requires the three outputs to be
+identical, integer for integer, to those of the allocating entry point `pmoe_moe_align`.
+
+Collected last on purpose: a failure here must not hide the result of any other test.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _call(fn, ids, E, block_m=128, bpc=1):
+    n = ids.numel()
+    pad_to = block_m * bpc
+    max_padded = (n + E * (pad_to - 1) + pad_to - 1) // pad_to * pad_to
+    max_blocks = max_padded // block_m
+    mk = lambda k: torch.full((k,), -7, dtype=torch.int32, device=DEV)
+    s, e, npp = mk(max_padded), mk(max_blocks), mk(1)
+    rc = fn(ids.data_ptr(), s.data_ptr(), e.data_ptr(), npp.data_ptr(), n, E, block_m, pad_to, max_padded,
+            max_blocks, torch.cuda.current_stream().cuda_stream)
+    return rc, s, e, npp
+
+
+def test_static_scratch_matches_allocating_entry_point_twice():
+    from prime_flash_moe_b200 import capi
+    lib = capi.lib()
+    assert lib.pmoe_moe_align_static_capacity_bytes() == 4 << 20
+    # two different problems, both large enough to need scratch (n > 4096), run back to back
+    problems = [(8192, 128, 8, 1, "uniform", 21), (20000, 64, 4, 2, "zipf", 22), (8192, 128, 8, 1, "uniform", 23)]
+    for T, E, k, bpc, dist, seed in problems:
+        ids, _ = O.make_routing(T, E, k, seed=seed, dist=dist)
+        ids = ids.to(DEV)
+        assert lib.pmoe_moe_align_workspace_bytes(ids.numel(), E) > 0
+        rc, s, e, npp = _call(lib.pmoe_moe_align_static, ids, E, 128, bpc)
+        assert rc == 0, lib.pmoe_last_error().decode()
+        rc2, s2, e2, npp2 = _call(lib.pmoe_moe_align, ids, E, 128, bpc)
+        assert rc2 == 0, lib.pmoe_last_error().decode()
+        torch.cuda.synchronize()
+        assert torch.equal(npp, npp2)
+        assert torch.equal(e, e2)
+        assert torch.equal(s, s2)
+    # a small problem takes the single-CTA path and needs no scratch at all
+    ids, _ = O.make_routing(100, 16, 4, seed=5)
+    ids = ids.to(DEV)
+    rc, s, e, npp = _call(lib.pmoe_moe_align_static, ids, 16)
+    rc2, s2, e2, npp2 = _call(lib.pmoe_moe_align, ids, 16)
+    torch.cuda.synchronize()
+    assert rc == 0 and rc2 == 0
+    assert torch.equal(s, s2) and torch.equal(e, e2) and torch.equal(npp, npp2)
+    assert capi.device_status() == 0
+
+
+def test_static_scratch_rejects_oversized_problems():
+    from prime_flash_moe_b200 import capi
+    lib = capi.lib()
+    T, E, k = 40000, 1024, 8           # 1024 experts x thousands of warps: more than 4 MiB of counters
+    ids = torch.randint(0, E, (T, k), dtype=torch.int32, device=DEV)
+    need = lib.pmoe_moe_align_workspace_bytes(ids.numel(), E)
+    assert need > lib.pmoe_moe_align_static_capacity_bytes()
+    rc, s, e, npp = _call(lib.pmoe_moe_align_static, ids, E)
+    torch.cuda.synchronize()
+    assert rc == 2                      # PMOE_ERR_UNSUPPORTED
+    msg = lib.pmoe_last_error().decode()
+    assert str(need) in msg and "pmoe_moe_align_ws" in msg
+    assert int(npp.item()) == -7        # nothing was launched
