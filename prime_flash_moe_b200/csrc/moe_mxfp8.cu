@@ -1,7 +1,621 @@
-// placeholder until the mxfp8 kernels land
+// mxfp8 (OCP-MX: e4m3 values, one e8m0 scale per 32 K-elements) fused MoE FFN for sm_100a.
+//
+// Replaces the kernels and launcher of prime_moe/csrc/kernels/fused_moe_mxfp8_kernel.cu
+// (gather_x_mxfp8_kernel :56-80, fused_moe_mxfp8_kernel :82-503, fused_moe_mxfp8_down_kernel :513-679,
+// launch_fused_moe_mxfp8_kernel :681-866) behind pmoe_fused_moe_mxfp8.
+//
+// Same decomposition and warp roles as the bf16 kernels (moe_bf16.cu): persistent CTAs, warp 0 = TMA
+// producer, warp 1 = tcgen05.mma issuer, 8 epilogue warps. Differences:
+//   * MMA = tcgen05.mma.kind::mxf8f6f4.block_scale, M128 x N256 x K32; a ring slot holds 128 K-bytes:
+//     A 128x128 B + B 256x128 B (128-byte swizzle) + three 512-byte scale tiles (A, B gate half / first
+//     128 rows, B up half / last 128 rows).
+//   * scale tiles travel global -> shared by untiled bulk copies, shared -> TMEM by
+//     tcgen05.cp.32x128b.warpx4 (4 TMEM columns per tile), issued by the MMA thread ahead of the four
+//     MMAs of the slot; the instruction descriptor's scale-factor ids select the K-block byte.
+//     Eight rotating 16-column TMEM regions keep the scales of in-flight slots apart.
+//   * TMEM: one 256-column accumulator (the scale regions leave no room for a second one). The
+//     epilogue warps first DRAIN the accumulator into registers (128 fp32 per thread), hand it back to
+//     the MMA thread, and only then do their arithmetic and stores, so the next tile's main loop
+//     overlaps all of the epilogue except the drain itself.
+//   * gate/up epilogue: SwiGLU in fp32, then per row and per 32 columns the MX re-quantisation of the
+//     reference (fused_moe_mxfp8_kernel.cu:4-20, 375-403): e = clamp(exponent(amax) - 8, 0, 254),
+//     q = satfinite_e4m3(v * 2^(127-e)); e4m3 tile -> TMA store, scale bytes -> 512-byte tiles.
+//   * routing weight stays fp32 (as in the reference's mxfp8 path).
+//
+// Scale tile layout everywhere (prime_moe/__init__.py:106-115): 128 rows x 4 K-blocks, byte
+// (r%32)*16 + (r/32)*4 + kb.
+#include <cuda_fp8.h>
+#include <stdio.h>
+
+#include <algorithm>
+
 #include "host_common.h"
+#include "ptx.cuh"
+#include "tile_sched.cuh"
+
 namespace pmoe {
+
 __device__ int g_status_mxfp8 = 0;
+
+namespace {
+
+constexpr int BM = kBlockM;
+constexpr int BKB = 128;                         // K bytes (= e4m3 elements) per ring slot
+constexpr uint32_t A_BYTES = BM * BKB;           // 16 KB
+constexpr uint32_t B_BYTES = 256 * BKB;          // 32 KB
+constexpr uint32_t SF_TILE = 512;
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + 2048;   // 50 KB: + SFA, SFB(2), pad
+constexpr uint32_t STAGE_TX_BYTES = A_BYTES + B_BYTES + 3 * SF_TILE;
+constexpr uint32_t ACT_TILE_BYTES = 128 * 128;   // e4m3 activation tile (store staging / fused A operand)
+constexpr int MAX_STAGES = 4;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t SF_TMEM_BASE = 256;           // columns [256, 384): eight 16-column scale regions
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr uint32_t BAR_BYTES = 256;
+
+struct Args {
+    const int32_t *sorted_ids;
+    const int32_t *expert_ids;
+    const int32_t *npp;
+    const float *topk_weights;
+    __nv_bfloat16 *out;
+    float *acc32;
+    const uint8_t *w_scales;    // blocked, [E*N/128][K/128][512]
+    const uint8_t *w2_scales;   // blocked, [E*K/128][H/128][512]
+    const uint8_t *xsf_tiles;   // up kernel (split): [blocks][K/128][512] re-tiled activation scales
+    uint8_t *act_sf;            // [blocks][H/128][512] scales of the re-quantised activation
+    int M, K, N, H;
+    int top_k;
+    int sorted_num;
+    int stages;
+    int zero_out;
+    int use_pdl;
+};
+
+struct Smem {
+    uint32_t ring, act, bars;
+    __device__ __forceinline__ uint32_t a(int s) const { return ring + s * STAGE_BYTES; }
+    __device__ __forceinline__ uint32_t b(int s) const { return ring + s * STAGE_BYTES + A_BYTES; }
+    __device__ __forceinline__ uint32_t sfa(int s) const { return ring + s * STAGE_BYTES + A_BYTES + B_BYTES; }
+    __device__ __forceinline__ uint32_t sfb(int s) const { return sfa(s) + SF_TILE; }
+    __device__ __forceinline__ uint32_t full(int s) const { return bars + 8 * s; }
+    __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8 * (MAX_STAGES + s); }
+    __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * MAX_STAGES + i); }
+    __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * MAX_STAGES + 12); }
+};
+__device__ __forceinline__ Smem carve(const uint8_t *raw, int stages, bool with_act) {
+    Smem s;
+    s.ring = (smem_u32(raw) + 1023u) & ~1023u;
+    s.act = s.ring + stages * STAGE_BYTES;
+    s.bars = s.act + (with_act ? ACT_TILE_BYTES + 1024 : 0);   // + one 512-byte scale tile (fused), padded
+    return s;
+}
+size_t smem_bytes(int stages, bool with_act) {
+    return 1024 + static_cast<size_t>(stages) * STAGE_BYTES + (with_act ? ACT_TILE_BYTES + 1024 : 0) + BAR_BYTES;
+}
+
+__device__ __forceinline__ void drain_fills(const Smem &sm, int stages, long long issued) {
+    const long long first = issued > stages ? issued - stages : 0;
+    for (long long f = first; f < issued; ++f) {
+        const uint32_t bar = sm.full(static_cast<int>(f % stages));
+        const uint32_t parity = static_cast<uint32_t>((f / stages) & 1);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(bar, parity)) {
+            if (globaltimer_ns() - t0 > 20000000ull) break;
+        }
+    }
+}
+
+__device__ __forceinline__ void ld32(float *dst, uint32_t taddr) {
+    tmem_ld_32x32(*reinterpret_cast<float(*)[32]>(dst), taddr);
+}
+
+// MX block scale of 32 values: returns the biased e8m0 exponent, *inv = 2^(127 - e)
+__device__ __forceinline__ uint32_t mx_block_scale(float amax, float *inv) {
+    int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
+    e = max(0, min(e, 254));
+    const uint32_t field = static_cast<uint32_t>(254 - e);
+    *inv = __uint_as_float(field ? field << 23 : 0x00400000u);   // 2^-127 is subnormal
+    return static_cast<uint32_t>(e);
+}
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+// one ring slot -> TMEM scale region, then four K32 MMAs
+__device__ __forceinline__ void issue_slot(uint32_t d, uint32_t a_smem, uint32_t b_smem, uint32_t sfa_smem,
+                                           uint32_t sfb0_smem, uint32_t sfb1_smem, uint32_t tmem_base,
+                                           long long fill, bool first, uint32_t idesc, int n_sfb_tiles) {
+    const uint32_t sfa_t = tmem_base + SF_TMEM_BASE + 16u * static_cast<uint32_t>(fill & 7);
+    const uint32_t sfb_t = sfa_t + 4;
+    tmem_cp_sf_32x128b_warpx4(sfa_t, smem_desc_sf(sfa_smem));
+    tmem_cp_sf_32x128b_warpx4(sfb_t, smem_desc_sf(sfb0_smem));
+    if (n_sfb_tiles > 1) tmem_cp_sf_32x128b_warpx4(sfb_t + 4, smem_desc_sf(sfb1_smem));
+#pragma unroll
+    for (uint32_t kb = 0; kb < 4; ++kb)
+        umma_mxf8(d, smem_desc_sw128(a_smem + kb * 32), smem_desc_sw128(b_smem + kb * 32),
+                  idesc_with_sf_ids(idesc, kb, kb), sfa_t, sfb_t, (!first || kb != 0) ? 1u : 0u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// pre-pass of the split pipeline: x_sorted[row] = x[token(row)] (e4m3 bytes) and the row-major
+// activation scales re-tiled into 512-byte tiles [block][K/128]. One warp per row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gather_rows_mxfp8_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ x_scales,
+                         uint8_t *__restrict__ x_sorted, uint8_t *__restrict__ xsf_tiles, const Args a) {
+    const int warps_per_cta = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rows = live_row_blocks(a.npp, a.sorted_num) * BM;
+    const int chunks = a.K / 16;
+    const int kblocks = a.K / 32;
+    for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
+        const int pair = a.sorted_ids[row];
+        int tok = pair >= 0 ? pair / a.top_k : 0;
+        if (tok >= a.M) tok = 0;
+        const int4 *src = reinterpret_cast<const int4 *>(x + static_cast<size_t>(tok) * a.K);
+        int4 *dst = reinterpret_cast<int4 *>(x_sorted + static_cast<size_t>(row) * a.K);
+        for (int ch = lane; ch < chunks; ch += 32) dst[ch] = __ldg(src + ch);
+        const int r = row & 127;
+        uint8_t *tiles = xsf_tiles + static_cast<size_t>(row >> 7) * (a.K / 128) * SF_TILE;
+        const uint8_t *srow = x_scales + static_cast<size_t>(tok) * kblocks;
+        for (int kb = lane; kb < kblocks; kb += 32)
+            tiles[(kb >> 2) * SF_TILE + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = srow[kb];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// up kernel (split): misc barriers 0 tmem_full | 1 tmem_empty | 2 staged | 3 stage_free
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1)
+moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
+                    const __grid_constant__ CUtensorMap map_act, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const Smem sm = carve(smem_raw, a.stages, true);
+    int *status = &g_status_mxfp8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int epi_threads = EPI_WARPS * 32;
+
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), epi_threads);
+        mbar_init(sm.misc(2), epi_threads);
+        mbar_init(sm.misc(3), 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w1);
+        tma_prefetch_desc(&map_act);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    const int m_blocks = live_row_blocks(a.npp, a.sorted_num);
+    const int n_tiles = a.H / 128;
+    const int num_tiles = m_blocks * n_tiles;
+    const int ksteps = a.K / BKB;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Coord c = tile_coord(t, m_blocks, n_tiles);
+                const int e = a.expert_ids[c.m_blk];
+                const int row_gate = e * a.N + c.n_tile * 128;
+                const int row_up = row_gate + a.H;
+                const uint8_t *sf_gate = a.w_scales + static_cast<size_t>(row_gate >> 7) * ksteps * SF_TILE;
+                const uint8_t *sf_up = a.w_scales + static_cast<size_t>(row_up >> 7) * ksteps * SF_TILE;
+                const uint8_t *sf_x = a.xsf_tiles + static_cast<size_t>(c.m_blk) * ksteps * SF_TILE;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sm.full(s), STAGE_TX_BYTES);
+                    tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BKB, c.m_blk * BM);
+                    tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BKB, row_gate);
+                    tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BKB, row_up);
+                    bulk_load_1d(sm.sfa(s), sf_x + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s), sf_gate + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s) + SF_TILE, sf_up + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+            if (!ok) drain_fills(sm, a.stages, issued);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_mxf8_f32(128, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            long long fill = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                ok = mbar_wait(sm.misc(1), (it & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int ks = 0; ks < ksteps; ++ks, ++fill) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_slot(tmem_base, sm.a(s), sm.b(s), sm.sfa(s), sm.sfb(s), sm.sfb(s) + SF_TILE, tmem_base, fill,
+                               ks == 0, idesc, 2);
+                    umma_commit(sm.empty(s));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit(sm.misc(0));
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const int et = threadIdx.x - 64;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int cg = ew >> 2;          // 0: activation columns [0,64), 1: [64,128)
+        if (a.zero_out) {
+            int4 *o4 = reinterpret_cast<int4 *>(a.out);
+            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const int4 z = make_int4(0, 0, 0, 0);
+            for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
+                 i += static_cast<long long>(gridDim.x) * epi_threads)
+                o4[i] = z;
+        }
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            if (!mbar_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            tc_fence_after();
+            float g[64], u[64];
+            ld32(g, tmem_addr(tmem_base, lane_base, cg * 64));
+            ld32(g + 32, tmem_addr(tmem_base, lane_base, cg * 64 + 32));
+            ld32(u, tmem_addr(tmem_base, lane_base, 128 + cg * 64));
+            ld32(u + 32, tmem_addr(tmem_base, lane_base, 128 + cg * 64 + 32));
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(sm.misc(1));   // accumulator drained: the next tile's main loop may start
+#pragma unroll
+            for (int i = 0; i < 64; ++i) g[i] = swiglu(g[i], u[i]);
+            if (!mbar_wait(sm.misc(3), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;   // staging tile free
+            uint8_t *sf_tile = a.act_sf + (static_cast<size_t>(c.m_blk) * n_tiles + c.n_tile) * SF_TILE;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(g[blk * 32 + i]));
+                float inv;
+                const uint32_t e = mx_block_scale(amax, &inv);
+                sf_tile[(row & 31) * 16 + (row >> 5) * 4 + cg * 2 + blk] = static_cast<uint8_t>(e);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float *v = g + blk * 32 + j * 16;
+                    const uint32_t chunk16 = static_cast<uint32_t>(cg * 4 + blk * 2 + j);
+                    st_shared_v4(sm.act + row * 128 + ((chunk16 ^ (row & 7)) << 4),
+                                 pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                                 pack_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv),
+                                 pack_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv),
+                                 pack_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv));
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(sm.misc(2));
+            if (et == 0) {
+                if (!mbar_wait(sm.misc(2), it & 1, status, ST_TIMEOUT_ACT)) break;
+                tma_store_2d(&map_act, sm.act, c.n_tile * 128, c.m_blk * BM);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+                mbar_arrive(sm.misc(3));
+            }
+        }
+        if (et == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// down kernel (split): misc barriers 0 tmem_full | 1 tmem_empty
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1)
+moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_w2,
+                      const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const Smem sm = carve(smem_raw, a.stages, false);
+    int *status = &g_status_mxfp8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int epi_threads = EPI_WARPS * 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), epi_threads);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_act);
+        tma_prefetch_desc(&map_w2);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (a.use_pdl) pdl_wait_primary();
+
+    const int m_blocks = live_row_blocks(a.npp, a.sorted_num);
+    const int n_tiles = a.K / 256;
+    const int num_tiles = m_blocks * n_tiles;
+    const int ksteps = a.H / BKB;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Coord c = tile_coord(t, m_blocks, n_tiles);
+                const int e = a.expert_ids[c.m_blk];
+                const int w2_row = e * a.K + c.n_tile * 256;
+                const uint8_t *sf_w0 = a.w2_scales + static_cast<size_t>(w2_row >> 7) * ksteps * SF_TILE;
+                const uint8_t *sf_w1 = sf_w0 + static_cast<size_t>(ksteps) * SF_TILE;
+                const uint8_t *sf_a = a.act_sf + static_cast<size_t>(c.m_blk) * ksteps * SF_TILE;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sm.full(s), STAGE_TX_BYTES);
+                    tma_load_2d(sm.a(s), &map_act, sm.full(s), ks * BKB, c.m_blk * BM);
+                    tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BKB, w2_row);
+                    bulk_load_1d(sm.sfa(s), sf_a + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s), sf_w0 + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s) + SF_TILE, sf_w1 + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+            if (!ok) drain_fills(sm, a.stages, issued);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_mxf8_f32(128, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            long long fill = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                ok = mbar_wait(sm.misc(1), (it & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int ks = 0; ks < ksteps; ++ks, ++fill) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_slot(tmem_base, sm.a(s), sm.b(s), sm.sfa(s), sm.sfb(s), sm.sfb(s) + SF_TILE, tmem_base, fill,
+                               ks == 0, idesc, 2);
+                    umma_commit(sm.empty(s));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit(sm.misc(0));
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int cg = ew >> 2;          // output columns [cg*128, cg*128+128) of the 256-wide tile
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int pair = a.sorted_ids[c.m_blk * BM + row];
+            const int tok = pair >= 0 ? pair / a.top_k : 0;
+            const bool valid = pair >= 0 && tok < a.M;
+            const float wgt = valid ? a.topk_weights[pair] : 0.f;
+            __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + c.n_tile * 256 + cg * 128;
+            if (!mbar_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            tc_fence_after();
+            float v[128];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) ld32(v + q * 32, tmem_addr(tmem_base, lane_base, cg * 128 + q * 32));
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(sm.misc(1));
+            if (valid) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    red_add_bf16x8(dst + j * 8, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                                   pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                                   pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                                   pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct Problem {
+    const void *x, *x_scales, *w, *w_scales, *w2, *w2_scales;
+    void *out;
+    const int32_t *sorted_ids, *expert_ids, *npp;
+    const float *topk_weights;
+    int top_k, M, K, N, E, sorted_num, block_n, warp_n, stages, bpc, split;
+};
+
+int validate(const Problem &p, int block_m) {
+    PMOE_REQUIRE(p.x && p.x_scales && p.w && p.w_scales && p.w2 && p.w2_scales && p.out && p.sorted_ids &&
+                     p.expert_ids && p.npp && p.topk_weights,
+                 PMOE_ERR_BAD_ARG, "fused_moe_mxfp8: null pointer");
+    PMOE_REQUIRE(p.M > 0 && p.K > 0 && p.N > 0 && p.E > 0 && p.top_k > 0 && p.sorted_num >= 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_mxfp8: M, K, N, num_experts, top_k must be positive");
+    PMOE_REQUIRE((p.K & 255) == 0, PMOE_ERR_BAD_ARG, "K dimension must be a multiple of 256 on the mxfp8 path");
+    PMOE_REQUIRE((p.N & 255) == 0, PMOE_ERR_BAD_ARG, "N dimension must be a multiple of 256 on the mxfp8 path");
+    PMOE_REQUIRE((p.block_n == 64 && p.warp_n == 4) || (p.block_n == 32 && p.warp_n == 8), PMOE_ERR_UNSUPPORTED,
+                 "(block_n, warp_n) must be (64, 4) or (32, 8)");
+    PMOE_REQUIRE(p.stages > 0 && p.stages < 5, PMOE_ERR_UNSUPPORTED, "mxfp8 supports stages in 1..4");
+    PMOE_REQUIRE(p.bpc == 1, PMOE_ERR_UNSUPPORTED,
+                 "mxfp8 supports bpc=1 only: tensor memory has no room for a second accumulator plus scale factors");
+    PMOE_REQUIRE(block_m == 128, PMOE_ERR_UNSUPPORTED, "Blackwell tcgen05 fused MoE requires block_m=128.");
+    PMOE_REQUIRE(p.sorted_num % 128 == 0, PMOE_ERR_BAD_ARG, "sorted_num must be a multiple of block_m");
+    PMOE_REQUIRE(static_cast<long long>(p.E) * p.N < (1ll << 31) && static_cast<long long>(p.E) * p.K < (1ll << 31),
+                 PMOE_ERR_UNSUPPORTED, "E*N and E*K must fit in 31 bits");
+    const uintptr_t align = reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.w) |
+                            reinterpret_cast<uintptr_t>(p.w2) | reinterpret_cast<uintptr_t>(p.out) |
+                            reinterpret_cast<uintptr_t>(p.w_scales) | reinterpret_cast<uintptr_t>(p.w2_scales) |
+                            reinterpret_cast<uintptr_t>(p.sorted_ids);
+    PMOE_REQUIRE((align & 15) == 0, PMOE_ERR_BAD_ARG,
+                 "x, w, w2, out, w_scales, w2_scales and sorted_token_ids must be 16-byte aligned");
+    return PMOE_OK;
+}
+
+template <typename Kernel>
+int set_smem(Kernel k, size_t bytes) {
+    PMOE_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    return PMOE_OK;
+}
+
+struct Workspace {
+    size_t act_q, act_sf, x_sorted, xsf, total;
+};
+Workspace plan_workspace(int M, int K, int N, int sorted_num, int split) {
+    Workspace w{};
+    (void)M;
+    const size_t H = N / 2, blocks = sorted_num / BM;
+    if (!split) return w;
+    auto up = [](size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); };
+    w.act_q = 0;
+    w.act_sf = up(w.act_q + static_cast<size_t>(sorted_num) * H);
+    w.x_sorted = up(w.act_sf + blocks * (H / 128) * SF_TILE);
+    w.xsf = up(w.x_sorted + static_cast<size_t>(sorted_num) * K);
+    w.total = up(w.xsf + blocks * (K / 128) * SF_TILE);
+    return w;
+}
+
+int run(const Problem &p, void *workspace, cudaStream_t stream) {
+    const int H = p.N / 2;
+    const int max_blocks = p.sorted_num / BM;
+    if (max_blocks == 0) {
+        if (p.split) PMOE_CUDA_OK(cudaMemsetAsync(p.out, 0, static_cast<size_t>(p.M) * p.K * 2, stream));
+        return PMOE_OK;
+    }
+    PMOE_REQUIRE(p.split, PMOE_ERR_UNSUPPORTED, "fused_moe_mxfp8: split=False is not available in this build");
+    Args a{};
+    a.sorted_ids = p.sorted_ids;
+    a.expert_ids = p.expert_ids;
+    a.npp = p.npp;
+    a.topk_weights = p.topk_weights;
+    a.out = static_cast<__nv_bfloat16 *>(p.out);
+    a.w_scales = static_cast<const uint8_t *>(p.w_scales);
+    a.w2_scales = static_cast<const uint8_t *>(p.w2_scales);
+    a.M = p.M;
+    a.K = p.K;
+    a.N = p.N;
+    a.H = H;
+    a.top_k = p.top_k;
+    a.sorted_num = p.sorted_num;
+    a.stages = std::min(p.stages, MAX_STAGES);
+    const int sms = sm_count();
+    const int phases = phase_mask();
+
+    PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_mxfp8: workspace must be 1024-byte aligned");
+    const Workspace w = plan_workspace(p.M, p.K, p.N, p.sorted_num, 1);
+    uint8_t *base = static_cast<uint8_t *>(workspace);
+    uint8_t *act_q = base + w.act_q, *act_sf = base + w.act_sf, *x_sorted = base + w.x_sorted, *xsf = base + w.xsf;
+    a.act_sf = act_sf;
+    a.xsf_tiles = xsf;
+
+    CUtensorMap map_x, map_w1, map_act, map_w2;
+    if (int rc = make_tmap_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x_sorted, p.sorted_num, p.K, 128, BKB,
+                              CU_TENSOR_MAP_SWIZZLE_128B, "x_sorted"))
+        return rc;
+    if (int rc = make_tmap_2d(&map_w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.w, static_cast<uint64_t>(p.E) * p.N, p.K,
+                              128, BKB, CU_TENSOR_MAP_SWIZZLE_128B, "w"))
+        return rc;
+    if (int rc = make_tmap_2d(&map_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, act_q, p.sorted_num, H, 128, BKB,
+                              CU_TENSOR_MAP_SWIZZLE_128B, "act"))
+        return rc;
+    if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.w2, static_cast<uint64_t>(p.E) * p.K, H,
+                              256, BKB, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
+        return rc;
+
+    if (phases & 1) {
+        gather_rows_mxfp8_kernel<<<std::min(4 * sms, (p.sorted_num + 7) / 8), 256, 0, stream>>>(
+            static_cast<const uint8_t *>(p.x), static_cast<const uint8_t *>(p.x_scales), x_sorted, xsf, a);
+        PMOE_CUDA_OK(cudaGetLastError());
+    }
+    if (phases & 2) {
+        Args up = a;
+        up.zero_out = 1;
+        const size_t smem = smem_bytes(up.stages, true);
+        if (int rc = set_smem(moe_up_mxfp8_kernel, smem)) return rc;
+        const int tiles = max_blocks * (H / 128);
+        moe_up_mxfp8_kernel<<<std::min(tiles, sms), THREADS, smem, stream>>>(map_x, map_w1, map_act, up);
+        PMOE_CUDA_OK(cudaGetLastError());
+    }
+    if (phases & 4) {
+        Args dn = a;
+        dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
+        const size_t smem = smem_bytes(dn.stages, false);
+        if (int rc = set_smem(moe_down_mxfp8_kernel, smem)) return rc;
+        const int tiles = max_blocks * (p.K / 256);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(std::min(tiles, sms));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = dn.use_pdl ? 1 : 0;
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_mxfp8_kernel, map_act, map_w2, dn));
+    }
+    return PMOE_OK;
+}
+
+}  // namespace
+
 int status_fetch_mxfp8(int *value, bool reset) {
     if (value) PMOE_CUDA_OK(cudaMemcpyFromSymbol(value, g_status_mxfp8, sizeof(int)));
     if (reset) {
@@ -10,11 +624,47 @@ int status_fetch_mxfp8(int *value, bool reset) {
     }
     return PMOE_OK;
 }
+
+}  // namespace pmoe
+
+extern "C" size_t pmoe_fused_moe_mxfp8_workspace_bytes(int M, int K, int N, int sorted_num, int split) {
+    if (sorted_num <= 0 || N <= 0 || K <= 0) return 0;
+    return pmoe::plan_workspace(M, K, N, sorted_num, split).total;
 }
-extern "C" size_t pmoe_fused_moe_mxfp8_workspace_bytes(int, int, int, int, int) { return 0; }
-extern "C" int pmoe_fused_moe_mxfp8_ws(const void *, const void *, const void *, const void *, const void *, const void *, void *, const int32_t *, const int32_t *, const int32_t *, const float *, int, int, int, int, int, int, int, int, int, int, int, int, void *, size_t, pmoe_stream_t) {
-    return pmoe::set_error(PMOE_ERR_UNSUPPORTED, "mxfp8 not built yet");
+
+extern "C" int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, const void *w_scales,
+                                       const void *w2, const void *w2_scales, void *out,
+                                       const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                       const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
+                                       int M, int K, int N, int num_experts, int sorted_num, int block_m,
+                                       int block_n, int warp_n, int stages, int bpc, int split, void *workspace,
+                                       size_t workspace_bytes, pmoe_stream_t stream) {
+    using namespace pmoe;
+    Problem p{x, x_scales, w, w_scales, w2, w2_scales, out, sorted_token_ids, expert_ids, num_tokens_post_padded,
+              topk_weights, top_k, M, K, N, num_experts, sorted_num, block_n, warp_n, stages, bpc, split ? 1 : 0};
+    if (int rc = validate(p, block_m)) return rc;
+    const size_t need = pmoe_fused_moe_mxfp8_workspace_bytes(M, K, N, sorted_num, split);
+    PMOE_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), PMOE_ERR_BAD_ARG,
+                 "fused_moe_mxfp8: workspace of %zu bytes required, got %zu", need, workspace_bytes);
+    return run(p, workspace, stream);
 }
-extern "C" int pmoe_fused_moe_mxfp8(const void *, const void *, const void *, const void *, const void *, const void *, void *, const int32_t *, const int32_t *, const int32_t *, const float *, int, int, int, int, int, int, int, int, int, int, int, int, pmoe_stream_t) {
-    return pmoe::set_error(PMOE_ERR_UNSUPPORTED, "mxfp8 not built yet");
+
+extern "C" int pmoe_fused_moe_mxfp8(const void *x, const void *x_scales, const void *w, const void *w_scales,
+                                    const void *w2, const void *w2_scales, void *out,
+                                    const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                    const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k, int M,
+                                    int K, int N, int num_experts, int sorted_num, int block_m, int block_n,
+                                    int warp_n, int stages, int bpc, int split, pmoe_stream_t stream) {
+    using namespace pmoe;
+    Problem p{x, x_scales, w, w_scales, w2, w2_scales, out, sorted_token_ids, expert_ids, num_tokens_post_padded,
+              topk_weights, top_k, M, K, N, num_experts, sorted_num, block_n, warp_n, stages, bpc, split ? 1 : 0};
+    if (int rc = validate(p, block_m)) return rc;
+    const size_t need = pmoe_fused_moe_mxfp8_workspace_bytes(M, K, N, sorted_num, split);
+    void *ws = nullptr;
+    if (need)
+        if (int rc = scratch_alloc(&ws, need, stream)) return rc;
+    const int rc = run(p, ws, stream);
+    if (ws)
+        if (int rc2 = scratch_free(ws, stream)) return rc2;
+    return rc;
 }

@@ -94,7 +94,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait. Returns false if the wait gave up (own time-out, or another thread of the grid
 // already recorded an error); the status word then holds the first error code.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int *status, int code) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int *status, int code) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t n = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -144,6 +144,12 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *map
         " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
         : "memory");
+}
+// untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16)
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -222,6 +228,12 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1024 >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
+}
+
+// Shared-memory descriptor of one 512-byte scale-factor tile (32 lines of 16 bytes, no swizzle) for
+// tcgen05.cp.32x128b: four 8-line core matrices 128 bytes apart (SBO = 128).
+__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr) {
+    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
 }
 
 // Instruction descriptor, kind::f16, bf16 x bf16 -> fp32, both operands K-major.
