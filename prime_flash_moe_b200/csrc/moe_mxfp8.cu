@@ -472,6 +472,255 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
 }
 
 // ---------------------------------------------------------------------------------------------
+// fused kernel (split == 0): per (row block, 128-wide H slice): gate/up GEMM -> SwiGLU -> MX requant ->
+// e4m3 activation tile + its scale tile kept in shared memory -> down GEMM against w2[e][:, slice] in
+// 128-column chunks -> weighted fp32 reductions into the zeroed fp32 buffer (split-K over H/128 slices).
+//   TMEM: [0,256) gate|up accumulator, [256,384) scale regions, [384,512) down accumulator
+//   misc barriers: 0 up_full | 1 up_empty | 2 act_ready | 3 act_free | 4 dn_full | 5 dn_empty
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1)
+moe_fused_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
+                       const __grid_constant__ CUtensorMap map_w2, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const Smem sm = carve(smem_raw, a.stages, true);
+    const uint32_t act_sf_smem = sm.act + ACT_TILE_BYTES;
+    int *status = &g_status_mxfp8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int epi_threads = EPI_WARPS * 32;
+    constexpr uint32_t DN_ACC = 384;
+
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), epi_threads);
+        mbar_init(sm.misc(2), epi_threads);
+        mbar_init(sm.misc(3), 1);
+        mbar_init(sm.misc(4), 1);
+        mbar_init(sm.misc(5), epi_threads);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w1);
+        tma_prefetch_desc(&map_w2);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (a.use_pdl) pdl_wait_primary();   // x_sorted / scale tiles come from the gather pre-pass
+
+    const int m_blocks = live_row_blocks(a.npp, a.sorted_num);
+    const int n_tiles = a.H / 128;
+    const int num_tiles = m_blocks * n_tiles;
+    const int ksteps = a.K / BKB;
+    const int dn_chunks = a.K / 128;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Coord c = tile_coord(t, m_blocks, n_tiles);
+                const int e = a.expert_ids[c.m_blk];
+                const int row_gate = e * a.N + c.n_tile * 128;
+                const int row_up = row_gate + a.H;
+                const uint8_t *sf_gate = a.w_scales + static_cast<size_t>(row_gate >> 7) * ksteps * SF_TILE;
+                const uint8_t *sf_up = a.w_scales + static_cast<size_t>(row_up >> 7) * ksteps * SF_TILE;
+                const uint8_t *sf_x = a.xsf_tiles + static_cast<size_t>(c.m_blk) * ksteps * SF_TILE;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sm.full(s), STAGE_TX_BYTES);
+                    tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BKB, c.m_blk * BM);
+                    tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BKB, row_gate);
+                    tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BKB, row_up);
+                    bulk_load_1d(sm.sfa(s), sf_x + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s), sf_gate + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s) + SF_TILE, sf_up + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!ok) break;
+                // down slots: 128 rows of w2[e] (output columns) x the 128 H-bytes of this slice + their scale tile
+                const uint8_t *sf_w2 = a.w2_scales + (static_cast<size_t>(e) * (a.K / 128) * n_tiles + c.n_tile) * SF_TILE;
+                for (int ch = 0; ch < dn_chunks; ++ch) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sm.full(s), B_BYTES / 2 + SF_TILE);
+                    tma_load_2d(sm.b(s), &map_w2, sm.full(s), c.n_tile * 128, e * a.K + ch * 128);
+                    bulk_load_1d(sm.sfb(s), sf_w2 + static_cast<size_t>(ch) * n_tiles * SF_TILE, SF_TILE, sm.full(s));
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+            if (!ok) drain_fills(sm, a.stages, issued);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_up = idesc_mxf8_f32(128, 256);
+            constexpr uint32_t idesc_dn = idesc_mxf8_f32(128, 128);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            long long fill = 0, dn_it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                ok = mbar_wait(sm.misc(1), (it & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int ks = 0; ks < ksteps; ++ks, ++fill) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_slot(tmem_base, sm.a(s), sm.b(s), sm.sfa(s), sm.sfb(s), sm.sfb(s) + SF_TILE, tmem_base, fill,
+                               ks == 0, idesc_up, 2);
+                    umma_commit(sm.empty(s));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(sm.misc(0));
+                ok = mbar_wait(sm.misc(2), it & 1, status, ST_TIMEOUT_ACT);
+                if (!ok) break;
+                tc_fence_after();
+                for (int ch = 0; ch < dn_chunks; ++ch, ++fill, ++dn_it) {
+                    ok = mbar_wait(sm.misc(5), static_cast<uint32_t>((dn_it & 1) ^ 1), status, ST_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_slot(tmem_base + DN_ACC, sm.act, sm.b(s), act_sf_smem, sm.sfb(s), 0, tmem_base, fill, true,
+                               idesc_dn, 1);
+                    umma_commit(sm.empty(s));
+                    umma_commit(sm.misc(4));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit(sm.misc(3));
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int cg = ew >> 2;
+        uint8_t *act_sf_generic = const_cast<uint8_t *>(smem_raw) + (act_sf_smem - smem_u32(smem_raw));
+        int it = 0;
+        long long dn_it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int pair = a.sorted_ids[c.m_blk * BM + row];
+            const int tok = pair >= 0 ? pair / a.top_k : 0;
+            const bool valid = pair >= 0 && tok < a.M;
+            const float wgt = valid ? a.topk_weights[pair] : 0.f;
+            float *dst = a.acc32 + static_cast<size_t>(valid ? tok : 0) * a.K + cg * 64;
+            if (!mbar_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            tc_fence_after();
+            {
+                float g[64], u[64];
+                ld32(g, tmem_addr(tmem_base, lane_base, cg * 64));
+                ld32(g + 32, tmem_addr(tmem_base, lane_base, cg * 64 + 32));
+                ld32(u, tmem_addr(tmem_base, lane_base, 128 + cg * 64));
+                ld32(u + 32, tmem_addr(tmem_base, lane_base, 128 + cg * 64 + 32));
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(sm.misc(1));
+#pragma unroll
+                for (int i = 0; i < 64; ++i) g[i] = swiglu(g[i], u[i]);
+                if (!mbar_wait(sm.misc(3), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;   // act tile reusable
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk) {
+                    float amax = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(g[blk * 32 + i]));
+                    float inv;
+                    const uint32_t e = mx_block_scale(amax, &inv);
+                    act_sf_generic[(row & 31) * 16 + (row >> 5) * 4 + cg * 2 + blk] = static_cast<uint8_t>(e);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float *v = g + blk * 32 + j * 16;
+                        const uint32_t chunk16 = static_cast<uint32_t>(cg * 4 + blk * 2 + j);
+                        st_shared_v4(sm.act + row * 128 + ((chunk16 ^ (row & 7)) << 4),
+                                     pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                                     pack_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv),
+                                     pack_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv),
+                                     pack_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv));
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(sm.misc(2));
+            }
+            for (int ch = 0; ch < dn_chunks; ++ch, ++dn_it) {
+                ok = mbar_wait(sm.misc(4), static_cast<uint32_t>(dn_it & 1), status, ST_TIMEOUT_TMEM_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                float v[64];
+                ld32(v, tmem_addr(tmem_base + DN_ACC, lane_base, cg * 64));
+                ld32(v + 32, tmem_addr(tmem_base + DN_ACC, lane_base, cg * 64 + 32));
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(sm.misc(5));
+                if (valid) {
+                    float *d = dst + ch * 128;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d + j * 4),
+                                     "f"(wgt * v[j * 4 + 0]), "f"(wgt * v[j * 4 + 1]), "f"(wgt * v[j * 4 + 2]),
+                                     "f"(wgt * v[j * 4 + 3])
+                                     : "memory");
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// out[i] += bf16(acc32[i])
+__global__ void __launch_bounds__(256)
+finalize_acc32_mxfp8_kernel(const float *__restrict__ acc32, __nv_bfloat16 *__restrict__ out, long long n8,
+                            int use_pdl) {
+    if (use_pdl) pdl_wait_primary();
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(acc32) + 2 * i);
+        const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(acc32) + 2 * i + 1);
+        uint4 o = reinterpret_cast<const uint4 *>(out)[i];
+        const __nv_bfloat162 *ob = reinterpret_cast<const __nv_bfloat162 *>(&o);
+        uint4 r;
+        r.x = pack_bf16x2(__low2float(ob[0]) + a0.x, __high2float(ob[0]) + a0.y);
+        r.y = pack_bf16x2(__low2float(ob[1]) + a0.z, __high2float(ob[1]) + a0.w);
+        r.z = pack_bf16x2(__low2float(ob[2]) + a1.x, __high2float(ob[2]) + a1.y);
+        r.w = pack_bf16x2(__low2float(ob[3]) + a1.z, __high2float(ob[3]) + a1.w);
+        reinterpret_cast<uint4 *>(out)[i] = r;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 struct Problem {
@@ -515,14 +764,19 @@ int set_smem(Kernel k, size_t bytes) {
 }
 
 struct Workspace {
-    size_t act_q, act_sf, x_sorted, xsf, total;
+    size_t act_q, act_sf, acc32, x_sorted, xsf, total;
 };
 Workspace plan_workspace(int M, int K, int N, int sorted_num, int split) {
     Workspace w{};
-    (void)M;
     const size_t H = N / 2, blocks = sorted_num / BM;
-    if (!split) return w;
     auto up = [](size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); };
+    if (!split) {   // fp32 accumulation buffer [M, K] instead of the activation workspace
+        w.acc32 = 0;
+        w.x_sorted = up(static_cast<size_t>(M) * K * sizeof(float));
+        w.xsf = up(w.x_sorted + static_cast<size_t>(sorted_num) * K);
+        w.total = up(w.xsf + blocks * (K / 128) * SF_TILE);
+        return w;
+    }
     w.act_q = 0;
     w.act_sf = up(w.act_q + static_cast<size_t>(sorted_num) * H);
     w.x_sorted = up(w.act_sf + blocks * (H / 128) * SF_TILE);
@@ -538,7 +792,6 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         if (p.split) PMOE_CUDA_OK(cudaMemsetAsync(p.out, 0, static_cast<size_t>(p.M) * p.K * 2, stream));
         return PMOE_OK;
     }
-    PMOE_REQUIRE(p.split, PMOE_ERR_UNSUPPORTED, "fused_moe_mxfp8: split=False is not available in this build");
     Args a{};
     a.sorted_ids = p.sorted_ids;
     a.expert_ids = p.expert_ids;
@@ -559,11 +812,12 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
 
     PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_mxfp8: workspace must be 1024-byte aligned");
-    const Workspace w = plan_workspace(p.M, p.K, p.N, p.sorted_num, 1);
+    const Workspace w = plan_workspace(p.M, p.K, p.N, p.sorted_num, p.split);
     uint8_t *base = static_cast<uint8_t *>(workspace);
     uint8_t *act_q = base + w.act_q, *act_sf = base + w.act_sf, *x_sorted = base + w.x_sorted, *xsf = base + w.xsf;
     a.act_sf = act_sf;
     a.xsf_tiles = xsf;
+    a.acc32 = reinterpret_cast<float *>(base + w.acc32);
 
     CUtensorMap map_x, map_w1, map_act, map_w2;
     if (int rc = make_tmap_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x_sorted, p.sorted_num, p.K, 128, BKB,
@@ -583,6 +837,43 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         gather_rows_mxfp8_kernel<<<std::min(4 * sms, (p.sorted_num + 7) / 8), 256, 0, stream>>>(
             static_cast<const uint8_t *>(p.x), static_cast<const uint8_t *>(p.x_scales), x_sorted, xsf, a);
         PMOE_CUDA_OK(cudaGetLastError());
+    }
+    if (!p.split) {
+        // memset(acc32) -> [gather] -> fused kernel -> out += bf16(acc32)
+        CUtensorMap map_w2f;
+        if (int rc = make_tmap_2d(&map_w2f, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.w2, static_cast<uint64_t>(p.E) * p.K,
+                                  H, 128, BKB, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
+            return rc;
+        const size_t elems = static_cast<size_t>(p.M) * p.K;
+        PMOE_CUDA_OK(cudaMemsetAsync(a.acc32, 0, elems * sizeof(float), stream));
+        const int use_pdl = pdl_enabled() ? 1 : 0;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        {
+            Args fa = a;
+            fa.use_pdl = use_pdl;
+            const size_t smem = smem_bytes(fa.stages, true);
+            if (int rc = set_smem(moe_fused_mxfp8_kernel, smem)) return rc;
+            const int tiles = max_blocks * (H / 128);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(std::min(tiles, sms));
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cfg.attrs = attr;
+            cfg.numAttrs = use_pdl ? 1 : 0;
+            PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_fused_mxfp8_kernel, map_x, map_w1, map_w2f, fa));
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>(4 * sms, (elems / 8 + 255) / 256)));
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_pdl ? 1 : 0;
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, finalize_acc32_mxfp8_kernel, static_cast<const float *>(a.acc32), a.out,
+                                        static_cast<long long>(elems / 8), use_pdl));
+        return PMOE_OK;
     }
     if (phases & 2) {
         Args up = a;
