@@ -590,9 +590,11 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
+                    if (a.pregathered) tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BK, c.m_blk * BM);
                 }
                 __syncwarp();
-                tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
+                if (!a.pregathered)
+                    tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
                 ++issued;
                 if (++s == a.stages) {
                     s = 0;
@@ -809,6 +811,19 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         a.acc32 = static_cast<float *>(workspace);
         const size_t elems = static_cast<size_t>(p.M) * p.K;
         PMOE_CUDA_OK(cudaMemsetAsync(a.acc32, 0, elems * sizeof(float), stream));
+        if (pregather_enabled()) {   // x_sorted follows the accumulation buffer (1024-byte aligned)
+            const size_t off = (elems * sizeof(float) + 1023) & ~static_cast<size_t>(1023);
+            __nv_bfloat16 *x_sorted = reinterpret_cast<__nv_bfloat16 *>(static_cast<uint8_t *>(workspace) + off);
+            PMOE_REQUIRE((reinterpret_cast<uintptr_t>(x_sorted) & 1023) == 0, PMOE_ERR_BAD_ARG,
+                         "fused_moe_bf16: workspace must be 1024-byte aligned");
+            gather_rows_kernel<<<std::min(4 * sms, (p.sorted_num + 7) / 8), 256, 0, stream>>>(
+                static_cast<const __nv_bfloat16 *>(p.x), x_sorted, a);
+            PMOE_CUDA_OK(cudaGetLastError());
+            if (int rc = make_tmap_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_sorted, p.sorted_num, p.K, 128,
+                                      BK, CU_TENSOR_MAP_SWIZZLE_128B, "x_sorted"))
+                return rc;
+            a.pregathered = 1;
+        }
         const size_t smem = smem_bytes(a.stages, true);
         if (int rc = set_smem(moe_fused_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
@@ -898,7 +913,11 @@ int status_fetch_bf16(int *value, bool reset) {
 
 extern "C" size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int sorted_num, int split) {
     if (sorted_num <= 0 || N <= 0) return 0;
-    if (!split) return static_cast<size_t>(M) * K * sizeof(float);
+    if (!split) {
+        size_t bytes = (static_cast<size_t>(M) * K * sizeof(float) + 1023) & ~static_cast<size_t>(1023);
+        if (pmoe::pregather_enabled()) bytes += static_cast<size_t>(sorted_num) * K * 2;
+        return bytes;
+    }
     size_t bytes = static_cast<size_t>(sorted_num) * (N / 2) * 2;
     if (pmoe::pregather_enabled()) bytes += static_cast<size_t>(sorted_num) * K * 2;
     return bytes;
@@ -932,11 +951,12 @@ extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2,
               top_k, M, K, N, num_experts, sorted_num, block_n, warp_n, stages, bpc, split ? 1 : 0};
     if (int rc = validate(p, block_m, cpc)) return rc;
     const size_t need = pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_num, split);
-    void *ws = nullptr;
+    void *raw = nullptr;
     if (need)
-        if (int rc = scratch_alloc(&ws, need, stream)) return rc;
-    const int rc = run(p, ws, stream);
-    if (ws)
-        if (int rc2 = scratch_free(ws, stream)) return rc2;
+        if (int rc = scratch_alloc(&raw, need + 1024, stream)) return rc;
+    void *ws = reinterpret_cast<void *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int rc = run(p, raw ? ws : nullptr, stream);
+    if (raw)
+        if (int rc2 = scratch_free(raw, stream)) return rc2;
     return rc;
 }

@@ -951,11 +951,12 @@ extern "C" int pmoe_fused_moe_mxfp8(const void *x, const void *x_scales, const v
               topk_weights, top_k, M, K, N, num_experts, sorted_num, block_n, warp_n, stages, bpc, split ? 1 : 0};
     if (int rc = validate(p, block_m)) return rc;
     const size_t need = pmoe_fused_moe_mxfp8_workspace_bytes(M, K, N, sorted_num, split);
-    void *ws = nullptr;
+    void *raw = nullptr;
     if (need)
-        if (int rc = scratch_alloc(&ws, need, stream)) return rc;
-    const int rc = run(p, ws, stream);
-    if (ws)
-        if (int rc2 = scratch_free(ws, stream)) return rc2;
+        if (int rc = scratch_alloc(&raw, need + 1024, stream)) return rc;
+    void *ws = reinterpret_cast<void *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int rc = run(p, raw ? ws : nullptr, stream);
+    if (raw)
+        if (int rc2 = scratch_free(raw, stream)) return rc2;
     return rc;
 }

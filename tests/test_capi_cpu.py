@@ -63,7 +63,7 @@ def test_fused_bf16_argument_errors(lib):
     assert _bf16_call(lib, block_m=64) == 2 and b"block_m=128" in lib.pmoe_last_error()
     assert _bf16_call(lib, cpc=2) == 2
     assert _bf16_call(lib, M=0) == 1
-    assert lib.pmoe_fused_moe_bf16_workspace_bytes(8, 256, 512, 512, 0) == 8 * 256 * 4   # fp32 split-K buffer
+    assert lib.pmoe_fused_moe_bf16_workspace_bytes(8, 256, 512, 512, 0) >= 8 * 256 * 4   # fp32 split-K buffer
     assert lib.pmoe_fused_moe_bf16_workspace_bytes(8, 256, 512, 512, 1) >= 512 * 256 * 2
 
 
