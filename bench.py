@@ -54,7 +54,9 @@ def parse_args():
     ap.add_argument("--split", type=int, default=1)
     ap.add_argument("--stages", type=int, default=4)
     ap.add_argument("--bpc", type=int, default=1)
-    ap.add_argument("--parallel", default="replica", choices=["replica", "ep"])
+    ap.add_argument("--parallel", default="auto", choices=["auto", "replica", "ep"],
+                    help="N > 1: 'ep' shards the experts over the ranks (NCCL all-to-all dispatch/combine, the "
+                         "default when the expert count divides), 'replica' runs N independent copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -169,6 +171,28 @@ def make_inputs(cfg, seed, device):
     return x, w1, w2, ids, wts
 
 
+def quantize_mx_device(t, block=32):
+    """The OCP-MX quantiser of the reference's tests (test/test_mxfp8.py:21-38) on whatever device `t` is on."""
+    import torch
+    k = t.shape[-1]
+    g = t.float().reshape(*t.shape[:-1], k // block, block)
+    bits = g.abs().amax(-1).contiguous().view(torch.int32)
+    e = (((bits >> 23) & 0xFF) - 8).clamp(0, 254)
+    inv = torch.exp2((127 - e).float())
+    q = (g * inv.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q.reshape(*t.shape[:-1], k).contiguous(), e.to(torch.uint8).view(torch.float8_e8m0fnu)
+
+
+def pack_scales(scales):
+    """Blocked scale layout (prime_moe/__init__.py:106-115); plain torch so that both arms can use it."""
+    import torch
+    u = scales.view(torch.uint8)
+    lead = u.shape[:-2]
+    mn, kb = u.shape[-2:]
+    t = u.reshape(-1, mn // 128, 4, 32, kb // 4, 4).permute(0, 1, 4, 3, 2, 5).contiguous()
+    return t.reshape(*lead, -1).view(torch.float8_e8m0fnu)
+
+
 def time_cpu_oracle(x, w1, w2, ids, wts, sample_tokens):
     """The reference's PyTorch MoE (restated in oracle/) on the host cores, on the first
     `sample_tokens` tokens of the batch. Returns (TFLOP/s, seconds, threads)."""
@@ -187,6 +211,45 @@ def time_cpu_oracle(x, w1, w2, ids, wts, sample_tokens):
     return flops / dt / 1e12, dt, torch.get_num_threads()
 
 
+def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tflops):
+    """Gate/up kernel of the mxfp8 split pipeline timed alone (profiling hook). No fp8 peak was measured on
+    this pool: the denominator is 2 x the measured bf16 burst peak, stated as an assumption."""
+    import torch
+    T, K, E, N, k, _ = cfg
+    xq, xs, w1q, w1s, w2q, w2s = tensors
+    lib = capi.lib()
+    s, e, n = ops.moe_align(ids, E, 128, 1)
+    nbytes = lib.pmoe_fused_moe_mxfp8_workspace_bytes(T, K, N, s.numel(), 1)
+    ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=out.device)
+    off = (-ws.data_ptr()) % 1024
+    ws = ws[off:off + nbytes]
+    call = lambda: capi.fused_moe_mxfp8(xq, xs, w1q, w1s, w2q, w2s, s, e, n, wts, out, k, 128, 64, 4, args.stages, 1, True,
+                                        workspace=ws)
+    call()
+    per_kernel = {}
+    for name, mask in (("gather_rows_mxfp8", 1), ("moe_up_mxfp8", 2), ("moe_down_mxfp8", 4)):
+        lib.pmoe_debug_set_phase_mask(mask)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(20):
+            call()
+        b.record()
+        torch.cuda.synchronize()
+        per_kernel[name] = a.elapsed_time(b) / 20
+    lib.pmoe_debug_set_phase_mask(7)
+    call()
+    torch.cuda.synchronize()
+    achieved = 2.0 * T * k * K * N / (per_kernel["moe_up_mxfp8"] * 1e-3) / 1e12
+    peak = 2.0 * peaks["bf16_tflops"]
+    assert capi.device_status() == 0
+    return {"kernel": "moe_up_mxfp8_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak, "peak_source": "ASSUMED 2 x measured bf16 burst peak (no fp8 peak measured)",
+            "traffic": None, "kernel_ms": per_kernel, "whole_op_frac": whole_tflops / peak}
+
+
 # ------------------------------------------------------------------------------------------------
 # arms
 # ------------------------------------------------------------------------------------------------
@@ -201,15 +264,50 @@ def run_gpu_arm(args, impl):
     if args.tokens:
         cfg[0] = args.tokens
     T, K, E, N, k, routing = cfg
-    if args.dtype != "bf16":
-        raise SystemExit("mxfp8 benchmarking: use --dtype bf16 until the mxfp8 arm is wired in")
+    mx = args.dtype == "mxfp8"
     x, w1, w2, ids_cpu, wts_cpu = make_inputs(cfg, 1234 + rank, device)
     ids, wts = ids_cpu.to(device), wts_cpu.to(device)
     out = torch.zeros(T, K, dtype=torch.bfloat16, device=device)
     flops = 3.0 * T * k * K * N
-    pad_note = ""
+    if mx:
+        # OCP-MX operands computed from the bf16 tensors: e4m3 values + e8m0 scale per 32 K-elements
+        xq, xs = quantize_mx_device(x)
+        w1q, w1s = quantize_mx_device(w1)
+        w2q, w2s = quantize_mx_device(w2)
+        w1s, w2s = pack_scales(w1s), pack_scales(w2s)
 
-    if impl == "ours":
+    xin = (xq, xs) if mx else x      # what a step consumes as its activation input
+    ep_mode = impl == "ours" and args.parallel == "ep"
+    if ep_mode:
+        # expert parallel: every rank generated the SAME full weights (seed 99), keeps its E/world experts,
+        # and runs its own T tokens; dispatch / combine are NCCL all-to-alls (prime_flash_moe_b200/ep.py)
+        sys.path.insert(0, str(ROOT))
+        import prime_flash_moe_b200  # noqa: F401
+        from prime_flash_moe_b200 import capi, ep
+        gw = torch.Generator(device=device).manual_seed(99)
+        w1 = torch.randn(E, N, K, device=device, generator=gw, dtype=torch.bfloat16) * K ** -0.5
+        w2 = torch.randn(E, K, N // 2, device=device, generator=gw, dtype=torch.bfloat16) * (N // 2) ** -0.5
+        if mx:
+            w1q, w1s = quantize_mx_device(ep.shard_experts(w1, rank, world))
+            w2q, w2s = quantize_mx_device(ep.shard_experts(w2, rank, world))
+            experts = ep.LocalExperts(w1q, w2q, pack_scales(w1s), pack_scales(w2s), stages=args.stages)
+        else:
+            experts = ep.LocalExperts(ep.shard_experts(w1, rank, world), ep.shard_experts(w2, rank, world),
+                                      stages=args.stages)
+        del w1, w2
+        torch.cuda.empty_cache()
+        layer = ep.ExpertParallelMoE(E, experts)
+        launches_per_step = None
+        ep_rows = []
+
+        def step(x_, ids_, wts_, out_):
+            if mx:
+                out_.copy_(layer(x_[0], ids_, wts_, x_[1]))
+            else:
+                out_.copy_(layer(x_, ids_, wts_))
+            ep_rows.append(layer.last_recv_rows)
+        knobs = {"stages": args.stages, "split": True, "experts_per_rank": E // world}
+    elif impl == "ours":
         sys.path.insert(0, str(ROOT))
         import prime_flash_moe_b200  # noqa: F401
         from prime_flash_moe_b200 import capi
@@ -221,7 +319,11 @@ def run_gpu_arm(args, impl):
             s, e, n = ops.moe_align(ids_, E, 128, bpc)
             if not split:
                 out_.zero_()
-            ops.fused_moe_bf16(x_, w1, w2, s, e, n, wts_, out_, k, 128, bn, wn, stages, bpc, 1, split)
+            if mx:
+                ops.fused_moe_mxfp8(x_[0], x_[1], w1q, w1s, w2q, w2s, s, e, n, wts_, out_, k, 128, bn, wn, stages, bpc,
+                                    split)
+            else:
+                ops.fused_moe_bf16(x_, w1, w2, s, e, n, wts_, out_, k, 128, bn, wn, stages, bpc, 1, split)
         knobs = {"block_n": bn, "warp_n": wn, "stages": stages, "split": split, "bpc": bpc}
     else:
         ref_dir = ROOT / "baseline" / "_ref"
@@ -241,15 +343,19 @@ def run_gpu_arm(args, impl):
                         s, e, n = ops.moe_align(ids_, E, 128, 1)
                         if not split:
                             out_.zero_()
-                        ref_pkg.fused_moe_bf16(x_, w1, w2, s, e, n, wts_, out_, k, 128, bn, wn, stages, 1, 1, split)
+                        if mx:
+                            ref_pkg.fused_moe_mxfp8(x_[0], x_[1], w1q, w1s, w2q, w2s, s, e, n, wts_, out_, k, 128, bn,
+                                                    wn, stages, 1, split)
+                        else:
+                            ref_pkg.fused_moe_bf16(x_, w1, w2, s, e, n, wts_, out_, k, 128, bn, wn, stages, 1, 1, split)
                     try:
                         for _ in range(2):
-                            cand(x, ids, wts, out)
+                            cand(xin, ids, wts, out)
                         torch.cuda.synchronize()
                         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                         a.record()
                         for _ in range(3):
-                            cand(x, ids, wts, out)
+                            cand(xin, ids, wts, out)
                         b.record()
                         torch.cuda.synchronize()
                         ms = a.elapsed_time(b) / 3
@@ -265,13 +371,13 @@ def run_gpu_arm(args, impl):
     ref_world = 1 if impl == "reference" else world
     # ---- device-resident timing ----
     for _ in range(max(args.warmup, 3)):
-        step(x, ids, wts, out)
+        step(xin, ids, wts, out)
     barrier_sync(ref_world)
     with ClockSampler(local) as clocks:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(args.steps):
-            step(x, ids, wts, out)
+            step(xin, ids, wts, out)
         b.record()
         barrier_sync(ref_world)
         ms_total = max_over_ranks(a.elapsed_time(b), ref_world, device)
@@ -279,16 +385,18 @@ def run_gpu_arm(args, impl):
     value = ref_world * flops / (ms_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers, copies inside the timed region ----
-    hx = x.cpu().pin_memory()
+    hx = tuple(t.cpu().pin_memory() for t in xin) if mx else (x.cpu().pin_memory(),)
     hids, hwts = ids_cpu.pin_memory(), wts_cpu.pin_memory()
     hout = torch.empty(T, K, dtype=torch.bfloat16).pin_memory()
-    dx, dids, dwts = torch.empty_like(x), torch.empty_like(ids), torch.empty_like(wts)
+    dx = tuple(torch.empty_like(t, device=device) for t in hx)
+    dids, dwts = torch.empty_like(ids), torch.empty_like(wts)
 
     def e2e_step():
-        dx.copy_(hx, non_blocking=True)
+        for d_, h_ in zip(dx, hx):
+            d_.copy_(h_, non_blocking=True)
         dids.copy_(hids, non_blocking=True)
         dwts.copy_(hwts, non_blocking=True)
-        step(dx, dids, dwts, out)
+        step(dx if mx else dx[0], dids, dwts, out)
         hout.copy_(out, non_blocking=True)
     e2e_steps = max(5, min(args.steps, 50))
     for _ in range(3):
@@ -301,14 +409,16 @@ def run_gpu_arm(args, impl):
     b.record()
     barrier_sync(ref_world)
     e2e_ms = max_over_ranks(a.elapsed_time(b), ref_world, device) / e2e_steps
-    h2d = hx.numel() * 2 + hids.numel() * 4 + hwts.numel() * 4
+    h2d = sum(t.numel() * t.element_size() for t in hx) + hids.numel() * 4 + hwts.numel() * 4
     d2h = hout.numel() * 2
     e2e = {"value": ref_world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
     peaks = measured_peaks()
     roofline = None
-    if impl == "ours" and args.split:
+    if impl == "ours" and args.split and mx and not ep_mode:
+        roofline = roofline_mxfp8(args, capi, ops, (xq, xs, w1q, w1s, w2q, w2s), ids, wts, out, cfg, peaks, value / world)
+    if impl == "ours" and args.split and not mx and not ep_mode:
         # dominant kernel = the gate/up GEMM (2/3 of the FLOPs); timed alone through the profiling hook
         lib = capi.lib()
         step(x, ids, wts, out)                      # fills the workspace-independent state
@@ -348,7 +458,7 @@ def run_gpu_arm(args, impl):
         assert capi.device_status() == 0, "a kernel recorded an error status"
 
     cpu_baseline = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and not args.no_cpu_baseline and not ep_mode and ref_world == 1:
         sample = 256 if T >= 256 else T
         tf, secs, threads = time_cpu_oracle(x, w1, w2, ids_cpu, wts_cpu, sample)
         cpu_baseline = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
@@ -359,16 +469,19 @@ def run_gpu_arm(args, impl):
         line = {
             "metric": "moe_ffn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": ref_world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "tokens_per_s": ref_world * T / (ms_step * 1e-3),
+            "vs_baseline": None, "dtype": "mxfp8 (e4m3 x e8m0/32, fp32 accumulate)" if mx else "bf16",
+            "data": "synthetic", "tokens_per_s": ref_world * T / (ms_step * 1e-3),
             "config": {"workload": f"{args.config}: T={T} K={K} E={E} N={N} top_k={k} routing={routing} "
-                                   f"(per GPU), moe_align + fused_moe_bf16",
+                                   f"(per GPU), moe_align + fused_moe_{args.dtype}",
                        "knobs": knobs, "parallelism": f"{args.parallel}{ref_world}",
                        "l2": "weights (>= 1 GB) exceed the 126 MB L2, no flush between steps" if
                              E * N * K * 3 > 256e6 else "inputs smaller than L2; steps are back to back"},
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": (launches_per_step or 0) * args.steps,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
+        if ep_mode:
+            line["config"]["ep"] = {"rows_computed_by_rank0_last_step": ep_rows[-1] if ep_rows else None,
+                                    "tokens_per_rank": T, "collective": "NCCL all-to-all (dispatch + combine)"}
         if impl == "reference":
             line["impl"] = "reference"
             line["gpu_launches"] = None
@@ -406,6 +519,9 @@ def run_cpu_arm(args):
 
 def main():
     args = parse_args()
+    if args.parallel == "auto":
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        args.parallel = "ep" if world > 1 and CONFIGS[args.config][2] % world == 0 else "replica"
     if args.impl == "cpu":
         run_cpu_arm(args)
     else:
