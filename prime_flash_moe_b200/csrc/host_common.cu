@@ -108,6 +108,15 @@ bool pdl_enabled() {
     return on;
 }
 
+int l2_prefetch_distance() {
+    static const int d = [] {
+        const char *e = getenv("PMOE_L2_AHEAD");
+        const int v = e ? atoi(e) : 0;
+        return v < 0 ? 0 : (v > 64 ? 64 : v);
+    }();
+    return d;
+}
+
 static int g_phase_mask = 7;
 int phase_mask() { return g_phase_mask; }
 

@@ -48,6 +48,9 @@ bool pdl_enabled();
 // (no pre-pass, smaller workspace, but gather4 issue rate then bounds the gate/up kernel).
 bool pregather_enabled();
 
+// PMOE_L2_AHEAD=n: the GEMM producers prefetch weight tiles n k-steps ahead of the ring into L2
+int l2_prefetch_distance();
+
 // which launches of a split pipeline run (pmoe_debug_set_phase_mask): 1 gather, 2 gate/up, 4 down
 int phase_mask();
 

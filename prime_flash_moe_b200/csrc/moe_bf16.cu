@@ -89,6 +89,7 @@ struct Args {
     int epi_warps;   // 4 or 8
     int zero_out;    // up kernel: clear `out` before the first tile
     int use_pdl;     // down kernel: wait for the primary grid before touching its results
+    int l2_ahead;    // producers prefetch weight tiles this many k-steps ahead of the ring into L2 (0 = off)
     int pregathered; // up kernel: A rows come from a row-gathered copy of x (plain 2-D TMA) instead of gather4
 };
 
@@ -301,6 +302,10 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
                     if (a.pregathered) tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BK, c.m_blk * BM);
+                    if (a.l2_ahead && ks + a.l2_ahead < ksteps) {
+                        tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_gate);
+                        tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_up);
+                    }
                 }
                 __syncwarp();
                 if (!a.pregathered)
@@ -449,6 +454,7 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
                     mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
                     tma_load_2d(sm.a(s), &map_act, sm.full(s), ks * BK, c.m_blk * BM);
                     tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BK, w2_row);
+                    if (a.l2_ahead && ks + a.l2_ahead < ksteps) tma_prefetch_l2_2d(&map_w2, (ks + a.l2_ahead) * BK, w2_row);
                     ++issued;
                     if (++s == a.stages) {
                         s = 0;
@@ -591,6 +597,10 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
                     if (a.pregathered) tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BK, c.m_blk * BM);
+                    if (a.l2_ahead && ks + a.l2_ahead < ksteps) {
+                        tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_gate);
+                        tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_up);
+                    }
                 }
                 __syncwarp();
                 if (!a.pregathered)
@@ -727,6 +737,213 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 }
 
 // ---------------------------------------------------------------------------------------------
+// bpc == 2: CTA pairs (cluster of 2) with tcgen05 cta_group::2 MMAs, M = 256 per pair
+//
+// A pair owns two consecutive 128-row blocks (same expert: moe_align pads experts to 256 rows when
+// bpc == 2) x one 256-column tile. Each CTA loads ITS 128 rows of A and ITS half of the B tile (up
+// kernel: CTA 0 the gate rows, CTA 1 the up rows; down kernel: 128 of the 256 w2 rows each), so a CTA
+// pulls 32 KB per k-step for 128x256x64 MACs instead of 48 KB - two thirds of the L2->SM traffic.
+// Plain TMA tile loads only (no multicast). The even CTA issues the MMAs for both; its `full`
+// barriers collect the bytes of both CTAs' loads; ring slots and accumulators are released to both
+// CTAs by multicast tcgen05.commit; both CTAs' epilogue warps arrive on the even CTA's tmem_empty.
+//   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2] (leader) | 4 staged | 5 stage_free (up only)
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2;   // 32 KB per CTA and slot
+constexpr int PAIR_MAX_STAGES = 6;
+constexpr int ST_BAD_PAIR = 8;                                 // the two blocks of a pair differ in expert
+
+struct SmemPair {
+    uint32_t ring, act, bars;
+    __device__ __forceinline__ uint32_t a(int s) const { return ring + s * PAIR_STAGE_BYTES; }
+    __device__ __forceinline__ uint32_t b(int s) const { return ring + s * PAIR_STAGE_BYTES + A_BYTES; }
+    __device__ __forceinline__ uint32_t full(int s) const { return bars + 8 * s; }
+    __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8 * (PAIR_MAX_STAGES + s); }
+    __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * PAIR_MAX_STAGES + i); }
+    __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * PAIR_MAX_STAGES + 12); }
+};
+__device__ __forceinline__ SmemPair carve_pair(const uint8_t *raw, int stages, bool with_act) {
+    SmemPair s;
+    s.ring = (smem_u32(raw) + 1023u) & ~1023u;
+    s.act = s.ring + stages * PAIR_STAGE_BYTES;
+    s.bars = s.act + (with_act ? ACT_TILE_BYTES : 0);
+    return s;
+}
+size_t smem_bytes_pair(int stages, bool with_act) {
+    return 1024 + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + (with_act ? ACT_TILE_BYTES : 0) + BAR_BYTES;
+}
+
+template <bool kUp>
+__global__ void __launch_bounds__(MAX_THREADS, 1)
+moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_act, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const SmemPair sm = carve_pair(smem_raw, a.stages, kUp);
+    int *status = &g_status_bf16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int epi_threads = a.epi_warps * 32;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (kUp) pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), 1);
+        mbar_init(sm.misc(2), 2 * epi_threads);
+        mbar_init(sm.misc(3), 2 * epi_threads);
+        mbar_init(sm.misc(4), epi_threads);
+        mbar_init(sm.misc(5), 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        if (kUp) tma_prefetch_desc(&map_act);
+    }
+    if (warp == 1) tmem_alloc_pair(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // both CTAs' barriers are initialised and both halves of TMEM allocated
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (!kUp && a.use_pdl) pdl_wait_primary();
+
+    const int m_pairs = num_row_blocks(a) / 2;
+    const int n_tiles = kUp ? a.H / 128 : (a.K + 255) / 256;
+    const int num_tiles = m_pairs * n_tiles;
+    const int ksteps = (kUp ? a.K : a.H) / BK;
+    const int first = blockIdx.x >> 1, step = gridDim.x >> 1;   // this pair's tile sequence
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = first; t < num_tiles && ok; t += step) {
+                const Coord c = tile_coord(t, m_pairs, n_tiles);
+                const int blk = 2 * c.m_blk + static_cast<int>(rank);
+                const int e = a.expert_ids[2 * c.m_blk];
+                if (leader && a.expert_ids[2 * c.m_blk + 1] != e) atomicCAS(status, 0, ST_BAD_PAIR);
+                int b_row;
+                if (kUp) b_row = e * a.N + c.n_tile * 128 + (leader ? 0 : a.H);
+                else b_row = e * a.K + c.n_tile * 256 + static_cast<int>(rank) * 128;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait_cluster(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    const uint32_t full_leader = mapa_shared(sm.full(s), 0);
+                    if (leader) mbar_arrive_expect_tx(sm.full(s), 2 * PAIR_STAGE_BYTES);
+                    tma_load_2d_pair(sm.a(s), &map_a, full_leader, ks * BK, blk * BM);
+                    tma_load_2d_pair(sm.b(s), &map_b, full_leader, ks * BK, b_row);
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = idesc_bf16_f32(256, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = first; t < num_tiles && ok; t += step, ++it) {
+                const int buf = it & 1;
+                ok = mbar_wait_cluster(sm.misc(2 + buf), ((it >> 1) & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * 256;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait_cluster(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16_pair(d, smem_desc_sw128(sm.a(s) + k * 32), smem_desc_sw128(sm.b(s) + k * 32), idesc,
+                                      (ks | k) != 0);
+                    umma_commit_pair(sm.empty(s), 3);
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit_pair(sm.misc(buf), 3);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const int et = threadIdx.x - 64;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int ncg = a.epi_warps / 4;
+        const int cg = ew / 4;
+        if (kUp && a.zero_out) {
+            int4 *o4 = reinterpret_cast<int4 *>(a.out);
+            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const int4 z = make_int4(0, 0, 0, 0);
+            for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
+                 i += static_cast<long long>(gridDim.x) * epi_threads)
+                o4[i] = z;
+        }
+        int it = 0;
+        for (int t = first; t < num_tiles; t += step, ++it) {
+            const Coord c = tile_coord(t, m_pairs, n_tiles);
+            const int blk = 2 * c.m_blk + static_cast<int>(rank);
+            const int buf = it & 1;
+            const uint32_t empty_leader = mapa_shared(sm.misc(2 + buf), 0);
+            const uint32_t acc = tmem_base + buf * 256;
+            if (kUp) {
+                if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+                if (!mbar_wait(sm.misc(5), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;
+                tc_fence_after();
+                for (int ch = cg * (4 / ncg); ch < (cg + 1) * (4 / ncg); ++ch)
+                    swiglu_chunk_to_smem(acc, lane_base, row, ch, sm.act);
+                tc_fence_before();
+                mbar_arrive_cluster(empty_leader);
+                fence_proxy_async_smem();
+                mbar_arrive(sm.misc(4));
+                if (et == 0) {
+                    if (!mbar_wait(sm.misc(4), it & 1, status, ST_TIMEOUT_ACT)) break;
+                    tma_store_2d(&map_act, sm.act, c.n_tile * 128, blk * BM);
+                    tma_store_2d(&map_act, sm.act + ACT_TILE_BYTES / 2, c.n_tile * 128 + 64, blk * BM);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                    mbar_arrive(sm.misc(5));
+                }
+            } else {
+                const int pair = a.sorted_ids[blk * BM + row];
+                const int tok = pair >= 0 ? pair / a.top_k : 0;
+                const bool valid = pair >= 0 && tok < a.M;
+                const float wgt = valid ? a.topk_weights[pair] : 0.f;
+                const int col0 = c.n_tile * 256;
+                __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + col0;
+                const int cols = min(256, a.K - col0);
+                if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+                tc_fence_after();
+                for (int ch = cg * (8 / ncg); ch < (cg + 1) * (8 / ncg); ++ch)
+                    reduce_chunk_to_out(tmem_addr(acc, lane_base, ch * 32), wgt, dst + ch * 32,
+                                        valid && ch * 32 < cols);
+                tc_fence_before();
+                mbar_arrive_cluster(empty_leader);
+            }
+        }
+        if (kUp && et == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // nobody frees TMEM or exits while the peer may still use this CTA's memory
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 struct Problem {
@@ -747,7 +964,11 @@ int validate(const Problem &p, int block_m, int cpc) {
     PMOE_REQUIRE((p.block_n == 64 && p.warp_n == 4) || (p.block_n == 32 && p.warp_n == 8), PMOE_ERR_UNSUPPORTED,
                  "(block_n, warp_n) must be (64, 4) or (32, 8)");
     PMOE_REQUIRE(p.stages > 0 && p.stages < 6, PMOE_ERR_UNSUPPORTED, "stages must be in 1..5");
-    PMOE_REQUIRE(p.bpc == 1 && cpc == 1, PMOE_ERR_UNSUPPORTED, "bpc=cpc=1 is the only supported configuration");
+    PMOE_REQUIRE((p.bpc == 1 || p.bpc == 2) && cpc == 1, PMOE_ERR_UNSUPPORTED,
+                 "bpc must be 1 or 2 and cpc must be 1");
+    PMOE_REQUIRE(p.bpc == 1 || p.split, PMOE_ERR_UNSUPPORTED, "bpc=2 (two-CTA MMA) requires split=True");
+    PMOE_REQUIRE(p.bpc == 1 || p.sorted_num % 256 == 0, PMOE_ERR_BAD_ARG,
+                 "bpc=2 requires routing tables built by moe_align with bpc=2 (rows padded to 256)");
     PMOE_REQUIRE(!p.split || p.stages <= 4, PMOE_ERR_UNSUPPORTED, "split=True requires stages<=4, got stages=%d",
                  p.stages);
     PMOE_REQUIRE(block_m == 128, PMOE_ERR_UNSUPPORTED, "Blackwell tcgen05 fused MoE requires block_m=128.");
@@ -789,6 +1010,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     a.sorted_num = p.sorted_num;
     a.stages = std::min(p.stages, MAX_STAGES);
     a.epi_warps = p.warp_n;
+    a.l2_ahead = l2_prefetch_distance();
     const int threads = 64 + 32 * a.epi_warps;
     const int sms = sm_count();
 
@@ -867,6 +1089,56 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2, static_cast<uint64_t>(p.E) * p.K,
                               H, 256, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
         return rc;
+    if (p.bpc == 2) {
+        // two-CTA pipeline: always fed from the row-gathered copy; B tiles are loaded as 128-row halves
+        PMOE_REQUIRE(pregather, PMOE_ERR_UNSUPPORTED, "bpc=2 needs the row-gather pre-pass (unset PMOE_PREGATHER=0)");
+        CUtensorMap map_w2h;
+        if (int rc = make_tmap_2d(&map_w2h, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2,
+                                  static_cast<uint64_t>(p.E) * p.K, H, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
+            return rc;
+        Args pa = a;
+        pa.stages = std::min(PAIR_MAX_STAGES, (a.stages * 3 + 1) / 2);   // same ring bytes as the 1-CTA kernels
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        auto launch_pair = [&](auto kernel, const CUtensorMap &ma, const CUtensorMap &mb, const Args &args, int tiles,
+                               bool with_act, int nattr) -> int {
+            const size_t smem = smem_bytes_pair(args.stages, with_act);
+            if (int rc = set_smem(kernel, smem)) return rc;
+            PMOE_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
+            cudaLaunchConfig_t cfg = {};
+            cfg.blockDim = dim3(threads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cfg.attrs = attr;
+            cfg.numAttrs = nattr;
+            cfg.gridDim = dim3(2);
+            int max_clusters = 0;
+            PMOE_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg));
+            if (max_clusters < 1) return set_error(PMOE_ERR_CUDA, "no CTA pair of the bpc=2 kernel fits on this device");
+            cfg.gridDim = dim3(2 * std::min(tiles, max_clusters));
+            PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, map_act, args));
+            return PMOE_OK;
+        };
+        if (phases & 2) {
+            Args up = pa;
+            up.zero_out = 1;
+            if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128), true, 1))
+                return rc;
+        }
+        if (phases & 4) {
+            Args dn = pa;
+            dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
+            if (int rc = launch_pair(moe_pair_bf16_kernel<false>, map_act, map_w2h, dn,
+                                     (max_blocks / 2) * ((p.K + 255) / 256), false, dn.use_pdl ? 2 : 1))
+                return rc;
+        }
+        return PMOE_OK;
+    }
     if (phases & 2) {
         Args up = a;
         up.zero_out = 1;

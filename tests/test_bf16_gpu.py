@@ -61,6 +61,21 @@ def test_knobs(split, bn, wn, stages):
     assert O.max_rel_to_peak(out, ref) <= TOL
 
 
+@pytest.mark.parametrize("bn,wn,stages", [(64, 4, 1), (64, 4, 4), (32, 8, 3)])
+@pytest.mark.parametrize("T,K,E,N,k", [(8, 128, 1, 256, 1), (300, 512, 4, 512, 2), (256, 4096, 8, 512, 4),
+                                        (1000, 1024, 16, 768, 8)])
+def test_two_cta_pipeline(T, K, E, N, k, bn, wn, stages):
+    """bpc = 2: CTA pairs with cta_group::2 MMAs on routing tables padded to 256 rows per expert."""
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=T + stages)
+    ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
+    out = run_mine(x, w1, w2, ids, wts, True, stages=stages, bn=bn, wn=wn, bpc=2)
+    assert torch.isfinite(out.float()).all()
+    assert O.max_rel_to_peak(out, ref) <= TOL
+    # same arithmetic as the one-CTA pipeline: only the order of the bf16 reductions into `out` differs
+    one = run_mine(x, w1, w2, ids, wts, True, stages=stages, bn=bn, wn=wn, bpc=1)
+    assert O.max_rel_to_peak(out, one) <= 1e-2
+
+
 def test_golden_vectors(golden):
     """Outputs of the reference's moe_naive_from_topk (test/test.py:13-48) stored in tests/golden."""
     for case in golden["moe_bf16"]:
@@ -131,6 +146,10 @@ def test_argument_checks():
     bad(12, 6)            # stages
     bad(12, 5)            # stages 5 with split=True
     bad(14, 2)            # cpc
+    bad(13, 3)            # bpc must be 1 or 2
+    b2 = list(a); b2[13] = 2; b2[15] = False
+    with pytest.raises(RuntimeError):
+        P.fused_moe_bf16(*b2)          # bpc=2 needs split=True
     bad(0, x.to(DEV).float())          # dtype
     bad(0, x.to(DEV)[:, ::2])          # contiguity / K mismatch
     bad(6, wts.to(DEV).double())       # topk_weights dtype

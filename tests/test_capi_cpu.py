@@ -62,6 +62,9 @@ def test_fused_bf16_argument_errors(lib):
     assert _bf16_call(lib, stages=5, split=1) == 2 and b"stages<=4" in lib.pmoe_last_error()
     assert _bf16_call(lib, block_m=64) == 2 and b"block_m=128" in lib.pmoe_last_error()
     assert _bf16_call(lib, cpc=2) == 2
+    assert _bf16_call(lib, bpc=3) == 2
+    assert _bf16_call(lib, bpc=2, split=0) == 2 and b"split=True" in lib.pmoe_last_error()
+    assert _bf16_call(lib, bpc=2, split=1, sorted_num=384) == 1     # tables must be padded to 256 rows
     assert _bf16_call(lib, M=0) == 1
     assert lib.pmoe_fused_moe_bf16_workspace_bytes(8, 256, 512, 512, 0) >= 8 * 256 * 4   # fp32 split-K buffer
     assert lib.pmoe_fused_moe_bf16_workspace_bytes(8, 256, 512, 512, 1) >= 512 * 256 * 2
