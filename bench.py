@@ -53,7 +53,7 @@ def parse_args():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "mxfp8"])
     ap.add_argument("--split", type=int, default=1)
     ap.add_argument("--stages", type=int, default=4)
-    ap.add_argument("--bpc", type=int, default=1)
+    ap.add_argument("--bpc", type=int, default=0, help="0 = 2 (CTA pairs) for bf16 split, 1 otherwise")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replica", "ep"],
                     help="N > 1: 'ep' shards the experts over the ranks (NCCL all-to-all dispatch/combine, the "
                          "default when the expert count divides), 'replica' runs N independent copies")
@@ -313,7 +313,7 @@ def run_gpu_arm(args, impl):
         from prime_flash_moe_b200 import capi
         ops = torch.ops.prime_moe
         bn, wn, stages, split, bpc = 64, 4, args.stages, bool(args.split), args.bpc
-        launches_per_step = (3 if T * k > 4096 else 1) + (3 if split else 1)
+        launches_per_step = (3 if T * k > 4096 else 1) + 3   # align kernels + gather, gate/up|fused, down|finalize
 
         def step(x_, ids_, wts_, out_):
             s, e, n = ops.moe_align(ids_, E, 128, bpc)
@@ -519,6 +519,8 @@ def run_cpu_arm(args):
 
 def main():
     args = parse_args()
+    if args.bpc == 0:
+        args.bpc = 2 if (args.dtype == "bf16" and args.split) else 1
     if args.parallel == "auto":
         world = int(os.environ.get("WORLD_SIZE", "1"))
         args.parallel = "ep" if world > 1 and CONFIGS[args.config][2] % world == 0 else "replica"

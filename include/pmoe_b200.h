@@ -159,6 +159,11 @@ int pmoe_reset_device_status(void);
  * previous mask. No counterpart in the reference. */
 int pmoe_debug_set_phase_mask(int mask);
 
+/* Tuning hook, process-wide: the GEMM producers prefetch weight tiles `ksteps` k-steps ahead of their
+ * shared-memory ring into L2 (0 = off, the default; initial value from PMOE_L2_AHEAD). Returns the
+ * previous value. No counterpart in the reference. */
+int pmoe_debug_set_l2_ahead(int ksteps);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,6 +33,7 @@ SIGNATURES = {
     "pmoe_device_status": (_i, [C.POINTER(_i)]),
     "pmoe_reset_device_status": (_i, []),
     "pmoe_debug_set_phase_mask": (_i, [_i]),
+    "pmoe_debug_set_l2_ahead": (_i, [_i]),
 }
 
 _lib = None

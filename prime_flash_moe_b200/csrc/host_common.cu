@@ -108,13 +108,14 @@ bool pdl_enabled() {
     return on;
 }
 
+static int g_l2_ahead = -1;
 int l2_prefetch_distance() {
-    static const int d = [] {
+    if (g_l2_ahead < 0) {
         const char *e = getenv("PMOE_L2_AHEAD");
         const int v = e ? atoi(e) : 0;
-        return v < 0 ? 0 : (v > 64 ? 64 : v);
-    }();
-    return d;
+        g_l2_ahead = v < 0 ? 0 : (v > 64 ? 64 : v);
+    }
+    return g_l2_ahead;
 }
 
 static int g_phase_mask = 7;
@@ -136,6 +137,12 @@ int status_fetch_mxfp8(int *value, bool reset);
 extern "C" const char *pmoe_last_error(void) { return pmoe::g_error; }
 
 extern "C" int pmoe_version(void) { return 100; }
+
+extern "C" int pmoe_debug_set_l2_ahead(int ksteps) {
+    const int old = pmoe::l2_prefetch_distance();
+    pmoe::g_l2_ahead = ksteps < 0 ? 0 : (ksteps > 64 ? 64 : ksteps);
+    return old;
+}
 
 extern "C" int pmoe_debug_set_phase_mask(int mask) {
     const int old = pmoe::g_phase_mask;
