@@ -145,6 +145,14 @@ int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, 
                             size_t workspace_bytes, pmoe_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Expert-parallel combine (no counterpart in the reference, which is single-GPU): after the combine
+ * all-to-all, pair p's expert output is row slot_of_pair[p] of y (bf16 [P, K], P = T*top_k);
+ * out[t, :] = bf16(sum_j weights[t*top_k + j] * y[slot_of_pair[t*top_k + j], :]), fp32 accumulation.
+ * K % 8 == 0; y and out 16-byte aligned. */
+int pmoe_ep_combine(const void *y, const int64_t *slot_of_pair, const float *weights, void *out, int T,
+                    int top_k, int K, pmoe_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Device status. Every wait inside the kernels is bounded; a wait that expires records a code in a
  * device status word and the kernel unwinds. These two calls synchronise the current device.
  * No counterpart in the reference (its waits are unbounded, tcgen05_prelude.cuh:404-414).

@@ -30,6 +30,7 @@ SIGNATURES = {
     "pmoe_fused_moe_mxfp8": (_i, [_vp] * 11 + [_i] * 12 + [_vp]),
     "pmoe_fused_moe_mxfp8_workspace_bytes": (_sz, [_i] * 5),
     "pmoe_fused_moe_mxfp8_ws": (_i, [_vp] * 11 + [_i] * 12 + [_vp, _sz, _vp]),
+    "pmoe_ep_combine": (_i, [_vp] * 4 + [_i] * 3 + [_vp]),
     "pmoe_device_status": (_i, [C.POINTER(_i)]),
     "pmoe_reset_device_status": (_i, []),
     "pmoe_debug_set_phase_mask": (_i, [_i]),

@@ -180,9 +180,29 @@ void fused_moe_mxfp8(const torch::Tensor &x, const torch::Tensor &x_scales, cons
         split ? 1 : 0, ws_ptr, ws_bytes, stream));
 }
 
+// expert-parallel combine: out[t] = sum_j weights[t, j] * y[slots[t, j]] (not in the reference)
+torch::Tensor ep_combine(const torch::Tensor &y, const torch::Tensor &slots, const torch::Tensor &weights,
+                         int64_t top_k) {
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    at::cuda::OptionalCUDAGuard guard{device_of(y)};
+    TORCH_CHECK(y.dim() == 2 && y.is_contiguous() && y.dtype() == torch::kBFloat16);
+    TORCH_CHECK(slots.is_contiguous() && slots.dtype() == torch::kInt64);
+    TORCH_CHECK(weights.is_contiguous() && weights.dtype() == torch::kFloat32);
+    TORCH_CHECK(top_k > 0 && slots.numel() == weights.numel() && slots.numel() % top_k == 0);
+    TORCH_CHECK(slots.numel() <= y.size(0), "every pair needs a row of y");
+    const int64_t T = slots.numel() / top_k, K = y.size(1);
+    torch::Tensor out = torch::empty({T, K}, y.options());
+    check_status(pmoe_ep_combine(y.const_data_ptr(), static_cast<const int64_t *>(slots.const_data_ptr()),
+                                 static_cast<const float *>(weights.const_data_ptr()), out.data_ptr(),
+                                 static_cast<int>(T), static_cast<int>(top_k), static_cast<int>(K), stream));
+    return out;
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(prime_moe, m) {
+    m.def("ep_combine(Tensor y, Tensor slots, Tensor weights, int top_k) -> Tensor");
+    m.impl("ep_combine", torch::kCUDA, &ep_combine);
     m.def(
         "fused_moe_bf16(Tensor x, Tensor w, Tensor w2, Tensor sorted_token_ids, Tensor expert_ids, "
         "Tensor num_tokens_post_padded, Tensor topk_weights, Tensor(a!) out, int top_k, int block_m, "

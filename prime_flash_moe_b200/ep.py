@@ -61,23 +61,26 @@ def _all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group) -> tor
 class LocalExperts:
     """The CUDA path for step 3: this rank's experts through ``moe_align`` + ``fused_moe_*``."""
 
-    def __init__(self, w1, w2, w1_scales=None, w2_scales=None, stages: int = 4, split: bool = True):
+    def __init__(self, w1, w2, w1_scales=None, w2_scales=None, stages: int = 4, split: bool = True, bpc: int = 0):
         self.w1, self.w2, self.w1_scales, self.w2_scales = w1, w2, w1_scales, w2_scales
         self.stages, self.split = stages, split
         self.num_local = w1.shape[0]
+        # CTA pairs (bpc=2) for the bf16 split pipeline unless told otherwise; mxfp8 supports bpc=1 only
+        self.bpc = bpc if bpc else (2 if (w1_scales is None and split) else 1)
 
     def __call__(self, rows: torch.Tensor, local_expert: torch.Tensor, row_scales: Optional[torch.Tensor] = None):
         if not rows.is_cuda:
             raise RuntimeError("LocalExperts needs CUDA tensors: this package has no CPU kernels")
         ops = torch.ops.prime_moe
         R, K = rows.shape
-        out = torch.zeros(R, K, dtype=torch.bfloat16, device=rows.device)
+        out = torch.empty(R, K, dtype=torch.bfloat16, device=rows.device)   # split=True zeroes it itself
         if R == 0:
             return out
-        s, e, n = ops.moe_align(local_expert.reshape(R, 1).contiguous(), self.num_local, 128, 1)
+        s, e, n = ops.moe_align(local_expert.reshape(R, 1).contiguous(), self.num_local, 128, self.bpc)
         ones = torch.ones(R, dtype=torch.float32, device=rows.device)
         if self.w1_scales is None:
-            ops.fused_moe_bf16(rows, self.w1, self.w2, s, e, n, ones, out, 1, 128, 64, 4, self.stages, 1, 1, self.split)
+            ops.fused_moe_bf16(rows, self.w1, self.w2, s, e, n, ones, out, 1, 128, 64, 4, self.stages, self.bpc, 1,
+                               self.split)
         else:
             ops.fused_moe_mxfp8(rows, row_scales, self.w1, self.w1_scales, self.w2, self.w2_scales, s, e, n, ones, out,
                                 1, 128, 64, 4, self.stages, 1, self.split)
@@ -104,21 +107,28 @@ class ExpertParallelMoE:
         if self.world > 1:
             recv_counts = torch.empty_like(plan.send_counts)
             dist.all_to_all_single(recv_counts, plan.send_counts, group=self.group)
-            send, recv = plan.send_counts.tolist(), recv_counts.tolist()   # the one host sync of the step
-            rows = _all_to_all_rows(x[plan.tokens], send, recv, self.group)
+            # everything that does not need the counts is enqueued before the one host sync of the step
+            send_rows = x[plan.tokens]
+            send_scales = x_scales[plan.tokens] if x_scales is not None else None
+            slots = torch.empty_like(plan.perm)
+            slots[plan.perm] = torch.arange(plan.perm.numel(), device=plan.perm.device)
+            send, recv = plan.send_counts.tolist(), recv_counts.tolist()
+            rows = _all_to_all_rows(send_rows, send, recv, self.group)
             local_e = _all_to_all_rows(plan.local_expert, send, recv, self.group)
-            scales = _all_to_all_rows(x_scales[plan.tokens], send, recv, self.group) if x_scales is not None else None
+            scales = _all_to_all_rows(send_scales, send, recv, self.group) if x_scales is not None else None
         else:
+            slots = torch.empty_like(plan.perm)
+            slots[plan.perm] = torch.arange(plan.perm.numel(), device=plan.perm.device)
             rows, local_e = x[plan.tokens], plan.local_expert
             scales = x_scales[plan.tokens] if x_scales is not None else None
         self.last_recv_rows = rows.shape[0]
         y = self.experts(rows, local_e, scales) if scales is not None else self.experts(rows, local_e)
         if self.world > 1:
             y = _all_to_all_rows(y, recv, send, self.group)
-        # combine at the source: pair p sits in slot inv[p]; out[t] = sum_j w[t,j] * y[inv[t*k+j]]
-        inv = torch.empty_like(plan.perm)
-        inv[plan.perm] = torch.arange(plan.perm.numel(), device=plan.perm.device)
-        y = y[inv].view(T, top_k, K).float()
+        # combine at the source: pair p sits in row slots[p]; out[t] = sum_j w[t,j] * y[slots[t*k+j]]
+        if y.is_cuda:
+            return torch.ops.prime_moe.ep_combine(y, slots, topk_weights.reshape(-1).float().contiguous(), top_k)
+        y = y[slots].view(T, top_k, K).float()          # CPU ranks (gloo tests of the host logic)
         return (y * topk_weights.view(T, top_k, 1).float()).sum(1).to(torch.bfloat16)
 
     __call__ = forward
