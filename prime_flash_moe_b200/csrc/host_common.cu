@@ -108,6 +108,14 @@ bool pdl_enabled() {
     return on;
 }
 
+int down_bulk_reduce_mode() {
+    static const int m = [] {
+        const char *e = getenv("PMOE_DOWN_BULK");
+        return e ? (e[0] == '0' ? 0 : 1) : -1;
+    }();
+    return m;
+}
+
 static int g_l2_ahead = -1;
 int l2_prefetch_distance() {
     if (g_l2_ahead < 0) {

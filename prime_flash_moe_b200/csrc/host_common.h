@@ -48,6 +48,10 @@ bool pdl_enabled();
 // (no pre-pass, smaller workspace, but gather4 issue rate then bounds the gate/up kernel).
 bool pregather_enabled();
 
+// PMOE_DOWN_BULK=0/1 forces the down kernels' epilogue (scattered vector reductions / bulk reductions from a
+// staging tile); unset = -1 = chosen per problem
+int down_bulk_reduce_mode();
+
 // PMOE_L2_AHEAD=n: the GEMM producers prefetch weight tiles n k-steps ahead of the ring into L2
 int l2_prefetch_distance();
 

@@ -59,6 +59,8 @@ constexpr int GROUP_M = 8;                       // row blocks that run side by 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int MAX_THREADS = 64 + 8 * 32;
 constexpr uint32_t BAR_BYTES = 256;
+constexpr uint32_t RED_ROW_BYTES = 256 + 16;     // down epilogue staging: 128 bf16 per row, padded against bank conflicts
+constexpr uint32_t RED_STAGE_BYTES = 128 * RED_ROW_BYTES;
 
 struct Coord {
     int m_blk, n_tile;
@@ -89,6 +91,7 @@ struct Args {
     int epi_warps;   // 4 or 8
     int zero_out;    // up kernel: clear `out` before the first tile
     int use_pdl;     // down kernel: wait for the primary grid before touching its results
+    int bulk_reduce; // down kernels: epilogue reduces into `out` with cp.reduce.async.bulk from a staging tile
     int l2_ahead;    // producers prefetch weight tiles this many k-steps ahead of the ring into L2 (0 = off)
     int pregathered; // up kernel: A rows come from a row-gathered copy of x (plain 2-D TMA) instead of gather4
 };
@@ -110,15 +113,15 @@ struct Smem {
     __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * MAX_STAGES + i); }
     __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * MAX_STAGES + 12); }
 };
-__device__ __forceinline__ Smem carve(const uint8_t *raw, int stages, bool with_act) {
+__device__ __forceinline__ Smem carve(const uint8_t *raw, int stages, uint32_t extra) {
     Smem s;
     s.ring = (smem_u32(raw) + 1023u) & ~1023u;
     s.act = s.ring + stages * STAGE_BYTES;
-    s.bars = s.act + (with_act ? ACT_TILE_BYTES : 0);
+    s.bars = s.act + extra;   // extra = activation tile (up / fused) or reduction staging (down) or 0
     return s;
 }
-size_t smem_bytes(int stages, bool with_act) {
-    return 1024 + static_cast<size_t>(stages) * STAGE_BYTES + (with_act ? ACT_TILE_BYTES : 0) + BAR_BYTES;
+size_t smem_bytes(int stages, uint32_t extra) {
+    return 1024 + static_cast<size_t>(stages) * STAGE_BYTES + extra + BAR_BYTES;
 }
 
 // token rows for the four A-tile rows a producer lane gathers (rows 4*lane .. 4*lane+3 of the block)
@@ -198,6 +201,36 @@ __device__ __forceinline__ void reduce_chunk_to_acc32(uint32_t taddr, float wgt,
     }
 }
 
+// Down epilogue through the TMA engine: one accumulator row (thread = row) of 256 columns is scaled,
+// rounded to bf16, staged 128 columns at a time in this thread's padded shared-memory row and added into
+// out[token] by one 256-byte bulk reduction per half (instead of 16 scattered 16-byte reductions).
+// Only the thread itself reads and writes its staging row, so its own bulk group is the only sync.
+// `release` is called once the accumulator has been read completely.
+template <typename Release>
+__device__ __forceinline__ void bulk_reduce_row(uint32_t acc, uint32_t lane_base, uint32_t red_row, float wgt,
+                                                __nv_bfloat16 *dst, bool valid, int cols, Release release) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        tma_store_wait_read<0>();   // this thread's previous reduction has finished reading the row
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float v[32];
+            tmem_ld_32x32(v, tmem_addr(acc, lane_base, (half * 4 + q) * 32));
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                st_shared_v4(red_row + q * 64 + j * 16, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                             pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                             pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                             pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
+        }
+        if (half == 1) release();
+        fence_proxy_async_smem();
+        if (valid && half * 128 < cols) bulk_reduce_add_bf16(dst + half * 128, red_row, 256);
+        tma_store_commit();
+    }
+}
+
 // out[i] += bf16(acc32[i]): last launch of the single-GEMM-launch pipeline (split == 0)
 __global__ void __launch_bounds__(256)
 finalize_acc32_kernel(const float *__restrict__ acc32, __nv_bfloat16 *__restrict__ out, long long n8, int use_pdl) {
@@ -245,7 +278,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                    const __grid_constant__ CUtensorMap map_act, const Args a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem sm = carve(smem_raw, a.stages, true);
+    const Smem sm = carve(smem_raw, a.stages, ACT_TILE_BYTES);
     int *status = &g_status_bf16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_threads = a.epi_warps * 32;
@@ -406,7 +439,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_w2,
                      const Args a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem sm = carve(smem_raw, a.stages, false);
+    const Smem sm = carve(smem_raw, a.stages, a.bulk_reduce ? RED_STAGE_BYTES : 0u);
     int *status = &g_status_bf16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_threads = a.epi_warps * 32;
@@ -418,8 +451,8 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
         }
         mbar_init(sm.misc(0), 1);
         mbar_init(sm.misc(1), 1);
-        mbar_init(sm.misc(2), epi_threads);
-        mbar_init(sm.misc(3), epi_threads);
+        mbar_init(sm.misc(2), a.bulk_reduce ? 128 : epi_threads);   // the bulk epilogue runs on 4 warps
+        mbar_init(sm.misc(3), a.bulk_reduce ? 128 : epi_threads);
         fence_mbar_init();
         tma_prefetch_desc(&map_act);
         tma_prefetch_desc(&map_w2);
@@ -513,15 +546,24 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
             const int col0 = c.n_tile * 256;
             __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + col0;
             const int cols = min(256, a.K - col0);
+            if (a.bulk_reduce && ew >= 4) break;   // warps beyond the first four idle in the bulk epilogue
             if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + buf * 256;
+            if (a.bulk_reduce) {
+                bulk_reduce_row(acc, lane_base, sm.act + row * RED_ROW_BYTES, wgt, dst, valid, cols, [&] {
+                    tc_fence_before();
+                    mbar_arrive(sm.misc(2 + buf));
+                });
+                continue;
+            }
             for (int ch = cg * (8 / ncg); ch < (cg + 1) * (8 / ncg); ++ch)
                 reduce_chunk_to_out(tmem_addr(acc, lane_base, ch * 32), wgt, dst + ch * 32,
                                     valid && ch * 32 < cols);
             tc_fence_before();
             mbar_arrive(sm.misc(2 + buf));
         }
+        if (a.bulk_reduce) tma_store_wait<0>();
     }
 
     tc_fence_before();
@@ -538,7 +580,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                       const __grid_constant__ CUtensorMap map_w2, const Args a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem sm = carve(smem_raw, a.stages, true);
+    const Smem sm = carve(smem_raw, a.stages, ACT_TILE_BYTES);
     int *status = &g_status_bf16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_threads = a.epi_warps * 32;
@@ -761,15 +803,15 @@ struct SmemPair {
     __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * PAIR_MAX_STAGES + i); }
     __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * PAIR_MAX_STAGES + 12); }
 };
-__device__ __forceinline__ SmemPair carve_pair(const uint8_t *raw, int stages, bool with_act) {
+__device__ __forceinline__ SmemPair carve_pair(const uint8_t *raw, int stages, uint32_t extra) {
     SmemPair s;
     s.ring = (smem_u32(raw) + 1023u) & ~1023u;
     s.act = s.ring + stages * PAIR_STAGE_BYTES;
-    s.bars = s.act + (with_act ? ACT_TILE_BYTES : 0);
+    s.bars = s.act + extra;
     return s;
 }
-size_t smem_bytes_pair(int stages, bool with_act) {
-    return 1024 + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + (with_act ? ACT_TILE_BYTES : 0) + BAR_BYTES;
+size_t smem_bytes_pair(int stages, uint32_t extra) {
+    return 1024 + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + extra + BAR_BYTES;
 }
 
 template <bool kUp>
@@ -777,7 +819,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_act, const Args a) {
     extern __shared__ uint8_t smem_raw[];
-    const SmemPair sm = carve_pair(smem_raw, a.stages, kUp);
+    const SmemPair sm = carve_pair(smem_raw, a.stages, kUp ? ACT_TILE_BYTES : (a.bulk_reduce ? RED_STAGE_BYTES : 0u));
     int *status = &g_status_bf16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_threads = a.epi_warps * 32;
@@ -793,8 +835,8 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         }
         mbar_init(sm.misc(0), 1);
         mbar_init(sm.misc(1), 1);
-        mbar_init(sm.misc(2), 2 * epi_threads);
-        mbar_init(sm.misc(3), 2 * epi_threads);
+        mbar_init(sm.misc(2), 2 * ((!kUp && a.bulk_reduce) ? 128 : epi_threads));
+        mbar_init(sm.misc(3), 2 * ((!kUp && a.bulk_reduce) ? 128 : epi_threads));
         mbar_init(sm.misc(4), epi_threads);
         mbar_init(sm.misc(5), 1);
         fence_mbar_init();
@@ -925,8 +967,16 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 const int col0 = c.n_tile * 256;
                 __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + col0;
                 const int cols = min(256, a.K - col0);
+                if (a.bulk_reduce && ew >= 4) break;
                 if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
                 tc_fence_after();
+                if (a.bulk_reduce) {
+                    bulk_reduce_row(acc, lane_base, sm.act + row * RED_ROW_BYTES, wgt, dst, valid, cols, [&] {
+                        tc_fence_before();
+                        mbar_arrive_cluster(empty_leader);
+                    });
+                    continue;
+                }
                 for (int ch = cg * (8 / ncg); ch < (cg + 1) * (8 / ncg); ++ch)
                     reduce_chunk_to_out(tmem_addr(acc, lane_base, ch * 32), wgt, dst + ch * 32,
                                         valid && ch * 32 < cols);
@@ -935,6 +985,7 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
         }
         if (kUp && et == 0) tma_store_wait<0>();
+        if (!kUp && a.bulk_reduce) tma_store_wait<0>();
     }
 
     tc_fence_before();
@@ -1011,6 +1062,8 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     a.stages = std::min(p.stages, MAX_STAGES);
     a.epi_warps = p.warp_n;
     a.l2_ahead = l2_prefetch_distance();
+    const int bulk = down_bulk_reduce_mode();   // -1 auto: on when the down GEMM's K extent (H) is short
+    const bool bulk_reduce = bulk < 0 ? (H <= 1024) : bulk != 0;
     const int threads = 64 + 32 * a.epi_warps;
     const int sms = sm_count();
 
@@ -1046,7 +1099,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
                 return rc;
             a.pregathered = 1;
         }
-        const size_t smem = smem_bytes(a.stages, true);
+        const size_t smem = smem_bytes(a.stages, ACT_TILE_BYTES);
         if (int rc = set_smem(moe_fused_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
         moe_fused_bf16_kernel<<<std::min(tiles, sms), threads, smem, stream>>>(map_x, map_w1, map_w2, a);
@@ -1106,8 +1159,8 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         auto launch_pair = [&](auto kernel, const CUtensorMap &ma, const CUtensorMap &mb, const Args &args, int tiles,
-                               bool with_act, int nattr) -> int {
-            const size_t smem = smem_bytes_pair(args.stages, with_act);
+                               uint32_t extra, int nattr) -> int {
+            const size_t smem = smem_bytes_pair(args.stages, extra);
             if (int rc = set_smem(kernel, smem)) return rc;
             PMOE_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
             cudaLaunchConfig_t cfg = {};
@@ -1127,14 +1180,18 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         if (phases & 2) {
             Args up = pa;
             up.zero_out = 1;
-            if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128), true, 1))
+            if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128),
+                                     ACT_TILE_BYTES, 1))
                 return rc;
         }
         if (phases & 4) {
             Args dn = pa;
             dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
+            dn.bulk_reduce = bulk_reduce ? 1 : 0;
+            if (bulk_reduce) dn.stages = std::min(dn.stages, 5);   // room for the reduction staging tile
             if (int rc = launch_pair(moe_pair_bf16_kernel<false>, map_act, map_w2h, dn,
-                                     (max_blocks / 2) * ((p.K + 255) / 256), false, dn.use_pdl ? 2 : 1))
+                                     (max_blocks / 2) * ((p.K + 255) / 256), bulk_reduce ? RED_STAGE_BYTES : 0u,
+                                     dn.use_pdl ? 2 : 1))
                 return rc;
         }
         return PMOE_OK;
@@ -1143,7 +1200,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         Args up = a;
         up.zero_out = 1;
         up.pregathered = pregather ? 1 : 0;
-        const size_t smem = smem_bytes(up.stages, true);
+        const size_t smem = smem_bytes(up.stages, ACT_TILE_BYTES);
         if (int rc = set_smem(moe_up_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
         moe_up_bf16_kernel<<<std::min(tiles, sms), threads, smem, stream>>>(map_x, map_w1, map_act, up);
@@ -1152,7 +1209,9 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (phases & 4) {
         Args dn = a;
         dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
-        const size_t smem = smem_bytes(dn.stages, false);
+        dn.bulk_reduce = bulk_reduce ? 1 : 0;
+        if (bulk_reduce) dn.stages = std::min(dn.stages, 3);       // room for the reduction staging tile
+        const size_t smem = smem_bytes(dn.stages, dn.bulk_reduce ? RED_STAGE_BYTES : 0u);
         if (int rc = set_smem(moe_down_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * ((p.K + 255) / 256);
         cudaLaunchConfig_t cfg = {};

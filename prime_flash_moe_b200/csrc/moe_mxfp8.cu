@@ -53,6 +53,8 @@ constexpr uint32_t SF_TMEM_BASE = 256;           // columns [256, 384): eight 16
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr uint32_t BAR_BYTES = 256;
+constexpr uint32_t RED_ROW_BYTES = 256 + 16;              // down epilogue staging: 128 bf16 per thread, padded
+constexpr uint32_t RED_STAGE_BYTES = EPI_WARPS * 32 * RED_ROW_BYTES;
 
 struct Args {
     const int32_t *sorted_ids;
@@ -71,6 +73,7 @@ struct Args {
     int stages;
     int zero_out;
     int use_pdl;
+    int bulk_reduce;   // down kernel: reduce into `out` with cp.reduce.async.bulk from a staging tile
 };
 
 struct Smem {
@@ -84,15 +87,16 @@ struct Smem {
     __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * MAX_STAGES + i); }
     __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * MAX_STAGES + 12); }
 };
-__device__ __forceinline__ Smem carve(const uint8_t *raw, int stages, bool with_act) {
+constexpr uint32_t ACT_EXTRA = ACT_TILE_BYTES + 1024;   // activation tile + one 512-byte scale tile (fused), padded
+__device__ __forceinline__ Smem carve(const uint8_t *raw, int stages, uint32_t extra) {
     Smem s;
     s.ring = (smem_u32(raw) + 1023u) & ~1023u;
     s.act = s.ring + stages * STAGE_BYTES;
-    s.bars = s.act + (with_act ? ACT_TILE_BYTES + 1024 : 0);   // + one 512-byte scale tile (fused), padded
+    s.bars = s.act + extra;   // extra = ACT_EXTRA (up / fused), reduction staging (down) or 0
     return s;
 }
-size_t smem_bytes(int stages, bool with_act) {
-    return 1024 + static_cast<size_t>(stages) * STAGE_BYTES + (with_act ? ACT_TILE_BYTES + 1024 : 0) + BAR_BYTES;
+size_t smem_bytes(int stages, uint32_t extra) {
+    return 1024 + static_cast<size_t>(stages) * STAGE_BYTES + extra + BAR_BYTES;
 }
 
 __device__ __forceinline__ void drain_fills(const Smem &sm, int stages, long long issued) {
@@ -174,7 +178,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                     const __grid_constant__ CUtensorMap map_act, const Args a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem sm = carve(smem_raw, a.stages, true);
+    const Smem sm = carve(smem_raw, a.stages, ACT_EXTRA);
     int *status = &g_status_mxfp8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int epi_threads = EPI_WARPS * 32;
@@ -344,7 +348,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_w2,
                       const Args a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem sm = carve(smem_raw, a.stages, false);
+    const Smem sm = carve(smem_raw, a.stages, a.bulk_reduce ? RED_STAGE_BYTES : 0u);
     int *status = &g_status_mxfp8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int epi_threads = EPI_WARPS * 32;
@@ -455,6 +459,21 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(sm.misc(1));
+            if (a.bulk_reduce) {
+                // scaled bf16 row segment -> this thread's padded staging row -> one 256-byte bulk reduction
+                const uint32_t red_row = sm.act + (threadIdx.x - 64) * RED_ROW_BYTES;
+                tma_store_wait_read<0>();
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    st_shared_v4(red_row + j * 16, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                                 pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                                 pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                                 pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
+                fence_proxy_async_smem();
+                if (valid) bulk_reduce_add_bf16(dst, red_row, 256);
+                tma_store_commit();
+                continue;
+            }
             if (valid) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
@@ -464,6 +483,7 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
                                    pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
             }
         }
+        if (a.bulk_reduce) tma_store_wait<0>();
     }
 
     tc_fence_before();
@@ -482,7 +502,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 moe_fused_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                        const __grid_constant__ CUtensorMap map_w2, const Args a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem sm = carve(smem_raw, a.stages, true);
+    const Smem sm = carve(smem_raw, a.stages, ACT_EXTRA);
     const uint32_t act_sf_smem = sm.act + ACT_TILE_BYTES;
     int *status = &g_status_mxfp8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -853,7 +873,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         {
             Args fa = a;
             fa.use_pdl = use_pdl;
-            const size_t smem = smem_bytes(fa.stages, true);
+            const size_t smem = smem_bytes(fa.stages, ACT_EXTRA);
             if (int rc = set_smem(moe_fused_mxfp8_kernel, smem)) return rc;
             const int tiles = max_blocks * (H / 128);
             cudaLaunchConfig_t cfg = {};
@@ -878,7 +898,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (phases & 2) {
         Args up = a;
         up.zero_out = 1;
-        const size_t smem = smem_bytes(up.stages, true);
+        const size_t smem = smem_bytes(up.stages, ACT_EXTRA);
         if (int rc = set_smem(moe_up_mxfp8_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
         moe_up_mxfp8_kernel<<<std::min(tiles, sms), THREADS, smem, stream>>>(map_x, map_w1, map_act, up);
@@ -887,7 +907,10 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (phases & 4) {
         Args dn = a;
         dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
-        const size_t smem = smem_bytes(dn.stages, false);
+        const int bulk = down_bulk_reduce_mode();   // -1 auto: on when the down GEMM's K extent (H) is short
+        dn.bulk_reduce = (bulk < 0 ? (H <= 1024) : bulk != 0) ? 1 : 0;
+        if (dn.bulk_reduce) dn.stages = std::min(dn.stages, 3);   // room for the reduction staging tile
+        const size_t smem = smem_bytes(dn.stages, dn.bulk_reduce ? RED_STAGE_BYTES : 0u);
         if (int rc = set_smem(moe_down_mxfp8_kernel, smem)) return rc;
         const int tiles = max_blocks * (p.K / 256);
         cudaLaunchConfig_t cfg = {};

@@ -161,6 +161,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
                  ::"l"(map), "r"(src), "r"(c0), "r"(c1)
                  : "memory");
 }
+// global[dst .. dst+bytes) += shared[src .. src+bytes) element-wise in bf16 (one bulk reduction handled
+// by the TMA engine; both addresses 16-byte aligned, bytes a multiple of 16; joins the thread's bulk group)
+__device__ __forceinline__ void bulk_reduce_add_bf16(void *gdst, uint32_t ssrc, uint32_t bytes) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;"
+                 ::"l"(gdst), "r"(ssrc), "r"(bytes)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all but the N most recent groups have finished READING shared memory
 template <int N>
