@@ -108,6 +108,18 @@ bool pdl_enabled() {
     return on;
 }
 
+int a_operand_mode() {
+    static const int m = [] {
+        const char *e = getenv("PMOE_AGATHER");
+        if (e && !strcmp(e, "tma4")) return 0;
+        if (e && !strcmp(e, "lsu")) return 2;
+        if (e && !strcmp(e, "pre")) return 1;
+        if (getenv("PMOE_PREGATHER")) return pregather_enabled() ? 1 : 0;
+        return -1;   // auto: LSU gather in the one-CTA kernels, row-gather pre-pass for the CTA-pair kernels
+    }();
+    return m;
+}
+
 int down_bulk_reduce_mode() {
     static const int m = [] {
         const char *e = getenv("PMOE_DOWN_BULK");

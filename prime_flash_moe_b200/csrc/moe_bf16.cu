@@ -57,7 +57,8 @@ constexpr uint32_t ACT_TILE_BYTES = 128 * 128 * 2;  // 128 rows x 128 bf16: two 
 constexpr int MAX_STAGES = 4;
 constexpr int GROUP_M = 8;                       // row blocks that run side by side on one weight slice
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int MAX_THREADS = 64 + 8 * 32;
+constexpr int GATHER_THREADS = 128;             // optional LSU gather warps at the end of the block
+constexpr int MAX_THREADS = 64 + 8 * 32 + GATHER_THREADS;
 constexpr uint32_t BAR_BYTES = 256;
 constexpr uint32_t RED_ROW_BYTES = 256 + 16;     // down epilogue staging: 128 bf16 per row, padded against bank conflicts
 constexpr uint32_t RED_STAGE_BYTES = 128 * RED_ROW_BYTES;
@@ -93,7 +94,9 @@ struct Args {
     int use_pdl;     // down kernel: wait for the primary grid before touching its results
     int bulk_reduce; // down kernels: epilogue reduces into `out` with cp.reduce.async.bulk from a staging tile
     int l2_ahead;    // producers prefetch weight tiles this many k-steps ahead of the ring into L2 (0 = off)
-    int pregathered; // up kernel: A rows come from a row-gathered copy of x (plain 2-D TMA) instead of gather4
+    int pregathered; // gate/up A operand: 0 = TMA gather4 from x, 1 = plain tiles from a row-gathered copy,
+                     // 2 = gathered from x by four LSU warps (cp.async), no pre-pass
+    const __nv_bfloat16 *x;   // mode 2: the activation matrix [M, K]
 };
 
 __device__ __forceinline__ int num_row_blocks(const Args &a) {
@@ -287,7 +290,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
-            mbar_init(sm.full(s), 1);
+            mbar_init(sm.full(s), a.pregathered == 2 ? 1 + GATHER_THREADS : 1);
             mbar_init(sm.empty(s), 1);
         }
         mbar_init(sm.misc(0), 1);
@@ -331,17 +334,17 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 if (lane == 0) {
-                    mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
+                    mbar_arrive_expect_tx(sm.full(s), a.pregathered == 2 ? B_BYTES : STAGE_BYTES);
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
-                    if (a.pregathered) tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BK, c.m_blk * BM);
+                    if (a.pregathered == 1) tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BK, c.m_blk * BM);
                     if (a.l2_ahead && ks + a.l2_ahead < ksteps) {
                         tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_gate);
                         tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_up);
                     }
                 }
                 __syncwarp();
-                if (!a.pregathered)
+                if (a.pregathered == 0)
                     tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
                 ++issued;
                 if (++s == a.stages) {
@@ -384,6 +387,59 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             }
         }
         __syncwarp();
+    } else if (warp >= 2 + a.epi_warps) {
+        // ---------------- LSU gather warps (mode 2): A tile rows straight from x ----------------
+        // 8 consecutive lanes copy the eight 16-byte chunks of one 128-byte row segment (a full line per
+        // row, 4 rows per warp instruction); thread g serves rows (g>>3) + 16*i, i = 0..7.
+        // cp.async writes shared memory through the generic proxy while tcgen05.mma reads it through the
+        // async proxy, so each thread waits for its own copies of a slot (lagging `lag` slots behind the
+        // ones it is issuing), fences the proxies, and only then arrives on the slot's full barrier.
+        const int g = threadIdx.x - 64 - epi_threads;
+        const int q = g >> 3, chunk = g & 7;
+        const int lag = min(2, a.stages - 1);
+        int s = 0, s_done = 0;
+        uint32_t ph = 0;
+        long long issued = 0, arrived = 0;
+        auto publish = [&](int pending_allowed) {   // copies of all but the newest `pending_allowed` slots landed
+            if (pending_allowed >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else if (pending_allowed == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            fence_proxy_async_smem();
+            while (arrived < issued - pending_allowed) {
+                mbar_arrive(sm.full(s_done));
+                if (++s_done == a.stages) s_done = 0;
+                ++arrived;
+            }
+        };
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const char *src[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int pair = a.sorted_ids[c.m_blk * BM + q + 16 * i];
+                int tok = pair >= 0 ? pair / a.top_k : 0;
+                if (tok >= a.M) tok = 0;
+                src[i] = reinterpret_cast<const char *>(a.x + static_cast<size_t>(tok) * a.K) + chunk * 16;
+            }
+            for (int ks = 0; ks < ksteps; ++ks) {
+                ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                if (!ok) break;
+                // (q + 16 i) & 7 == q & 7: every row of this thread uses the same swizzled chunk slot
+                const uint32_t dst = sm.a(s) + q * 128 + ((chunk ^ (q & 7)) << 4);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) cp_async_16(dst + i * 16 * 128, src[i] + ks * 128);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                ++issued;
+                if (++s == a.stages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+                if (issued - arrived > lag) publish(lag);
+            }
+        }
+        publish(0);
+        cp_async_wait_all();
     } else {
         // ---------------- epilogue: thread = accumulator row ----------------
         const int ew = warp - 2;
@@ -1122,7 +1178,9 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     // split pipeline: workspace = activation [sorted_num, H] bf16 (+ x_sorted [sorted_num, K] when pre-gathering)
     PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16: workspace must be 1024-byte aligned");
-    const bool pregather = pregather_enabled();
+    int a_mode = a_operand_mode();                // 0 gather4, 1 row-gather pre-pass, 2 LSU gather in the kernel
+    if (a_mode < 0) a_mode = 1;
+    const bool pregather = a_mode == 1 || p.bpc == 2;   // the CTA-pair kernels always take pre-gathered rows
     const int phases = phase_mask();  // profiling hook: 1 = gather, 2 = gate/up, 4 = down (default all)
     if (pregather) {
         __nv_bfloat16 *x_sorted = static_cast<__nv_bfloat16 *>(workspace) + static_cast<size_t>(p.sorted_num) * H;
@@ -1144,7 +1202,6 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         return rc;
     if (p.bpc == 2) {
         // two-CTA pipeline: always fed from the row-gathered copy; B tiles are loaded as 128-row halves
-        PMOE_REQUIRE(pregather, PMOE_ERR_UNSUPPORTED, "bpc=2 needs the row-gather pre-pass (unset PMOE_PREGATHER=0)");
         CUtensorMap map_w2h;
         if (int rc = make_tmap_2d(&map_w2h, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2,
                                   static_cast<uint64_t>(p.E) * p.K, H, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
@@ -1180,6 +1237,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         if (phases & 2) {
             Args up = pa;
             up.zero_out = 1;
+
             if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128),
                                      ACT_TILE_BYTES, 1))
                 return rc;
@@ -1199,7 +1257,9 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (phases & 2) {
         Args up = a;
         up.zero_out = 1;
-        up.pregathered = pregather ? 1 : 0;
+        up.pregathered = a_mode;
+        up.x = static_cast<const __nv_bfloat16 *>(p.x);
+        const int threads = 64 + 32 * a.epi_warps + (a_mode == 2 ? GATHER_THREADS : 0);
         const size_t smem = smem_bytes(up.stages, ACT_TILE_BYTES);
         if (int rc = set_smem(moe_up_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);

@@ -181,6 +181,21 @@ __device__ __forceinline__ void tma_store_wait() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// LSU-side asynchronous copies (row gathers the TMA engine is too slow for)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+// the barrier receives one (pre-counted) arrival once all earlier cp.async of this thread have landed
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // programmatic dependent launch
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait_primary() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
