@@ -1179,7 +1179,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16: workspace must be 1024-byte aligned");
     int a_mode = a_operand_mode();                // 0 gather4, 1 row-gather pre-pass, 2 LSU gather in the kernel
-    if (a_mode < 0) a_mode = 1;
+    if (a_mode < 0) a_mode = (p.bpc == 1 && p.N < 8192) ? 2 : 1;   // measured: the pre-pass costs ~250/N of the step
     const bool pregather = a_mode == 1 || p.bpc == 2;   // the CTA-pair kernels always take pre-gathered rows
     const int phases = phase_mask();  // profiling hook: 1 = gather, 2 = gate/up, 4 = down (default all)
     if (pregather) {

@@ -201,3 +201,35 @@ def test_vs_reference_kernels(T, K, E, N, k):
         # one tolerance: bound the distance by 1.5 tolerances, and hold this library to the gate itself
         assert O.max_rel_to_peak(mine, ref_out.cpu()) <= 1.5 * TOL
         assert O.max_rel_to_peak(mine, ref32) <= TOL
+
+
+@pytest.mark.parametrize("split", [True, False])
+def test_cuda_graph_capture_and_replay(split):
+    """The operators enqueue on the caller's stream without synchronising the host, so a CUDA graph can
+    capture them (the reference's benchmark times graph replays, benchmark/benchmark.py:355-370)."""
+    import prime_flash_moe_b200 as P
+    x, w1, w2, ids, wts = O.make_case(96, 512, 8, 512, 2, seed=21)
+    ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
+    xd, w1d, w2d, idd, wd = x.to(DEV), w1.to(DEV), w2.to(DEV), ids.to(DEV), wts.to(DEV)
+    out = torch.zeros(96, 512, dtype=torch.bfloat16, device=DEV)
+
+    def step():
+        s, e, n = torch.ops.prime_moe.moe_align(idd, 8, 128, 1)
+        if not split:
+            out.zero_()
+        P.fused_moe_bf16(xd, w1d, w2d, s, e, n, wd, out, 2, 128, 64, 4, 4, 1, 1, split)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()                      # warm-up outside the capture (lazy initialisation)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(3):
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert O.max_rel_to_peak(out.cpu(), ref) <= TOL
