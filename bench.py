@@ -247,7 +247,8 @@ def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tf
     assert capi.device_status() == 0
     return {"kernel": "moe_up_mxfp8_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "peak_source": source,
-            "traffic": None, "kernel_ms": per_kernel, "whole_op_frac": whole_tflops / peak}
+            "traffic": 0.6565e9 if (args.config == "c2" and not args.tokens) else None,   # profiles/bench_c2_qwen3_T8192.md
+            "kernel_ms": per_kernel, "whole_op_frac": whole_tflops / peak}
 
 
 def measure_mxfp8_peak(device):
@@ -477,12 +478,15 @@ def run_gpu_arm(args, impl):
         torch.cuda.synchronize()
         up_flops = 2.0 * T * k * K * N
         achieved = up_flops / (per_kernel["moe_up_bf16"] * 1e-3) / 1e12
-        roofline = {"kernel": "moe_up_bf16_kernel", "bound": "tensor", "achieved": achieved,
+        # DRAM bytes of one launch of that kernel from the committed ncu captures (profiles/bench_*.md)
+        traffic = {("c1", 2): 5.379e9, ("c2", 1): 1.112e9}.get((args.config, args.bpc)) if not args.tokens else None
+        roofline = {"kernel": "moe_pair_bf16_kernel<up>" if args.bpc == 2 else "moe_up_bf16_kernel", "bound": "tensor",
+                    "achieved": achieved,
                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                     "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
                     "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
-                    "traffic": None, "kernel_ms": per_kernel,
-                    "whole_op_frac": value / world / peaks["bf16_tflops"]}
+                    "traffic": traffic, "algorithmic_bytes": float(E * N * K * 2 + T * k * K * 2 + T * k * N + T * K * 2),
+                    "kernel_ms": per_kernel, "whole_op_frac": value / world / peaks["bf16_tflops"]}
         assert capi.device_status() == 0, "a kernel recorded an error status"
 
     cpu_baseline = None
