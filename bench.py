@@ -247,7 +247,7 @@ def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tf
     assert capi.device_status() == 0
     return {"kernel": "moe_up_mxfp8_kernel", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak, "peak_source": source,
-            "traffic": 0.6565e9 if (args.config == "c2" and not args.tokens) else None,   # profiles/bench_c2_qwen3_T8192.md
+            "traffic": 0.6565e9 if (args.config == "c2" and not args.tokens) else None,   # from the ncu capture summarised under profiles/
             "kernel_ms": per_kernel, "whole_op_frac": whole_tflops / peak}
 
 
@@ -478,7 +478,7 @@ def run_gpu_arm(args, impl):
         torch.cuda.synchronize()
         up_flops = 2.0 * T * k * K * N
         achieved = up_flops / (per_kernel["moe_up_bf16"] * 1e-3) / 1e12
-        # DRAM bytes of one launch of that kernel from the committed ncu captures (profiles/bench_*.md)
+        # DRAM bytes of one launch of that kernel, from the ncu captures summarised under profiles/
         traffic = {("c1", 2): 5.379e9, ("c2", 1): 1.112e9}.get((args.config, args.bpc)) if not args.tokens else None
         roofline = {"kernel": "moe_pair_bf16_kernel<up>" if args.bpc == 2 else "moe_up_bf16_kernel", "bound": "tensor",
                     "achieved": achieved,

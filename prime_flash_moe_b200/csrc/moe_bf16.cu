@@ -255,18 +255,21 @@ finalize_acc32_kernel(const float *__restrict__ acc32, __nv_bfloat16 *__restrict
 
 // ---------------------------------------------------------------------------------------------
 // optional pre-pass of the split pipeline: x_sorted[row] = x[token(row)] (one warp per row, 16-byte
-// loads/stores); padding rows copy token 0. Only rows below num_tokens_post_padded are written.
+// loads/stores) for the valid rows below num_tokens_post_padded; padding rows are left as they are.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ x_sorted, const Args a) {
+    pdl_launch_dependents();   // the gate/up kernel may set itself up; it waits for this grid before loading
     const int warps_per_cta = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int rows = num_row_blocks(a) * BM;
     const int chunks = a.K / 8;  // 16-byte chunks per row
     for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
         const int pair = a.sorted_ids[row];
-        int tok = pair >= 0 ? pair / a.top_k : 0;
-        if (tok >= a.M) tok = 0;
+        const int tok = pair >= 0 ? pair / a.top_k : -1;
+        // padding rows are not copied: whatever the workspace holds there only feeds accumulator rows that
+        // no epilogue ever writes out (every output row depends on its own A row alone)
+        if (tok < 0 || tok >= a.M) continue;
         const int4 *src = reinterpret_cast<const int4 *>(x + static_cast<size_t>(tok) * a.K);
         int4 *dst = reinterpret_cast<int4 *>(x_sorted + static_cast<size_t>(row) * a.K);
         for (int ch = lane; ch < chunks; ch += 32) dst[ch] = __ldg(src + ch);
@@ -310,6 +313,8 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (a.use_pdl) pdl_wait_primary();   // launched as a programmatic dependent of the row-gather kernel
 
     const int m_blocks = num_row_blocks(a);
     const int n_tiles = a.H / 128;
@@ -908,7 +913,7 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
 
-    if (!kUp && a.use_pdl) pdl_wait_primary();
+    if (a.use_pdl) pdl_wait_primary();   // up: after the row-gather kernel; down: after the gate/up kernel
 
     const int m_pairs = num_row_blocks(a) / 2;
     const int n_tiles = kUp ? a.H / 128 : (a.K + 255) / 256;
@@ -1179,7 +1184,11 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16: workspace must be 1024-byte aligned");
     int a_mode = a_operand_mode();                // 0 gather4, 1 row-gather pre-pass, 2 LSU gather in the kernel
-    if (a_mode < 0) a_mode = (p.bpc == 1 && p.N < 8192) ? 2 : 1;   // measured: the pre-pass costs ~250/N of the step
+    // auto: the in-kernel LSU gather pays off when the row-gather pre-pass is a visible share of the step (its
+    // cost is ~250/N of a compute-bound step) and the step is compute-bound (>= 256 routed rows per expert on
+    // average; in the weight-streaming regime the pre-pass with plain tiles streams faster)
+    if (a_mode < 0)
+        a_mode = (p.bpc == 1 && p.N < 8192 && static_cast<long long>(p.M) * p.top_k >= 256ll * p.E) ? 2 : 1;
     const bool pregather = a_mode == 1 || p.bpc == 2;   // the CTA-pair kernels always take pre-gathered rows
     const int phases = phase_mask();  // profiling hook: 1 = gather, 2 = gate/up, 4 = down (default all)
     if (pregather) {
@@ -1237,9 +1246,9 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         if (phases & 2) {
             Args up = pa;
             up.zero_out = 1;
-
+            up.use_pdl = (pdl_enabled() && (phases & 1)) ? 1 : 0;
             if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128),
-                                     ACT_TILE_BYTES, 1))
+                                     ACT_TILE_BYTES, up.use_pdl ? 2 : 1))
                 return rc;
         }
         if (phases & 4) {
@@ -1263,8 +1272,18 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         const size_t smem = smem_bytes(up.stages, ACT_TILE_BYTES);
         if (int rc = set_smem(moe_up_bf16_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
-        moe_up_bf16_kernel<<<std::min(tiles, sms), threads, smem, stream>>>(map_x, map_w1, map_act, up);
-        PMOE_CUDA_OK(cudaGetLastError());
+        up.use_pdl = (pdl_enabled() && pregather && (phases & 1)) ? 1 : 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(std::min(tiles, sms));
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = up.use_pdl ? 1 : 0;
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_bf16_kernel, map_x, map_w1, map_act, up));
     }
     if (phases & 4) {
         Args dn = a;

@@ -151,6 +151,7 @@ __device__ __forceinline__ void issue_slot(uint32_t d, uint32_t a_smem, uint32_t
 __global__ void __launch_bounds__(256)
 gather_rows_mxfp8_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ x_scales,
                          uint8_t *__restrict__ x_sorted, uint8_t *__restrict__ xsf_tiles, const Args a) {
+    pdl_launch_dependents();   // the gate/up (or fused) kernel may set itself up; it waits for this grid before loading
     const int warps_per_cta = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int rows = live_row_blocks(a.npp, a.sorted_num) * BM;
@@ -158,8 +159,10 @@ gather_rows_mxfp8_kernel(const uint8_t *__restrict__ x, const uint8_t *__restric
     const int kblocks = a.K / 32;
     for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
         const int pair = a.sorted_ids[row];
-        int tok = pair >= 0 ? pair / a.top_k : 0;
-        if (tok >= a.M) tok = 0;
+        const int tok = pair >= 0 ? pair / a.top_k : -1;
+        // padding rows (values and scales) are not copied: they only feed accumulator rows that are never
+        // written out, and every output row depends on its own A row alone
+        if (tok < 0 || tok >= a.M) continue;
         const int4 *src = reinterpret_cast<const int4 *>(x + static_cast<size_t>(tok) * a.K);
         int4 *dst = reinterpret_cast<int4 *>(x_sorted + static_cast<size_t>(row) * a.K);
         for (int ch = lane; ch < chunks; ch += 32) dst[ch] = __ldg(src + ch);
@@ -205,6 +208,8 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (a.use_pdl) pdl_wait_primary();   // launched as a programmatic dependent of the row-gather kernel
 
     const int m_blocks = live_row_blocks(a.npp, a.sorted_num);
     const int n_tiles = a.H / 128;
@@ -901,8 +906,18 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         const size_t smem = smem_bytes(up.stages, ACT_EXTRA);
         if (int rc = set_smem(moe_up_mxfp8_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
-        moe_up_mxfp8_kernel<<<std::min(tiles, sms), THREADS, smem, stream>>>(map_x, map_w1, map_act, up);
-        PMOE_CUDA_OK(cudaGetLastError());
+        up.use_pdl = (pdl_enabled() && (phases & 1)) ? 1 : 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(std::min(tiles, sms));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = up.use_pdl ? 1 : 0;
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_mxfp8_kernel, map_x, map_w1, map_act, up));
     }
     if (phases & 4) {
         Args dn = a;

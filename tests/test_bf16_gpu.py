@@ -198,8 +198,10 @@ def test_vs_reference_kernels(T, K, E, N, k):
         mine = run_mine(x, w1, w2, ids, wts, split)
         # the reference's own result sits up to ~1.9e-2 from the fp32 oracle on these shapes (bf16
         # atomics over top_k * H/128 partials), so two correct implementations may differ by more than
-        # one tolerance: bound the distance by 1.5 tolerances, and hold this library to the gate itself
-        assert O.max_rel_to_peak(mine, ref_out.cpu()) <= 1.5 * TOL
+        # one tolerance: bound the distance by two tolerances, and hold this library to the gate itself
+        # (the reference's bf16 atomics make its own result vary from run to run; observed distance to
+        # this library 0.6e-2 .. 2.4e-2, so the bound is two tolerances to keep the check stable)
+        assert O.max_rel_to_peak(mine, ref_out.cpu()) <= 2.0 * TOL
         assert O.max_rel_to_peak(mine, ref32) <= TOL
 
 

@@ -150,7 +150,9 @@ def test_vs_reference_kernels(T, K, E, N, k):
         torch.cuda.synchronize()
         assert O.max_rel_to_peak(mine, ref32) <= TOL
         # the reference's split=False result itself sits ~2e-2 from the oracle (bf16 atomics)
-        assert O.max_rel_to_peak(mine, ref_out.cpu()) <= 1.5 * TOL
+        # (the reference's bf16 atomics make its own result vary from run to run; observed distance to
+        # this library 0.6e-2 .. 2.4e-2, so the bound is two tolerances to keep the check stable)
+        assert O.max_rel_to_peak(mine, ref_out.cpu()) <= 2.0 * TOL
 
 
 def test_full_size_properties_qwen3():
