@@ -138,6 +138,11 @@ int l2_prefetch_distance() {
     return g_l2_ahead;
 }
 
+int short_boxes_mode() {
+    const char *e = getenv("PMOE_SHORT_A");
+    return e ? atoi(e) & 3 : 3;
+}
+
 static int g_phase_mask = 7;
 int phase_mask() { return g_phase_mask; }
 

@@ -60,6 +60,10 @@ int down_bulk_reduce_mode();
 // PMOE_L2_AHEAD=n: the GEMM producers prefetch weight tiles n k-steps ahead of the ring into L2
 int l2_prefetch_distance();
 
+// PMOE_SHORT_A=0 switches off the short TMA boxes (row blocks with few routed rows move only those rows of the
+// A operand and of the activation tile); read on every call so that tests can compare both settings
+int short_boxes_mode();   // bit 0: loads, bit 1: activation stores
+
 // which launches of a split pipeline run (pmoe_debug_set_phase_mask): 1 gather, 2 gate/up, 4 down
 int phase_mask();
 

@@ -97,7 +97,17 @@ struct Args {
     int pregathered; // gate/up A operand: 0 = TMA gather4 from x, 1 = plain tiles from a row-gathered copy,
                      // 2 = gathered from x by four LSU warps (cp.async), no pre-pass
     const __nv_bfloat16 *x;   // mode 2: the activation matrix [M, K]
+    int short_boxes; // one-CTA split kernels: row blocks with <= SHORT_ROWS routed rows move only those rows of
+                     // the A operand and of the activation tile (the rest of a 128-row block is padding)
 };
+
+constexpr int SHORT_ROWS = 32;
+constexpr uint32_t SHORT_A_BYTES = SHORT_ROWS * 128;
+
+// routed rows come first in a block, so the block is short when row SHORT_ROWS is already padding
+__device__ __forceinline__ bool block_is_short(const Args &a, int blk, int what = 1) {
+    return (a.short_boxes & what) && a.sorted_ids[blk * BM + SHORT_ROWS] < 0;
+}
 
 __device__ __forceinline__ int num_row_blocks(const Args &a) {
     int npp = *a.npp;
@@ -282,7 +292,8 @@ gather_rows_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restric
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
-                   const __grid_constant__ CUtensorMap map_act, const Args a) {
+                   const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_x_short,
+                   const __grid_constant__ CUtensorMap map_act_short, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, a.stages, ACT_TILE_BYTES);
     int *status = &g_status_bf16;
@@ -334,15 +345,19 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             gather_rows(a, c.m_blk, lane, r);
             const int row_gate = e * a.N + c.n_tile * 128;
             const int row_up = row_gate + a.H;
+            const bool short_a = a.pregathered == 1 && block_is_short(a, c.m_blk);
+            const uint32_t fill_bytes =
+                a.pregathered == 2 ? B_BYTES : (short_a ? B_BYTES + SHORT_A_BYTES : STAGE_BYTES);
             for (int ks = 0; ks < ksteps; ++ks) {
                 if (lane == 0) ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 if (lane == 0) {
-                    mbar_arrive_expect_tx(sm.full(s), a.pregathered == 2 ? B_BYTES : STAGE_BYTES);
+                    mbar_arrive_expect_tx(sm.full(s), fill_bytes);
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
-                    if (a.pregathered == 1) tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BK, c.m_blk * BM);
+                    if (a.pregathered == 1)
+                        tma_load_2d(sm.a(s), short_a ? &map_x_short : &map_x, sm.full(s), ks * BK, c.m_blk * BM);
                     if (a.l2_ahead && ks + a.l2_ahead < ksteps) {
                         tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_gate);
                         tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_up);
@@ -477,8 +492,9 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             mbar_arrive(sm.misc(4));        // staging tile written
             if (et == 0) {
                 if (!mbar_wait(sm.misc(4), it & 1, status, ST_TIMEOUT_ACT)) break;
-                tma_store_2d(&map_act, sm.act, c.n_tile * 128, c.m_blk * BM);
-                tma_store_2d(&map_act, sm.act + ACT_TILE_BYTES / 2, c.n_tile * 128 + 64, c.m_blk * BM);
+                const CUtensorMap *st = block_is_short(a, c.m_blk, 2) ? &map_act_short : &map_act;
+                tma_store_2d(st, sm.act, c.n_tile * 128, c.m_blk * BM);
+                tma_store_2d(st, sm.act + ACT_TILE_BYTES / 2, c.n_tile * 128 + 64, c.m_blk * BM);
                 tma_store_commit();
                 tma_store_wait_read<0>();
                 mbar_arrive(sm.misc(5));
@@ -498,7 +514,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_w2,
-                     const Args a) {
+                     const __grid_constant__ CUtensorMap map_act_short, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, a.stages, a.bulk_reduce ? RED_STAGE_BYTES : 0u);
     int *status = &g_status_bf16;
@@ -542,11 +558,12 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
                 const Coord c = tile_coord(t, m_blocks, n_tiles);
                 const int e = a.expert_ids[c.m_blk];
                 const int w2_row = e * a.K + c.n_tile * 256;
+                const bool short_a = block_is_short(a, c.m_blk);
                 for (int ks = 0; ks < ksteps; ++ks) {
                     ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
-                    tma_load_2d(sm.a(s), &map_act, sm.full(s), ks * BK, c.m_blk * BM);
+                    mbar_arrive_expect_tx(sm.full(s), short_a ? B_BYTES + SHORT_A_BYTES : STAGE_BYTES);
+                    tma_load_2d(sm.a(s), short_a ? &map_act_short : &map_act, sm.full(s), ks * BK, c.m_blk * BM);
                     tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BK, w2_row);
                     if (a.l2_ahead && ks + a.l2_ahead < ksteps) tma_prefetch_l2_2d(&map_w2, (ks + a.l2_ahead) * BK, w2_row);
                     ++issued;
@@ -1209,6 +1226,16 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.w2, static_cast<uint64_t>(p.E) * p.K,
                               H, 256, BK, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
         return rc;
+    CUtensorMap map_x_short = map_x, map_act_short;
+    if (int rc = make_tmap_2d(&map_act_short, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, workspace, p.sorted_num, H,
+                              SHORT_ROWS, BK, CU_TENSOR_MAP_SWIZZLE_128B, "act (short box)"))
+        return rc;
+    if (pregather)
+        if (int rc = make_tmap_2d(&map_x_short, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                  static_cast<__nv_bfloat16 *>(workspace) + static_cast<size_t>(p.sorted_num) * H,
+                                  p.sorted_num, p.K, SHORT_ROWS, BK, CU_TENSOR_MAP_SWIZZLE_128B, "x_sorted (short box)"))
+            return rc;
+    a.short_boxes = short_boxes_mode();
     if (p.bpc == 2) {
         // two-CTA pipeline: always fed from the row-gathered copy; B tiles are loaded as 128-row halves
         CUtensorMap map_w2h;
@@ -1283,7 +1310,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = up.use_pdl ? 1 : 0;
-        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_bf16_kernel, map_x, map_w1, map_act, up));
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_bf16_kernel, map_x, map_w1, map_act, map_x_short, map_act_short, up));
     }
     if (phases & 4) {
         Args dn = a;
@@ -1303,7 +1330,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = dn.use_pdl ? 1 : 0;
-        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_bf16_kernel, map_act, map_w2, dn));
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_bf16_kernel, map_act, map_w2, map_act_short, dn));
     }
     return PMOE_OK;
 }

@@ -74,7 +74,17 @@ struct Args {
     int zero_out;
     int use_pdl;
     int bulk_reduce;   // down kernel: reduce into `out` with cp.reduce.async.bulk from a staging tile
+    int short_boxes;   // split kernels: row blocks with <= SHORT_ROWS routed rows move only those rows of the A
+                       // operand and of the activation tile (the rest of a 128-row block is padding)
 };
+
+constexpr int SHORT_ROWS = 32;
+constexpr uint32_t SHORT_A_BYTES = SHORT_ROWS * BKB;
+
+// routed rows come first in a block, so the block is short when row SHORT_ROWS is already padding
+__device__ __forceinline__ bool block_is_short(const Args &a, int blk, int what = 1) {
+    return (a.short_boxes & what) && a.sorted_ids[blk * BM + SHORT_ROWS] < 0;
+}
 
 struct Smem {
     uint32_t ring, act, bars;
@@ -179,7 +189,8 @@ gather_rows_mxfp8_kernel(const uint8_t *__restrict__ x, const uint8_t *__restric
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(THREADS, 1)
 moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
-                    const __grid_constant__ CUtensorMap map_act, const Args a) {
+                    const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_x_short,
+                    const __grid_constant__ CUtensorMap map_act_short, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, a.stages, ACT_EXTRA);
     int *status = &g_status_mxfp8;
@@ -230,11 +241,12 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const uint8_t *sf_gate = a.w_scales + static_cast<size_t>(row_gate >> 7) * ksteps * SF_TILE;
                 const uint8_t *sf_up = a.w_scales + static_cast<size_t>(row_up >> 7) * ksteps * SF_TILE;
                 const uint8_t *sf_x = a.xsf_tiles + static_cast<size_t>(c.m_blk) * ksteps * SF_TILE;
+                const bool short_a = block_is_short(a, c.m_blk);
                 for (int ks = 0; ks < ksteps; ++ks) {
                     ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(sm.full(s), STAGE_TX_BYTES);
-                    tma_load_2d(sm.a(s), &map_x, sm.full(s), ks * BKB, c.m_blk * BM);
+                    mbar_arrive_expect_tx(sm.full(s), short_a ? STAGE_TX_BYTES - A_BYTES + SHORT_A_BYTES : STAGE_TX_BYTES);
+                    tma_load_2d(sm.a(s), short_a ? &map_x_short : &map_x, sm.full(s), ks * BKB, c.m_blk * BM);
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BKB, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BKB, row_up);
                     bulk_load_1d(sm.sfa(s), sf_x + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
@@ -332,7 +344,8 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             mbar_arrive(sm.misc(2));
             if (et == 0) {
                 if (!mbar_wait(sm.misc(2), it & 1, status, ST_TIMEOUT_ACT)) break;
-                tma_store_2d(&map_act, sm.act, c.n_tile * 128, c.m_blk * BM);
+                tma_store_2d(block_is_short(a, c.m_blk, 2) ? &map_act_short : &map_act, sm.act, c.n_tile * 128,
+                             c.m_blk * BM);
                 tma_store_commit();
                 tma_store_wait_read<0>();
                 mbar_arrive(sm.misc(3));
@@ -351,7 +364,7 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(THREADS, 1)
 moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_w2,
-                      const Args a) {
+                      const __grid_constant__ CUtensorMap map_act_short, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, a.stages, a.bulk_reduce ? RED_STAGE_BYTES : 0u);
     int *status = &g_status_mxfp8;
@@ -396,11 +409,12 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
                 const uint8_t *sf_w0 = a.w2_scales + static_cast<size_t>(w2_row >> 7) * ksteps * SF_TILE;
                 const uint8_t *sf_w1 = sf_w0 + static_cast<size_t>(ksteps) * SF_TILE;
                 const uint8_t *sf_a = a.act_sf + static_cast<size_t>(c.m_blk) * ksteps * SF_TILE;
+                const bool short_a = block_is_short(a, c.m_blk);
                 for (int ks = 0; ks < ksteps; ++ks) {
                     ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(sm.full(s), STAGE_TX_BYTES);
-                    tma_load_2d(sm.a(s), &map_act, sm.full(s), ks * BKB, c.m_blk * BM);
+                    mbar_arrive_expect_tx(sm.full(s), short_a ? STAGE_TX_BYTES - A_BYTES + SHORT_A_BYTES : STAGE_TX_BYTES);
+                    tma_load_2d(sm.a(s), short_a ? &map_act_short : &map_act, sm.full(s), ks * BKB, c.m_blk * BM);
                     tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BKB, w2_row);
                     bulk_load_1d(sm.sfa(s), sf_a + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
                     bulk_load_1d(sm.sfb(s), sf_w0 + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
@@ -857,6 +871,14 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (int rc = make_tmap_2d(&map_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.w2, static_cast<uint64_t>(p.E) * p.K, H,
                               256, BKB, CU_TENSOR_MAP_SWIZZLE_128B, "w2"))
         return rc;
+    CUtensorMap map_x_short, map_act_short;
+    if (int rc = make_tmap_2d(&map_x_short, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x_sorted, p.sorted_num, p.K, SHORT_ROWS,
+                              BKB, CU_TENSOR_MAP_SWIZZLE_128B, "x_sorted (short box)"))
+        return rc;
+    if (int rc = make_tmap_2d(&map_act_short, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, act_q, p.sorted_num, H, SHORT_ROWS,
+                              BKB, CU_TENSOR_MAP_SWIZZLE_128B, "act (short box)"))
+        return rc;
+    a.short_boxes = short_boxes_mode();
 
     if (phases & 1) {
         gather_rows_mxfp8_kernel<<<std::min(4 * sms, (p.sorted_num + 7) / 8), 256, 0, stream>>>(
@@ -917,7 +939,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = up.use_pdl ? 1 : 0;
-        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_mxfp8_kernel, map_x, map_w1, map_act, up));
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_mxfp8_kernel, map_x, map_w1, map_act, map_x_short, map_act_short, up));
     }
     if (phases & 4) {
         Args dn = a;
@@ -938,7 +960,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = dn.use_pdl ? 1 : 0;
-        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_mxfp8_kernel, map_act, map_w2, dn));
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_mxfp8_kernel, map_act, map_w2, map_act_short, dn));
     }
     return PMOE_OK;
 }

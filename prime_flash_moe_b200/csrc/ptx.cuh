@@ -426,7 +426,11 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
-// SwiGLU on fp32 accumulators: up * silu(gate)
-__device__ __forceinline__ float swiglu(float gate, float up) { return up * (gate / (1.f + __expf(-gate))); }
+// SwiGLU on fp32 accumulators: up * silu(gate). The quotient is the approximate division (2 ulp): the IEEE
+// one branches into a slow path when the denominator leaves [2^-126, 2^126], which padding rows (whose
+// accumulators are arbitrary bit patterns) hit all the time - it made the gate/up epilogue several times slower.
+__device__ __forceinline__ float swiglu(float gate, float up) {
+    return up * __fdividef(gate, 1.f + __expf(-gate));
+}
 
 }  // namespace pmoe

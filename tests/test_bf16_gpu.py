@@ -235,3 +235,32 @@ def test_cuda_graph_capture_and_replay(split):
         graph.replay()
         torch.cuda.synchronize()
         assert O.max_rel_to_peak(out.cpu(), ref) <= TOL
+
+
+FEW_ROW_CASES = [
+    (1, 128, 2, 256, 1), (1, 2048, 128, 1536, 8), (16, 2048, 128, 1536, 8),   # decode shapes of the Qwen3 layer
+    (8, 256, 1, 512, 1),
+    (32, 128, 1, 256, 1),     # exactly 32 routed rows in the block: the largest short block
+    (33, 128, 1, 256, 1),     # 33 rows: a full block again
+    (8, 7168, 4, 512, 4),     # long rows (DeepSeek-V3 hidden size)
+    (5, 384, 7, 768, 3),      # K a multiple of 128 only, H = 384
+    (200, 512, 6, 512, 3),    # short and full blocks mixed
+]
+
+
+@pytest.mark.parametrize("T,K,E,N,k", FEW_ROW_CASES)
+def test_short_row_blocks(T, K, E, N, k, monkeypatch):
+    """Row blocks holding at most 32 routed rows load and store only those rows of the A operand and of the
+    activation tile (short TMA boxes); PMOE_SHORT_A=0 moves whole 128-row tiles. Both must meet the oracle bound,
+    and they run the same arithmetic on the routed rows, so their outputs must be identical up to the order of
+    the bf16 reductions into `out`."""
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=3 * T + K)
+    ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
+    monkeypatch.setenv("PMOE_SHORT_A", "3")
+    short = run_mine(x, w1, w2, ids, wts, True)
+    monkeypatch.setenv("PMOE_SHORT_A", "0")
+    full = run_mine(x, w1, w2, ids, wts, True)
+    assert torch.isfinite(short.float()).all()
+    assert O.max_rel_to_peak(short, ref) <= TOL
+    assert O.max_rel_to_peak(full, ref) <= TOL
+    assert O.max_rel_to_peak(short, full.float()) <= TOL / 2

@@ -169,3 +169,23 @@ def test_full_size_properties_qwen3():
     assert O.max_rel_to_peak(a[:64], ref) <= TOL
     b, _ = run_mine(sub_q, ids[:64], wts[:64], False)
     assert O.max_rel_to_peak(b, ref) <= TOL
+
+
+@pytest.mark.parametrize("T,K,E,N,k", [
+    (1, 256, 2, 256, 1), (1, 2048, 128, 1536, 8), (16, 2048, 128, 1536, 8), (8, 256, 1, 512, 1),
+    (32, 256, 1, 256, 1), (33, 256, 1, 256, 1), (8, 7168, 4, 512, 4), (5, 512, 7, 768, 3), (200, 512, 6, 512, 3),
+])
+def test_short_row_blocks(T, K, E, N, k, monkeypatch):
+    """Row blocks holding at most 32 routed rows load and store only those rows of the A operand and of the
+    activation tile (short TMA boxes); PMOE_SHORT_A=0 moves whole 128-row tiles. Both must meet the oracle
+    bound and agree with each other."""
+    q, deq, ids, wts = quantised_case(T, K, E, N, k, seed=3 * T + K)
+    ref = O.moe_ref_fp32(deq["x"], deq["w1"], deq["w2"], ids, wts, requant_act=True)
+    monkeypatch.setenv("PMOE_SHORT_A", "3")
+    short, _ = run_mine(q, ids, wts, True)
+    monkeypatch.setenv("PMOE_SHORT_A", "0")
+    full, _ = run_mine(q, ids, wts, True)
+    assert torch.isfinite(short.float()).all()
+    assert O.max_rel_to_peak(short, ref) <= TOL
+    assert O.max_rel_to_peak(full, ref) <= TOL
+    assert O.max_rel_to_peak(short, full.float()) <= TOL / 2
