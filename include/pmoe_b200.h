@@ -99,7 +99,8 @@ size_t pmoe_moe_align_static_capacity_bytes(void);
  *   block_m == 128; (block_n, warp_n) in {(32,8), (64,4)}; stages 1..5 (<= 4 when split);
  *   bpc in {1, 2} (2 = two-CTA MMA; needs moe_align run with the same bpc); cpc == 1;
  *   K % 128 == 0, N % 256 == 0.
- *   split == 0: one launch, ACCUMULATES into `out` (caller zeroes it).
+ *   split == 0: one GEMM launch (gate/up + down per tile, split-K partials reduced in an fp32 workspace
+ *               buffer) followed by a small launch that ADDS the rounded sums to `out` (caller zeroes it).
  *   split != 0: gate/up kernel -> activation workspace -> down kernel chained by programmatic
  *               dependent launch; `out` is zeroed by the library.
  * `_ws` variant: caller-provided workspace (>= pmoe_fused_moe_bf16_workspace_bytes, 1024-byte
