@@ -129,7 +129,8 @@ int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *w2, void *o
  *   (prime_moe/__init__.py:106-115): 512-byte tiles of 128 rows x 4 scale columns, tile index
  *   row_tile * (K/128) + k_tile, byte (r%32)*16 + (r/32)*4 + (kb%4);
  *   w2 e4m3[E, K, N/2], w2_scales e8m0[E*K*(N/2)/32] blocked likewise; K % 256 == 0, N % 256 == 0,
- *   stages 1..4, bpc == 1. Other arguments as for bf16. */
+ *   stages 1..4; bpc in {1, 2}: 2 = CTA pairs (two-CTA block-scaled MMA; the reference's mxfp8 path rejects it),
+ *   split only, needs moe_align run with bpc = 2 and 16-byte aligned packed scales. Other arguments as for bf16. */
 int pmoe_fused_moe_mxfp8(const void *x, const void *x_scales, const void *w, const void *w_scales,
                          const void *w2, const void *w2_scales, void *out, const int32_t *sorted_token_ids,
                          const int32_t *expert_ids, const int32_t *num_tokens_post_padded,

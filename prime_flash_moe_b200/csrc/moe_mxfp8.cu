@@ -125,6 +125,21 @@ __device__ __forceinline__ void ld32(float *dst, uint32_t taddr) {
     tmem_ld_32x32(*reinterpret_cast<float(*)[32]>(dst), taddr);
 }
 
+// epilogue warps poll and arrive through lane 0 only: 8 pollers / arrivals per barrier instead of 256
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int *status, int code, int lane) {
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(bar, parity, status, code);
+    return __shfl_sync(0xffffffffu, ok, 0);
+}
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
+__device__ __forceinline__ void warp_arrive_cluster(uint32_t cluster_bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(cluster_bar);
+}
+
 // MX block scale of 32 values: returns the biased e8m0 exponent, *inv = 2^(127 - e)
 __device__ __forceinline__ uint32_t mx_block_scale(float amax, float *inv) {
     int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
@@ -205,8 +220,8 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             mbar_init(sm.empty(s), 1);
         }
         mbar_init(sm.misc(0), 1);
-        mbar_init(sm.misc(1), epi_threads);
-        mbar_init(sm.misc(2), epi_threads);
+        mbar_init(sm.misc(1), EPI_WARPS);
+        mbar_init(sm.misc(2), EPI_WARPS);
         mbar_init(sm.misc(3), 1);
         fence_mbar_init();
         tma_prefetch_desc(&map_x);
@@ -307,7 +322,7 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             const Coord c = tile_coord(t, m_blocks, n_tiles);
-            if (!mbar_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            if (!warp_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL, lane)) break;
             tc_fence_after();
             float g[64], u[64];
             ld32(g, tmem_addr(tmem_base, lane_base, cg * 64));
@@ -316,10 +331,10 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             ld32(u + 32, tmem_addr(tmem_base, lane_base, 128 + cg * 64 + 32));
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(sm.misc(1));   // accumulator drained: the next tile's main loop may start
+            warp_arrive(sm.misc(1), lane);   // accumulator drained: the next tile's main loop may start
 #pragma unroll
             for (int i = 0; i < 64; ++i) g[i] = swiglu(g[i], u[i]);
-            if (!mbar_wait(sm.misc(3), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;   // staging tile free
+            if (!warp_wait(sm.misc(3), (it & 1) ^ 1, status, ST_TIMEOUT_ACT, lane)) break;   // staging tile free
             uint8_t *sf_tile = a.act_sf + (static_cast<size_t>(c.m_blk) * n_tiles + c.n_tile) * SF_TILE;
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
@@ -341,15 +356,19 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             }
             fence_proxy_async_smem();
-            mbar_arrive(sm.misc(2));
+            warp_arrive(sm.misc(2), lane);
+            bool stored = true;
             if (et == 0) {
-                if (!mbar_wait(sm.misc(2), it & 1, status, ST_TIMEOUT_ACT)) break;
-                tma_store_2d(block_is_short(a, c.m_blk, 2) ? &map_act_short : &map_act, sm.act, c.n_tile * 128,
-                             c.m_blk * BM);
-                tma_store_commit();
-                tma_store_wait_read<0>();
-                mbar_arrive(sm.misc(3));
+                stored = mbar_wait(sm.misc(2), it & 1, status, ST_TIMEOUT_ACT);
+                if (stored) {
+                    tma_store_2d(block_is_short(a, c.m_blk, 2) ? &map_act_short : &map_act, sm.act, c.n_tile * 128,
+                                 c.m_blk * BM);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                    mbar_arrive(sm.misc(3));
+                }
             }
+            if (!__shfl_sync(0xffffffffu, stored, 0)) break;   // keep the warp together on the error path
         }
         if (et == 0) tma_store_wait<0>();
     }
@@ -369,7 +388,6 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
     const Smem sm = carve(smem_raw, a.stages, a.bulk_reduce ? RED_STAGE_BYTES : 0u);
     int *status = &g_status_mxfp8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int epi_threads = EPI_WARPS * 32;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
@@ -377,7 +395,7 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
             mbar_init(sm.empty(s), 1);
         }
         mbar_init(sm.misc(0), 1);
-        mbar_init(sm.misc(1), epi_threads);
+        mbar_init(sm.misc(1), EPI_WARPS);
         fence_mbar_init();
         tma_prefetch_desc(&map_act);
         tma_prefetch_desc(&map_w2);
@@ -470,14 +488,14 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
             const bool valid = pair >= 0 && tok < a.M;
             const float wgt = valid ? a.topk_weights[pair] : 0.f;
             __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + c.n_tile * 256 + cg * 128;
-            if (!mbar_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            if (!warp_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL, lane)) break;
             tc_fence_after();
             float v[128];
 #pragma unroll
             for (int q = 0; q < 4; ++q) ld32(v + q * 32, tmem_addr(tmem_base, lane_base, cg * 128 + q * 32));
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(sm.misc(1));
+            warp_arrive(sm.misc(1), lane);
             if (a.bulk_reduce) {
                 // scaled bf16 row segment -> this thread's padded staging row -> one 256-byte bulk reduction
                 const uint32_t red_row = sm.act + (threadIdx.x - 64) * RED_ROW_BYTES;
@@ -508,6 +526,285 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair kernels (bpc == 2; no counterpart in the reference, whose mxfp8 path is bpc=1 only): cluster of
+// two CTAs, tcgen05.mma.cta_group::2 with M = 256. A pair owns two consecutive 128-row blocks of one expert
+// (moe_align pads experts to 256 rows when bpc == 2) x one 256-column tile. Per k-step each CTA loads ITS
+// 128 A rows, ITS half of the B tile (gate/up kernel: even CTA the gate rows, odd CTA the up rows; down
+// kernel: 128 of the 256 w2 rows each), its own A scale tile and BOTH B scale tiles (every CTA's tensor
+// memory needs the scales of all 256 B rows): 33.5 KB instead of 49.5 KB, which buys a ring of six slots.
+// All loads are plain TMA tile loads (.cta_group::2 only routes their completion bytes to the even CTA's
+// `full` barrier; the 512-byte scale tiles travel as 1 x 128 boxes of 32-bit words) - no multicast. The even
+// CTA issues the scale copies and MMAs for both; slots and the accumulator are handed back to both CTAs by
+// multicast tcgen05.commit; both CTAs' epilogues arrive on the even CTA's tmem_empty.
+//   misc barriers: 0 tmem_full (each CTA) | 1 tmem_empty (even CTA) | 2 staged | 3 stage_free (up only)
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2 + 2048;          // 34 KB: + SFA, SFB(2), pad
+constexpr uint32_t PAIR_TX_BYTES = A_BYTES + B_BYTES / 2 + 3 * SF_TILE;      // bytes one CTA loads per slot
+constexpr int PAIR_MAX_STAGES = 6;
+constexpr int ST_BAD_PAIR = 8;                                               // the two blocks of a pair differ in expert
+
+struct SmemPair {
+    uint32_t ring, act, bars;
+    __device__ __forceinline__ uint32_t a(int s) const { return ring + s * PAIR_STAGE_BYTES; }
+    __device__ __forceinline__ uint32_t b(int s) const { return ring + s * PAIR_STAGE_BYTES + A_BYTES; }
+    __device__ __forceinline__ uint32_t sfa(int s) const { return ring + s * PAIR_STAGE_BYTES + A_BYTES + B_BYTES / 2; }
+    __device__ __forceinline__ uint32_t sfb(int s) const { return sfa(s) + SF_TILE; }
+    __device__ __forceinline__ uint32_t full(int s) const { return bars + 8 * s; }
+    __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8 * (PAIR_MAX_STAGES + s); }
+    __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * PAIR_MAX_STAGES + i); }
+    __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * PAIR_MAX_STAGES + 8); }
+};
+__device__ __forceinline__ SmemPair carve_pair(const uint8_t *raw, int stages, uint32_t extra) {
+    SmemPair s;
+    s.ring = (smem_u32(raw) + 1023u) & ~1023u;
+    s.act = s.ring + stages * PAIR_STAGE_BYTES;
+    s.bars = s.act + extra;
+    return s;
+}
+size_t smem_bytes_pair(int stages, uint32_t extra) {
+    return 1024 + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + extra + BAR_BYTES;
+}
+
+template <bool kUp>
+__global__ void __launch_bounds__(THREADS, 1)
+moe_pair_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                      const __grid_constant__ CUtensorMap map_act, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const SmemPair sm = carve_pair(smem_raw, a.stages, kUp ? ACT_EXTRA : (a.bulk_reduce ? RED_STAGE_BYTES : 0u));
+    int *status = &g_status_mxfp8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int epi_threads = EPI_WARPS * 32;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (kUp) pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), 2 * EPI_WARPS);
+        mbar_init(sm.misc(2), EPI_WARPS);
+        mbar_init(sm.misc(3), 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        tma_prefetch_desc(&map_sfa);
+        tma_prefetch_desc(&map_sfb);
+        if (kUp) tma_prefetch_desc(&map_act);
+    }
+    if (warp == 1) tmem_alloc_pair(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // both CTAs' barriers are initialised and both halves of TMEM allocated
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (a.use_pdl) pdl_wait_primary();   // up: after the row-gather kernel; down: after the gate/up kernel
+
+    const int m_pairs = live_row_blocks(a.npp, a.sorted_num) / 2;
+    const int n_tiles = kUp ? a.H / 128 : a.K / 256;
+    const int num_tiles = m_pairs * n_tiles;
+    const int ksteps = (kUp ? a.K : a.H) / BKB;
+    const int first = blockIdx.x >> 1, step = gridDim.x >> 1;   // this pair's tile sequence
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = first; t < num_tiles && ok; t += step) {
+                const Coord c = tile_coord(t, m_pairs, n_tiles);
+                const int blk = 2 * c.m_blk + static_cast<int>(rank);
+                const int e = a.expert_ids[2 * c.m_blk];
+                if (leader && a.expert_ids[2 * c.m_blk + 1] != e) atomicCAS(status, 0, ST_BAD_PAIR);
+                int b_row, sfb0, sfb1;   // B rows of this CTA; scale-tile rows of the two 128-row halves of B
+                if (kUp) {
+                    const int row_gate = e * a.N + c.n_tile * 128;
+                    b_row = row_gate + (leader ? 0 : a.H);
+                    sfb0 = (row_gate >> 7) * ksteps;
+                    sfb1 = ((row_gate + a.H) >> 7) * ksteps;
+                } else {
+                    const int w2_row = e * a.K + c.n_tile * 256;
+                    b_row = w2_row + static_cast<int>(rank) * 128;
+                    sfb0 = (w2_row >> 7) * ksteps;
+                    sfb1 = sfb0 + ksteps;
+                }
+                const int sfa0 = blk * ksteps;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait_cluster(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    const uint32_t full_leader = mapa_shared(sm.full(s), 0);
+                    if (leader) mbar_arrive_expect_tx(sm.full(s), 2 * PAIR_TX_BYTES);
+                    tma_load_2d_pair(sm.a(s), &map_a, full_leader, ks * BKB, blk * BM);
+                    tma_load_2d_pair(sm.b(s), &map_b, full_leader, ks * BKB, b_row);
+                    tma_load_2d_pair(sm.sfa(s), &map_sfa, full_leader, 0, sfa0 + ks);
+                    tma_load_2d_pair(sm.sfb(s), &map_sfb, full_leader, 0, sfb0 + ks);
+                    tma_load_2d_pair(sm.sfb(s) + SF_TILE, &map_sfb, full_leader, 0, sfb1 + ks);
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = idesc_mxf8_f32(256, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            long long fill = 0;
+            bool ok = true;
+            for (int t = first; t < num_tiles && ok; t += step, ++it) {
+                ok = mbar_wait_cluster(sm.misc(1), (it & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int ks = 0; ks < ksteps; ++ks, ++fill) {
+                    ok = mbar_wait_cluster(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sfa_t = tmem_base + SF_TMEM_BASE + 16u * static_cast<uint32_t>(fill & 7);
+                    const uint32_t sfb_t = sfa_t + 4;
+                    tmem_cp_sf_32x128b_warpx4_pair(sfa_t, smem_desc_sf(sm.sfa(s)));
+                    tmem_cp_sf_32x128b_warpx4_pair(sfb_t, smem_desc_sf(sm.sfb(s)));
+                    tmem_cp_sf_32x128b_warpx4_pair(sfb_t + 4, smem_desc_sf(sm.sfb(s) + SF_TILE));
+#pragma unroll
+                    for (uint32_t kb = 0; kb < 4; ++kb)
+                        umma_mxf8_pair(tmem_base, smem_desc_sw128(sm.a(s) + kb * 32), smem_desc_sw128(sm.b(s) + kb * 32),
+                                       idesc_with_sf_ids(idesc, kb, kb), sfa_t, sfb_t, (ks | kb) != 0 ? 1u : 0u);
+                    umma_commit_pair(sm.empty(s), 3);
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit_pair(sm.misc(0), 3);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const int et = threadIdx.x - 64;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int cg = ew >> 2;
+        const uint32_t empty_leader = mapa_shared(sm.misc(1), 0);
+        if (kUp && a.zero_out) {
+            int4 *o4 = reinterpret_cast<int4 *>(a.out);
+            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const int4 z = make_int4(0, 0, 0, 0);
+            for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
+                 i += static_cast<long long>(gridDim.x) * epi_threads)
+                o4[i] = z;
+        }
+        int it = 0;
+        for (int t = first; t < num_tiles; t += step, ++it) {
+            const Coord c = tile_coord(t, m_pairs, n_tiles);
+            const int blk = 2 * c.m_blk + static_cast<int>(rank);
+            if (kUp) {
+                // cg 0: activation columns [0,64), cg 1: [64,128) of this CTA's 128 rows
+                if (!warp_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL, lane)) break;
+                tc_fence_after();
+                float g[64], u[64];
+                ld32(g, tmem_addr(tmem_base, lane_base, cg * 64));
+                ld32(g + 32, tmem_addr(tmem_base, lane_base, cg * 64 + 32));
+                ld32(u, tmem_addr(tmem_base, lane_base, 128 + cg * 64));
+                ld32(u + 32, tmem_addr(tmem_base, lane_base, 128 + cg * 64 + 32));
+                tmem_ld_wait();
+                tc_fence_before();
+                warp_arrive_cluster(empty_leader, lane);   // accumulator drained: the next tile's main loop may start
+#pragma unroll
+                for (int i = 0; i < 64; ++i) g[i] = swiglu(g[i], u[i]);
+                if (!warp_wait(sm.misc(3), (it & 1) ^ 1, status, ST_TIMEOUT_ACT, lane)) break;   // staging tile free
+                uint8_t *sf_tile = a.act_sf + (static_cast<size_t>(blk) * n_tiles + c.n_tile) * SF_TILE;
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    float amax = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(g[q * 32 + i]));
+                    float inv;
+                    const uint32_t e = mx_block_scale(amax, &inv);
+                    sf_tile[(row & 31) * 16 + (row >> 5) * 4 + cg * 2 + q] = static_cast<uint8_t>(e);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float *v = g + q * 32 + j * 16;
+                        const uint32_t chunk16 = static_cast<uint32_t>(cg * 4 + q * 2 + j);
+                        st_shared_v4(sm.act + row * 128 + ((chunk16 ^ (row & 7)) << 4),
+                                     pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                                     pack_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv),
+                                     pack_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv),
+                                     pack_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv));
+                    }
+                }
+                fence_proxy_async_smem();
+                warp_arrive(sm.misc(2), lane);
+                bool stored = true;
+                if (et == 0) {
+                    stored = mbar_wait(sm.misc(2), it & 1, status, ST_TIMEOUT_ACT);
+                    if (stored) {
+                        tma_store_2d(&map_act, sm.act, c.n_tile * 128, blk * BM);
+                        tma_store_commit();
+                        tma_store_wait_read<0>();
+                        mbar_arrive(sm.misc(3));
+                    }
+                }
+                if (!__shfl_sync(0xffffffffu, stored, 0)) break;   // keep the warp together on the error path
+            } else {
+                // cg selects output columns [cg*128, cg*128+128) of the 256-wide tile
+                const int pair = a.sorted_ids[blk * BM + row];
+                const int tok = pair >= 0 ? pair / a.top_k : 0;
+                const bool valid = pair >= 0 && tok < a.M;
+                const float wgt = valid ? a.topk_weights[pair] : 0.f;
+                __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + c.n_tile * 256 + cg * 128;
+                if (!warp_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL, lane)) break;
+                tc_fence_after();
+                float v[128];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) ld32(v + q * 32, tmem_addr(tmem_base, lane_base, cg * 128 + q * 32));
+                tmem_ld_wait();
+                tc_fence_before();
+                warp_arrive_cluster(empty_leader, lane);
+                if (a.bulk_reduce) {
+                    const uint32_t red_row = sm.act + (threadIdx.x - 64) * RED_ROW_BYTES;
+                    tma_store_wait_read<0>();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        st_shared_v4(red_row + j * 16, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                                     pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                                     pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                                     pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
+                    fence_proxy_async_smem();
+                    if (valid) bulk_reduce_add_bf16(dst, red_row, 256);
+                    tma_store_commit();
+                    continue;
+                }
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        red_add_bf16x8(dst + j * 8, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                                       pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                                       pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                                       pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
+                }
+            }
+        }
+        if (kUp && et == 0) tma_store_wait<0>();
+        if (!kUp && a.bulk_reduce) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // nobody frees TMEM or exits while the peer may still use this CTA's memory
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -781,8 +1078,10 @@ int validate(const Problem &p, int block_m) {
     PMOE_REQUIRE((p.block_n == 64 && p.warp_n == 4) || (p.block_n == 32 && p.warp_n == 8), PMOE_ERR_UNSUPPORTED,
                  "(block_n, warp_n) must be (64, 4) or (32, 8)");
     PMOE_REQUIRE(p.stages > 0 && p.stages < 5, PMOE_ERR_UNSUPPORTED, "mxfp8 supports stages in 1..4");
-    PMOE_REQUIRE(p.bpc == 1, PMOE_ERR_UNSUPPORTED,
-                 "mxfp8 supports bpc=1 only: tensor memory has no room for a second accumulator plus scale factors");
+    PMOE_REQUIRE(p.bpc == 1 || p.bpc == 2, PMOE_ERR_UNSUPPORTED, "bpc must be 1 or 2");
+    PMOE_REQUIRE(p.bpc == 1 || p.split, PMOE_ERR_UNSUPPORTED, "bpc=2 (two-CTA MMA) requires split=True");
+    PMOE_REQUIRE(p.bpc == 1 || p.sorted_num % 256 == 0, PMOE_ERR_BAD_ARG,
+                 "bpc=2 requires routing tables built by moe_align with bpc=2 (rows padded to 256)");
     PMOE_REQUIRE(block_m == 128, PMOE_ERR_UNSUPPORTED, "Blackwell tcgen05 fused MoE requires block_m=128.");
     PMOE_REQUIRE(p.sorted_num % 128 == 0, PMOE_ERR_BAD_ARG, "sorted_num must be a multiple of block_m");
     PMOE_REQUIRE(static_cast<long long>(p.E) * p.N < (1ll << 31) && static_cast<long long>(p.E) * p.K < (1ll << 31),
@@ -920,6 +1219,78 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         cfg.numAttrs = use_pdl ? 1 : 0;
         PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, finalize_acc32_mxfp8_kernel, static_cast<const float *>(a.acc32), a.out,
                                         static_cast<long long>(elems / 8), use_pdl));
+        return PMOE_OK;
+    }
+    if (p.bpc == 2) {
+        // CTA pairs: B tiles travel as 128-row halves, the 512-byte scale tiles as rows of 128 32-bit words
+        CUtensorMap map_w2h, sf_x, sf_w1, sf_act, sf_w2;
+        if (int rc = make_tmap_2d(&map_w2h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.w2, static_cast<uint64_t>(p.E) * p.K,
+                                  H, 128, BKB, CU_TENSOR_MAP_SWIZZLE_128B, "w2 (half tiles)"))
+            return rc;
+        const uint64_t kt = p.K / 128, ht = H / 128;
+        if (int rc = make_tmap_2d(&sf_x, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, xsf, max_blocks * kt, 128, 1, 128,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE, "x scale tiles"))
+            return rc;
+        if (int rc = make_tmap_2d(&sf_w1, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.w_scales,
+                                  static_cast<uint64_t>(p.E) * p.N / 128 * kt, 128, 1, 128, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  "w scale tiles"))
+            return rc;
+        if (int rc = make_tmap_2d(&sf_act, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, act_sf, max_blocks * ht, 128, 1, 128,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE, "activation scale tiles"))
+            return rc;
+        if (int rc = make_tmap_2d(&sf_w2, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.w2_scales,
+                                  static_cast<uint64_t>(p.E) * p.K / 128 * ht, 128, 1, 128, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  "w2 scale tiles"))
+            return rc;
+        PMOE_REQUIRE((reinterpret_cast<uintptr_t>(p.w_scales) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.w2_scales) & 15) == 0,
+                     PMOE_ERR_BAD_ARG, "fused_moe_mxfp8: packed scales must be 16-byte aligned");
+        Args pa = a;
+        pa.stages = std::min(PAIR_MAX_STAGES, (a.stages * 3 + 1) / 2);   // same ring bytes as the 1-CTA kernels
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        auto launch_pair = [&](auto kernel, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &msa,
+                               const CUtensorMap &msb, const Args &args, int tiles, uint32_t extra, int nattr) -> int {
+            const size_t smem = smem_bytes_pair(args.stages, extra);
+            if (int rc = set_smem(kernel, smem)) return rc;
+            PMOE_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
+            cudaLaunchConfig_t cfg = {};
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cfg.attrs = attr;
+            cfg.numAttrs = nattr;
+            cfg.gridDim = dim3(2);
+            int max_clusters = 0;
+            PMOE_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg));
+            if (max_clusters < 1) return set_error(PMOE_ERR_CUDA, "no CTA pair of the bpc=2 kernel fits on this device");
+            cfg.gridDim = dim3(2 * std::min(tiles, max_clusters));
+            PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, msa, msb, map_act, args));
+            return PMOE_OK;
+        };
+        if (phases & 2) {
+            Args up = pa;
+            up.zero_out = 1;
+            up.use_pdl = (pdl_enabled() && (phases & 1)) ? 1 : 0;
+            if (int rc = launch_pair(moe_pair_mxfp8_kernel<true>, map_x, map_w1, sf_x, sf_w1, up,
+                                     (max_blocks / 2) * (H / 128), ACT_EXTRA, up.use_pdl ? 2 : 1))
+                return rc;
+        }
+        if (phases & 4) {
+            Args dn = pa;
+            dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
+            const int bulk = down_bulk_reduce_mode();
+            dn.bulk_reduce = (bulk < 0 ? (H <= 1024) : bulk != 0) ? 1 : 0;
+            if (dn.bulk_reduce) dn.stages = std::min(dn.stages, 4);   // room for the reduction staging tile
+            if (int rc = launch_pair(moe_pair_mxfp8_kernel<false>, map_act, map_w2h, sf_act, sf_w2, dn,
+                                     (max_blocks / 2) * (p.K / 256), dn.bulk_reduce ? RED_STAGE_BYTES : 0u,
+                                     dn.use_pdl ? 2 : 1))
+                return rc;
+        }
         return PMOE_OK;
     }
     if (phases & 2) {

@@ -65,8 +65,9 @@ class LocalExperts:
         self.w1, self.w2, self.w1_scales, self.w2_scales = w1, w2, w1_scales, w2_scales
         self.stages, self.split = stages, split
         self.num_local = w1.shape[0]
-        # CTA pairs (bpc=2) for the bf16 split pipeline unless told otherwise; mxfp8 supports bpc=1 only
-        self.bpc = bpc if bpc else (2 if (w1_scales is None and split) else 1)
+        # CTA pairs (bpc=2) for the bf16 split pipeline on wide layers unless told otherwise: narrow layers are
+        # faster on the one-CTA kernels (in-kernel row gather, less padding), and so is mxfp8
+        self.bpc = bpc if bpc else (2 if (w1_scales is None and split and w1.shape[1] >= 8192) else 1)
 
     def __call__(self, rows: torch.Tensor, local_expert: torch.Tensor, row_scales: Optional[torch.Tensor] = None):
         if not rows.is_cuda:
@@ -83,7 +84,7 @@ class LocalExperts:
                                self.split)
         else:
             ops.fused_moe_mxfp8(rows, row_scales, self.w1, self.w1_scales, self.w2, self.w2_scales, s, e, n, ones, out,
-                                1, 128, 64, 4, self.stages, 1, self.split)
+                                1, 128, 64, 4, self.stages, self.bpc, self.split)
         return out
 
 

@@ -170,7 +170,8 @@ def test_full_size_properties_mixtral():
     a = run_mine(x, w1, w2, ids, wts, True)
     assert torch.isfinite(a.float()).all()
     sub = run_mine(x[:64], w1, w2, ids[:64], wts[:64], True)
-    assert O.max_rel_to_peak(sub, a[:64]) <= 1e-2
+    # same arithmetic per routed row; the bf16 reductions into an output element land in a different order
+    assert O.max_rel_to_peak(sub, a[:64]) <= TOL
     # CPU oracle on the same 64 tokens (bounded work: 64 tokens x 2 experts each)
     ref = O.moe_ref_fp32(x[:64].cpu(), w1.cpu(), w2.cpu(), ids[:64], wts[:64])
     assert O.max_rel_to_peak(a[:64], ref) <= TOL
