@@ -497,6 +497,9 @@ def run_gpu_arm(args, impl):
                         "sample": f"first {sample} of {T} tokens of the same batch, torch CPU grouped_mm oracle, "
                                   f"{secs:.2f} s", "host_cpus": os.cpu_count()}
 
+    if ep_mode:
+        # kernels of this package per step: plan (3) + moe_align (1 or 3) + row gather, gate/up, down (3) + combine (1)
+        launches_per_step = 3 + (3 if (ep_rows[-1] if ep_rows else 0) * k > 4096 else 1) + 3 + 1
     if rank == 0:
         line = {
             "metric": "moe_ffn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": ref_world, "steps": args.steps,
@@ -513,7 +516,9 @@ def run_gpu_arm(args, impl):
         }
         if ep_mode:
             line["config"]["ep"] = {"rows_computed_by_rank0_last_step": ep_rows[-1] if ep_rows else None,
-                                    "tokens_per_rank": T, "collective": "NCCL all-to-all (dispatch + combine)"}
+                                    "rows_sent_by_rank0_last_step": layer.last_sent_rows, "routes_per_rank": T * k,
+                                    "tokens_per_rank": T,
+                                    "collective": "NCCL all-to-all (dispatch + combine), one row per (token, rank) visit"}
         if impl == "reference":
             line["impl"] = "reference"
             line["gpu_launches"] = None

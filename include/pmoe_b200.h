@@ -147,12 +147,27 @@ int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, 
                             size_t workspace_bytes, pmoe_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Expert-parallel combine (no counterpart in the reference, which is single-GPU): after the combine
- * all-to-all, pair p's expert output is row slot_of_pair[p] of y (bf16 [P, K], P = T*top_k);
- * out[t, :] = bf16(sum_j weights[t*top_k + j] * y[slot_of_pair[t*top_k + j], :]), fp32 accumulation.
- * K % 8 == 0; y and out 16-byte aligned. */
-int pmoe_ep_combine(const void *y, const int64_t *slot_of_pair, const float *weights, void *out, int T,
-                    int top_k, int K, pmoe_stream_t stream);
+ * Expert-parallel glue (no counterpart in the reference, which is single-GPU). Experts are sharded
+ * contiguously over `world` ranks (num_experts / world each). The unit of exchange is a VISIT: a (token,
+ * destination rank) pair such that at least one of the token's top_k experts lives on that rank.
+ *
+ * pmoe_ep_plan: from this rank's topk_ids int32[T, top_k] and topk_weights fp32[T, top_k] writes
+ *   counts int32[world]           visits per destination rank; V = their sum (<= T * min(top_k, world))
+ *   visit_token int32[V]          token of each visit; visits ordered by destination rank, tokens ascending
+ *   visit_meta int32[V, 2*top_k]  per visit: top_k local expert ids (-1 where the route goes elsewhere), then
+ *                                 the top_k routing weights as fp32 bit patterns (0 where it goes elsewhere)
+ *   slot_of int32[T, world]       visit index of (token, rank), -1 if the token does not visit that rank
+ * The arrays are sized by the caller for the upper bound of V. Ids outside [0, num_experts) are ignored.
+ * workspace: pmoe_ep_plan_workspace_bytes(T, world) bytes, 4-byte aligned. world <= 32.
+ *
+ * pmoe_ep_combine: after the return exchange, y bf16[V, K] holds one row per visit (the weighted partial sum
+ * over the visited rank's experts); out[t, :] = bf16(sum over g with slot_of[t, g] >= 0 of y[slot_of[t, g], :]),
+ * fp32 accumulation. K % 8 == 0; y and out 16-byte aligned. */
+size_t pmoe_ep_plan_workspace_bytes(int T, int world);
+int pmoe_ep_plan(const int32_t *topk_ids, const float *topk_weights, int T, int top_k, int num_experts, int world,
+                 int32_t *counts, int32_t *visit_token, int32_t *visit_meta, int32_t *slot_of, void *workspace,
+                 size_t workspace_bytes, pmoe_stream_t stream);
+int pmoe_ep_combine(const void *y, const int32_t *slot_of, void *out, int T, int world, int K, pmoe_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Device status. Every wait inside the kernels is bounded; a wait that expires records a code in a

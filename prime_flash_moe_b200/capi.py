@@ -30,7 +30,9 @@ SIGNATURES = {
     "pmoe_fused_moe_mxfp8": (_i, [_vp] * 11 + [_i] * 12 + [_vp]),
     "pmoe_fused_moe_mxfp8_workspace_bytes": (_sz, [_i] * 5),
     "pmoe_fused_moe_mxfp8_ws": (_i, [_vp] * 11 + [_i] * 12 + [_vp, _sz, _vp]),
-    "pmoe_ep_combine": (_i, [_vp] * 4 + [_i] * 3 + [_vp]),
+    "pmoe_ep_plan_workspace_bytes": (C.c_size_t, [_i, _i]),
+    "pmoe_ep_plan": (_i, [_vp] * 2 + [_i] * 4 + [_vp] * 5 + [C.c_size_t, _vp]),
+    "pmoe_ep_combine": (_i, [_vp] * 3 + [_i] * 3 + [_vp]),
     "pmoe_device_status": (_i, [C.POINTER(_i)]),
     "pmoe_reset_device_status": (_i, []),
     "pmoe_debug_set_phase_mask": (_i, [_i]),

@@ -180,28 +180,58 @@ void fused_moe_mxfp8(const torch::Tensor &x, const torch::Tensor &x_scales, cons
         split ? 1 : 0, ws_ptr, ws_bytes, stream));
 }
 
-// expert-parallel combine: out[t] = sum_j weights[t, j] * y[slots[t, j]] (not in the reference)
-torch::Tensor ep_combine(const torch::Tensor &y, const torch::Tensor &slots, const torch::Tensor &weights,
-                         int64_t top_k) {
+// expert-parallel plan (not in the reference): visits (token, destination rank) ordered by rank, see pmoe_ep_plan.
+// Returns (counts[world], visit_token[Vmax], visit_meta[Vmax, 2*top_k], slot_of[T, world]), all int32;
+// only the first sum(counts) visits are meaningful.
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> ep_plan(const torch::Tensor &topk_ids,
+                                                                               const torch::Tensor &topk_weights,
+                                                                               int64_t num_experts, int64_t world) {
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    at::cuda::OptionalCUDAGuard guard{device_of(topk_ids)};
+    TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous() && topk_ids.dtype() == torch::kInt32,
+                "topk_ids must be a contiguous int32 [T, top_k] tensor");
+    TORCH_CHECK(topk_weights.is_contiguous() && topk_weights.dtype() == torch::kFloat32 &&
+                    topk_weights.numel() == topk_ids.numel(),
+                "topk_weights must be contiguous fp32 with one weight per route");
+    TORCH_CHECK(world > 0 && num_experts > 0);
+    const int64_t T = topk_ids.size(0), top_k = topk_ids.size(1);
+    const int64_t vmax = T * std::min<int64_t>(top_k, world);
+    auto opts = topk_ids.options();
+    torch::Tensor counts = torch::empty({world}, opts);
+    torch::Tensor visit_token = torch::empty({vmax}, opts);
+    torch::Tensor visit_meta = torch::empty({vmax, 2 * top_k}, opts);
+    torch::Tensor slot_of = torch::empty({T, world}, opts);
+    const size_t ws_bytes = pmoe_ep_plan_workspace_bytes(static_cast<int>(T), static_cast<int>(world));
+    torch::Tensor ws = torch::empty({static_cast<int64_t>(ws_bytes / 4) + 1}, opts);
+    check_status(pmoe_ep_plan(static_cast<const int32_t *>(topk_ids.const_data_ptr()),
+                              static_cast<const float *>(topk_weights.const_data_ptr()), static_cast<int>(T),
+                              static_cast<int>(top_k), static_cast<int>(num_experts), static_cast<int>(world),
+                              static_cast<int32_t *>(counts.data_ptr()), static_cast<int32_t *>(visit_token.data_ptr()),
+                              static_cast<int32_t *>(visit_meta.data_ptr()), static_cast<int32_t *>(slot_of.data_ptr()),
+                              ws.data_ptr(), ws_bytes, stream));
+    return {counts, visit_token, visit_meta, slot_of};
+}
+
+// expert-parallel combine: out[t] = sum over the token's visits of y[slot_of[t, g]] (not in the reference)
+torch::Tensor ep_combine(const torch::Tensor &y, const torch::Tensor &slot_of) {
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     at::cuda::OptionalCUDAGuard guard{device_of(y)};
     TORCH_CHECK(y.dim() == 2 && y.is_contiguous() && y.dtype() == torch::kBFloat16);
-    TORCH_CHECK(slots.is_contiguous() && slots.dtype() == torch::kInt64);
-    TORCH_CHECK(weights.is_contiguous() && weights.dtype() == torch::kFloat32);
-    TORCH_CHECK(top_k > 0 && slots.numel() == weights.numel() && slots.numel() % top_k == 0);
-    TORCH_CHECK(slots.numel() <= y.size(0), "every pair needs a row of y");
-    const int64_t T = slots.numel() / top_k, K = y.size(1);
+    TORCH_CHECK(slot_of.dim() == 2 && slot_of.is_contiguous() && slot_of.dtype() == torch::kInt32);
+    const int64_t T = slot_of.size(0), world = slot_of.size(1), K = y.size(1);
     torch::Tensor out = torch::empty({T, K}, y.options());
-    check_status(pmoe_ep_combine(y.const_data_ptr(), static_cast<const int64_t *>(slots.const_data_ptr()),
-                                 static_cast<const float *>(weights.const_data_ptr()), out.data_ptr(),
-                                 static_cast<int>(T), static_cast<int>(top_k), static_cast<int>(K), stream));
+    check_status(pmoe_ep_combine(y.const_data_ptr(), static_cast<const int32_t *>(slot_of.const_data_ptr()),
+                                 out.data_ptr(), static_cast<int>(T), static_cast<int>(world), static_cast<int>(K),
+                                 stream));
     return out;
 }
 
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(prime_moe, m) {
-    m.def("ep_combine(Tensor y, Tensor slots, Tensor weights, int top_k) -> Tensor");
+    m.def("ep_plan(Tensor topk_ids, Tensor topk_weights, int num_experts, int world) -> (Tensor, Tensor, Tensor, Tensor)");
+    m.impl("ep_plan", torch::kCUDA, &ep_plan);
+    m.def("ep_combine(Tensor y, Tensor slot_of) -> Tensor");
     m.impl("ep_combine", torch::kCUDA, &ep_combine);
     m.def(
         "fused_moe_bf16(Tensor x, Tensor w, Tensor w2, Tensor sorted_token_ids, Tensor expert_ids, "

@@ -2,21 +2,25 @@
 
 Not in the reference (single GPU, single process). One process per GPU; rank ``r`` of ``G`` holds the
 contiguous experts ``[r*E/G, (r+1)*E/G)`` (weights and packed scales resident), tokens are data-parallel.
-One step:
+The unit of exchange is a VISIT: a (token, destination rank) pair such that at least one of the token's
+``top_k`` experts lives on that rank - a token row crosses NVLink once per visited rank, not once per route
+(``top_k=8`` over 8 ranks: 5.25 visits per token on average instead of 8 rows). One step:
 
-1. every (token, route) pair is assigned to the rank owning its expert; pairs are ordered by destination
-   rank (stable), the per-destination counts are exchanged (all-to-all of ``G`` integers);
-2. **dispatch**: one all-to-all of the routed rows of ``x`` (bf16 rows of ``2K`` bytes, or e4m3 rows of ``K``
-   bytes plus ``K/32`` scale bytes) and one of their local expert ids - NCCL over NVLink, rows land in
-   the receiver's own HBM before any kernel reads them (no remote loads, no TMA multicast anywhere);
-3. local compute: ``moe_align`` on the received local expert ids (one route per received row) and the
-   fused MoE FFN kernels of this package on the ``E/G`` local experts, routing weight 1;
-4. **combine**: the reverse all-to-all of the bf16 result rows, then each token's ``top_k`` rows are summed
-   with its fp32 routing weights at the source rank.
+1. **plan** (``pmoe_ep_plan`` on the GPU): visits ordered by destination rank, per visit the token, ``top_k``
+   slots of (local expert id or -1, routing weight or 0), per rank the visit count; the counts are
+   exchanged (all-to-all of ``G`` integers) - the one host sync of the step, NCCL needs split sizes;
+2. **dispatch**: one all-to-all of the visiting rows of ``x`` (bf16 rows of ``2K`` bytes, or e4m3 rows of ``K``
+   bytes plus ``K/32`` scale bytes) and one of their slot tables - NCCL over NVLink, rows land in the
+   receiver's own HBM before any kernel reads them (no remote loads, no TMA multicast anywhere);
+3. local compute: ``moe_align`` on the received slot tables (ids of -1 are ignored) and the fused MoE FFN
+   kernels of this package on the ``E/G`` local experts with the received routing weights, so the result
+   is ONE row per visit: the weighted partial sum over this rank's experts;
+4. **combine**: the reverse all-to-all of the bf16 partial sums, then each token's visits are added in fp32 at
+   the source rank (``pmoe_ep_combine``).
 
-The index arithmetic (steps 1, 2, 4) is plain, device-agnostic torch and runs unchanged on CPU tensors
-over ``gloo``; the expert compute is a callable, by default the CUDA kernels (``LocalExperts``), which
-raises without a GPU - there is no CPU implementation of the kernels in this package.
+The plan has a plain, device-agnostic torch version used for CPU tensors (ranks over ``gloo`` in the tests)
+and as the checker of the CUDA one; the expert compute is a callable, by default the CUDA kernels
+(``LocalExperts``), which raises without a GPU - there is no CPU implementation of the kernels in this package.
 """
 from __future__ import annotations
 
@@ -29,25 +33,49 @@ import torch.distributed as dist
 
 @dataclass
 class DispatchPlan:
-    """Where every (token, route) pair goes. ``perm[i]`` is the pair id sent in slot ``i`` (slots ordered by
-    destination rank, pairs in ascending id inside a destination); ``send_counts[g]`` pairs go to rank g."""
-    perm: torch.Tensor
-    tokens: torch.Tensor          # token of each send slot
-    local_expert: torch.Tensor    # expert index on the destination rank, int32
-    send_counts: torch.Tensor     # int64 [G]
+    """Visits of this rank's tokens, ordered by destination rank, tokens ascending inside a rank. Only the first
+    ``sum(counts)`` entries of ``visit_token`` / ``visit_meta`` are meaningful."""
+    counts: torch.Tensor        # int32 [G]: visits per destination rank
+    visit_token: torch.Tensor   # int32 [>= V]: token of each visit
+    visit_meta: torch.Tensor    # int32 [>= V, 2*top_k]: local expert ids (-1 = elsewhere) | fp32 weight bits
+    slot_of: torch.Tensor       # int32 [T, G]: visit index of (token, rank) or -1
 
 
-def make_dispatch_plan(topk_ids: torch.Tensor, num_experts: int, world_size: int) -> DispatchPlan:
+def make_dispatch_plan_torch(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int,
+                             world_size: int) -> DispatchPlan:
+    """Reference construction of the plan with torch ops (any device; synchronises on ``nonzero``)."""
     assert num_experts % world_size == 0, "experts must divide evenly over the ranks"
     per_rank = num_experts // world_size
-    top_k = topk_ids.shape[1]
-    flat = topk_ids.reshape(-1).to(torch.int64)
-    dest = torch.div(flat, per_rank, rounding_mode="floor")
-    perm = torch.argsort(dest, stable=True)
-    send_counts = torch.bincount(dest, minlength=world_size)
-    return DispatchPlan(perm=perm, tokens=torch.div(perm, top_k, rounding_mode="floor"),
-                        local_expert=(flat[perm] - dest[perm] * per_rank).to(torch.int32),
-                        send_counts=send_counts)
+    T, top_k = topk_ids.shape
+    ids = topk_ids.to(torch.int64)
+    valid = (ids >= 0) & (ids < num_experts)
+    dest = torch.where(valid, torch.div(ids, per_rank, rounding_mode="floor"), torch.zeros_like(ids))
+    flags = torch.zeros(T, world_size, dtype=torch.int32, device=ids.device)
+    flags.scatter_add_(1, dest, valid.to(torch.int32))
+    flags = flags > 0
+    gt = torch.nonzero(flags.t().contiguous().view(-1)).view(-1)           # rank-major, tokens ascending
+    g, t = torch.div(gt, max(T, 1), rounding_mode="floor"), gt % max(T, 1)
+    here = valid[t] & (dest[t] == g.view(-1, 1))                           # [V, top_k]
+    local = torch.where(here, ids[t] - g.view(-1, 1) * per_rank, torch.full_like(ids[t], -1)).to(torch.int32)
+    w = torch.where(here, topk_weights.view(T, top_k).float()[t], torch.zeros((), device=ids.device))
+    meta = torch.cat([local, w.contiguous().view(torch.int32)], dim=1).contiguous()
+    slot_of = torch.full((T, world_size), -1, dtype=torch.int32, device=ids.device)
+    slot_of[t, g] = torch.arange(gt.numel(), dtype=torch.int32, device=ids.device)
+    return DispatchPlan(counts=flags.sum(0).to(torch.int32), visit_token=t.to(torch.int32), visit_meta=meta,
+                        slot_of=slot_of)
+
+
+def make_dispatch_plan(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int,
+                       world_size: int) -> DispatchPlan:
+    """The plan of one step: three small kernels on a GPU (no host sync), torch ops on CPU tensors."""
+    assert num_experts % world_size == 0, "experts must divide evenly over the ranks"
+    if not topk_ids.is_cuda:
+        return make_dispatch_plan_torch(topk_ids, topk_weights, num_experts, world_size)
+    T, top_k = topk_ids.shape
+    counts, visit_token, visit_meta, slot_of = torch.ops.prime_moe.ep_plan(
+        topk_ids.to(torch.int32).contiguous(), topk_weights.reshape(T, top_k).float().contiguous(), num_experts,
+        world_size)
+    return DispatchPlan(counts, visit_token, visit_meta, slot_of)
 
 
 def _all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
@@ -59,7 +87,10 @@ def _all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group) -> tor
 
 
 class LocalExperts:
-    """The CUDA path for step 3: this rank's experts through ``moe_align`` + ``fused_moe_*``."""
+    """The CUDA path for step 3: this rank's experts through ``moe_align`` + ``fused_moe_*``.
+
+    ``rows[R, K]`` are the visiting token rows, ``local_ids[R, top_k]`` their local expert ids (-1 = no route in
+    that slot), ``weights[R, top_k]`` the routing weights; returns the weighted partial sums ``[R, K]`` bf16."""
 
     def __init__(self, w1, w2, w1_scales=None, w2_scales=None, stages: int = 4, split: bool = True, bpc: int = 0):
         self.w1, self.w2, self.w1_scales, self.w2_scales = w1, w2, w1_scales, w2_scales
@@ -69,22 +100,26 @@ class LocalExperts:
         # faster on the one-CTA kernels (in-kernel row gather, less padding), and so is mxfp8
         self.bpc = bpc if bpc else (2 if (w1_scales is None and split and w1.shape[1] >= 8192) else 1)
 
-    def __call__(self, rows: torch.Tensor, local_expert: torch.Tensor, row_scales: Optional[torch.Tensor] = None):
+    def __call__(self, rows: torch.Tensor, local_ids: torch.Tensor, weights: torch.Tensor,
+                 row_scales: Optional[torch.Tensor] = None):
         if not rows.is_cuda:
             raise RuntimeError("LocalExperts needs CUDA tensors: this package has no CPU kernels")
         ops = torch.ops.prime_moe
         R, K = rows.shape
+        top_k = local_ids.shape[1]
         out = torch.empty(R, K, dtype=torch.bfloat16, device=rows.device)   # split=True zeroes it itself
         if R == 0:
             return out
-        s, e, n = ops.moe_align(local_expert.reshape(R, 1).contiguous(), self.num_local, 128, self.bpc)
-        ones = torch.ones(R, dtype=torch.float32, device=rows.device)
+        if not self.split:
+            out.zero_()
+        s, e, n = ops.moe_align(local_ids.contiguous(), self.num_local, 128, self.bpc)
+        w = weights.reshape(-1).contiguous()
         if self.w1_scales is None:
-            ops.fused_moe_bf16(rows, self.w1, self.w2, s, e, n, ones, out, 1, 128, 64, 4, self.stages, self.bpc, 1,
+            ops.fused_moe_bf16(rows, self.w1, self.w2, s, e, n, w, out, top_k, 128, 64, 4, self.stages, self.bpc, 1,
                                self.split)
         else:
-            ops.fused_moe_mxfp8(rows, row_scales, self.w1, self.w1_scales, self.w2, self.w2_scales, s, e, n, ones, out,
-                                1, 128, 64, 4, self.stages, self.bpc, self.split)
+            ops.fused_moe_mxfp8(rows, row_scales, self.w1, self.w1_scales, self.w2, self.w2_scales, s, e, n, w, out,
+                                top_k, 128, 64, 4, self.stages, self.bpc, self.split)
         return out
 
 
@@ -92,7 +127,8 @@ class ExpertParallelMoE:
     """``out = layer(x, topk_ids, topk_weights[, x_scales])`` with GLOBAL expert ids in ``topk_ids``.
 
     ``experts`` is the callable for step 3 (``LocalExperts`` on a GPU). ``last_recv_rows`` holds the number of
-    rows this rank computed in the last call (load imbalance under skewed routing shows up there)."""
+    visits this rank computed in the last call and ``last_sent_rows`` the number it sent (load imbalance under
+    skewed routing and the saving over one row per route show up there)."""
 
     def __init__(self, num_experts: int, experts: Callable, group=None):
         self.num_experts = num_experts
@@ -100,37 +136,42 @@ class ExpertParallelMoE:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.last_recv_rows = 0
+        self.last_sent_rows = 0
 
     def forward(self, x, topk_ids, topk_weights, x_scales=None):
         T, K = x.shape
         top_k = topk_ids.shape[1]
-        plan = make_dispatch_plan(topk_ids, self.num_experts, self.world)
+        plan = make_dispatch_plan(topk_ids, topk_weights, self.num_experts, self.world)
         if self.world > 1:
-            recv_counts = torch.empty_like(plan.send_counts)
-            dist.all_to_all_single(recv_counts, plan.send_counts, group=self.group)
-            # everything that does not need the counts is enqueued before the one host sync of the step
-            send_rows = x[plan.tokens]
-            send_scales = x_scales[plan.tokens] if x_scales is not None else None
-            slots = torch.empty_like(plan.perm)
-            slots[plan.perm] = torch.arange(plan.perm.numel(), device=plan.perm.device)
-            send, recv = plan.send_counts.tolist(), recv_counts.tolist()
+            recv_counts = torch.empty_like(plan.counts)
+            dist.all_to_all_single(recv_counts, plan.counts, group=self.group)
+            send, recv = plan.counts.tolist(), recv_counts.tolist()         # the one host sync of the step
+        else:
+            send = recv = plan.counts.tolist()
+        V = sum(send)
+        tokens = plan.visit_token[:V]
+        send_rows = x[tokens]
+        send_scales = x_scales[tokens] if x_scales is not None else None
+        meta = plan.visit_meta[:V]
+        if self.world > 1:
             rows = _all_to_all_rows(send_rows, send, recv, self.group)
-            local_e = _all_to_all_rows(plan.local_expert, send, recv, self.group)
+            meta = _all_to_all_rows(meta, send, recv, self.group)
             scales = _all_to_all_rows(send_scales, send, recv, self.group) if x_scales is not None else None
         else:
-            slots = torch.empty_like(plan.perm)
-            slots[plan.perm] = torch.arange(plan.perm.numel(), device=plan.perm.device)
-            rows, local_e = x[plan.tokens], plan.local_expert
-            scales = x_scales[plan.tokens] if x_scales is not None else None
-        self.last_recv_rows = rows.shape[0]
-        y = self.experts(rows, local_e, scales) if scales is not None else self.experts(rows, local_e)
+            rows, scales = send_rows, send_scales
+        self.last_sent_rows, self.last_recv_rows = V, rows.shape[0]
+        local_ids = meta[:, :top_k].contiguous()
+        weights = meta[:, top_k:].contiguous().view(torch.float32)
+        y = (self.experts(rows, local_ids, weights, scales) if scales is not None
+             else self.experts(rows, local_ids, weights))
         if self.world > 1:
             y = _all_to_all_rows(y, recv, send, self.group)
-        # combine at the source: pair p sits in row slots[p]; out[t] = sum_j w[t,j] * y[slots[t*k+j]]
+        # combine at the source: out[t] = sum of the partial sums of the token's visits
         if y.is_cuda:
-            return torch.ops.prime_moe.ep_combine(y, slots, topk_weights.reshape(-1).float().contiguous(), top_k)
-        y = y[slots].view(T, top_k, K).float()          # CPU ranks (gloo tests of the host logic)
-        return (y * topk_weights.view(T, top_k, 1).float()).sum(1).to(torch.bfloat16)
+            return torch.ops.prime_moe.ep_combine(y.contiguous(), plan.slot_of)
+        slot = plan.slot_of.to(torch.int64)                      # CPU ranks (gloo tests of the host logic)
+        part = torch.cat([y.float(), torch.zeros(1, K)])[torch.where(slot >= 0, slot, torch.full_like(slot, y.shape[0]))]
+        return part.sum(1).to(torch.bfloat16)
 
     __call__ = forward
 

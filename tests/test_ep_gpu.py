@@ -45,7 +45,7 @@ def _worker(rank, world, port, mx, ret):
             out = layer(x[lo:hi].to(dev), ids[lo:hi].to(dev), wts[lo:hi].to(dev))
             ref = O.moe_ref_fp32(x, w1, w2, ids, wts)[lo:hi]
         torch.cuda.synchronize()
-        ret[rank] = (O.max_rel_to_peak(out.cpu(), ref), layer.last_recv_rows)
+        ret[rank] = (O.max_rel_to_peak(out.cpu(), ref), layer.last_recv_rows, layer.last_sent_rows)
     finally:
         dist.destroy_process_group()
 
@@ -57,6 +57,42 @@ def test_ep_two_gpus(mx):
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, _free_port(), mx, ret), nprocs=2, join=True)
     assert len(ret) == 2
-    assert sum(ret[r][1] for r in range(2)) == 300 * 2 * 4
+    _, _, _, ids, _ = O.make_case(300 * 2, 1024, 16, 1024, 4, seed=11, dist="zipf")
+    visits = sum(len(set(int(e) // 8 for e in row)) for row in ids.tolist())      # distinct (token, rank) pairs
+    assert sum(ret[r][1] for r in range(2)) == sum(ret[r][2] for r in range(2)) == visits
     for r in range(2):
         assert ret[r][0] <= 2e-2, f"rank {r}: {ret[r][0]}"
+
+
+@pytest.mark.parametrize("T,E,k,G,dist_name", [(1, 8, 2, 2, "uniform"), (300, 16, 4, 4, "zipf"), (4096, 8, 2, 8, "uniform"),
+                                               (5000, 256, 8, 8, "uniform"), (1000, 128, 8, 32, "zipf")])
+def test_plan_kernels_match_torch_construction(T, E, k, G, dist_name):
+    """pmoe_ep_plan (three kernels, no host sync) against the torch construction of the same plan: bit-exact."""
+    from prime_flash_moe_b200 import ep
+    ids, wts = O.make_routing(T, E, k, seed=T, dist=dist_name)
+    if T >= 300:
+        ids[7, 0] = -1          # ids outside [0, E) are ignored
+        ids[9, 1] = E
+    ref = ep.make_dispatch_plan_torch(ids, wts, E, G)
+    got = ep.make_dispatch_plan(ids.cuda(), wts.cuda(), E, G)
+    torch.cuda.synchronize()
+    V = int(ref.counts.sum())
+    assert torch.equal(got.counts.cpu(), ref.counts)
+    assert torch.equal(got.visit_token[:V].cpu(), ref.visit_token)
+    assert torch.equal(got.visit_meta[:V].cpu(), ref.visit_meta)
+    assert torch.equal(got.slot_of.cpu(), ref.slot_of)
+
+
+def test_single_rank_layer_equals_the_operator():
+    """World size 1 (no process group): plan -> LocalExperts -> combine must reproduce the plain operator."""
+    import prime_flash_moe_b200 as P
+    from prime_flash_moe_b200 import ep
+    T, K, E, N, k = 200, 512, 8, 512, 4
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=3)
+    ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
+    dev = "cuda:0"
+    layer = ep.ExpertParallelMoE(E, ep.LocalExperts(w1.to(dev), w2.to(dev)))
+    out = layer(x.to(dev), ids.to(dev), wts.to(dev))
+    torch.cuda.synchronize()
+    assert layer.last_sent_rows == T                       # one visit per token on a single rank
+    assert O.max_rel_to_peak(out.cpu(), ref) <= 2e-2
