@@ -108,16 +108,13 @@ bool pdl_enabled() {
     return on;
 }
 
-int a_operand_mode() {
-    static const int m = [] {
-        const char *e = getenv("PMOE_AGATHER");
-        if (e && !strcmp(e, "tma4")) return 0;
-        if (e && !strcmp(e, "lsu")) return 2;
-        if (e && !strcmp(e, "pre")) return 1;
-        if (getenv("PMOE_PREGATHER")) return pregather_enabled() ? 1 : 0;
-        return -1;   // auto: LSU gather in the one-CTA kernels, row-gather pre-pass for the CTA-pair kernels
-    }();
-    return m;
+int a_operand_mode() {   // read on every call: tests switch modes inside one process
+    const char *e = getenv("PMOE_AGATHER");
+    if (e && !strcmp(e, "tma4")) return 0;
+    if (e && !strcmp(e, "lsu")) return 2;
+    if (e && !strcmp(e, "pre")) return 1;
+    if (getenv("PMOE_PREGATHER")) return pregather_enabled() ? 1 : 0;
+    return -1;   // auto: chosen per call from the layer width and the routed rows per expert
 }
 
 int down_bulk_reduce_mode() {

@@ -50,7 +50,8 @@ bool pregather_enabled();
 
 // How the split pipelines' gate/up GEMM gets the routed rows of x: PMOE_AGATHER=tma4 (0, TMA gather4),
 // pre (1, row-gather pre-pass + plain tiles), lsu (2, cp.async gather by extra warps inside the kernel);
-// unset = -1 = lsu for the one-CTA kernels, pre for the CTA-pair kernels (measured best of each)
+// unset = -1 = chosen per call: lsu for compute-bound calls of narrow layers on the one-CTA kernels, pre
+// otherwise (measured best of each)
 int a_operand_mode();
 
 // PMOE_DOWN_BULK=0/1 forces the down kernels' epilogue (scattered vector reductions / bulk reductions from a

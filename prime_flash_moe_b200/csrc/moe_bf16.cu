@@ -345,7 +345,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             gather_rows(a, c.m_blk, lane, r);
             const int row_gate = e * a.N + c.n_tile * 128;
             const int row_up = row_gate + a.H;
-            const bool short_a = a.pregathered == 1 && block_is_short(a, c.m_blk);
+            const bool short_a = a.pregathered != 2 && block_is_short(a, c.m_blk);
             const uint32_t fill_bytes =
                 a.pregathered == 2 ? B_BYTES : (short_a ? B_BYTES + SHORT_A_BYTES : STAGE_BYTES);
             for (int ks = 0; ks < ksteps; ++ks) {
@@ -364,7 +364,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     }
                 }
                 __syncwarp();
-                if (a.pregathered == 0)
+                if (a.pregathered == 0 && (!short_a || lane < SHORT_ROWS / 4))   // short block: rows 0..31 only
                     tma_gather4(sm.a(s) + lane * 512, &map_x, sm.full(s), ks * BK, r[0], r[1], r[2], r[3]);
                 ++issued;
                 if (++s == a.stages) {
@@ -1204,6 +1204,8 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     // auto: the in-kernel LSU gather pays off when the row-gather pre-pass is a visible share of the step (its
     // cost is ~250/N of a compute-bound step) and the step is compute-bound (>= 256 routed rows per expert on
     // average; in the weight-streaming regime the pre-pass with plain tiles streams faster)
+    // (TMA gather4 straight from x - 8 instead of 32 gather4 per k-step for short row blocks - was measured for
+    // calls with <= 32 routed rows per expert: same time as the PDL-chained pre-pass, so it stays an option)
     if (a_mode < 0)
         a_mode = (p.bpc == 1 && p.N < 8192 && static_cast<long long>(p.M) * p.top_k >= 256ll * p.E) ? 2 : 1;
     const bool pregather = a_mode == 1 || p.bpc == 2;   // the CTA-pair kernels always take pre-gathered rows

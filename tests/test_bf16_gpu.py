@@ -249,14 +249,17 @@ FEW_ROW_CASES = [
 ]
 
 
+@pytest.mark.parametrize("agather", ["auto", "tma4"])
 @pytest.mark.parametrize("T,K,E,N,k", FEW_ROW_CASES)
-def test_short_row_blocks(T, K, E, N, k, monkeypatch):
+def test_short_row_blocks(T, K, E, N, k, agather, monkeypatch):
     """Row blocks holding at most 32 routed rows load and store only those rows of the A operand and of the
     activation tile (short TMA boxes); PMOE_SHORT_A=0 moves whole 128-row tiles. Both must meet the oracle bound,
     and they run the same arithmetic on the routed rows, so their outputs must be identical up to the order of
     the bf16 reductions into `out`."""
     x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=3 * T + K)
     ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
+    if agather != "auto":       # auto = row-gather pre-pass for calls this small
+        monkeypatch.setenv("PMOE_AGATHER", agather)
     monkeypatch.setenv("PMOE_SHORT_A", "3")
     short = run_mine(x, w1, w2, ids, wts, True)
     monkeypatch.setenv("PMOE_SHORT_A", "0")
