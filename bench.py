@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "mxfp8"])
     ap.add_argument("--split", type=int, default=1)
     ap.add_argument("--stages", type=int, default=4)
+    ap.add_argument("--warp-n", type=int, default=4, choices=[4, 8],
+                    help="epilogue warps of the bf16 kernels: (block_n, warp_n) = (64, 4) or (32, 8)")
     ap.add_argument("--bpc", type=int, default=0, help="0 = 2 (CTA pairs) for bf16 split, 1 otherwise")
     ap.add_argument("--parallel", default="auto", choices=["auto", "replica", "ep"],
                     help="N > 1: 'ep' shards the experts over the ranks (NCCL all-to-all dispatch/combine, the "
@@ -341,7 +343,7 @@ def run_gpu_arm(args, impl):
         import prime_flash_moe_b200  # noqa: F401
         from prime_flash_moe_b200 import capi
         ops = torch.ops.prime_moe
-        bn, wn, stages, split, bpc = 64, 4, args.stages, bool(args.split), args.bpc
+        (bn, wn), stages, split, bpc = ((64, 4) if args.warp_n == 4 else (32, 8)), args.stages, bool(args.split), args.bpc
         launches_per_step = (3 if T * k > 4096 else 1) + 3   # align kernels + gather, gate/up|fused, down|finalize
 
         def step(x_, ids_, wts_, out_):
@@ -456,8 +458,8 @@ def run_gpu_arm(args, impl):
         ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
         off = (-ws.data_ptr()) % 1024
         ws = ws[off:off + nbytes]
-        call = lambda: capi.fused_moe_bf16(x, w1, w2, s, e, n, wts, out, k, 128, 64, 4, args.stages, args.bpc, 1, True,
-                                           workspace=ws)
+        call = lambda: capi.fused_moe_bf16(x, w1, w2, s, e, n, wts, out, k, 128, 64 if args.warp_n == 4 else 32, args.warp_n,
+                                           args.stages, args.bpc, 1, True, workspace=ws)
         call()
         per_kernel = {}
         for name, mask in (("gather_rows", 1), ("moe_up_bf16", 2), ("moe_down_bf16", 4)):
