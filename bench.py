@@ -7,7 +7,9 @@ Prints ONE JSON line (rank 0). A step = one pass of the hot path over one synthe
 `torch.ops.prime_moe.moe_align` + `torch.ops.prime_moe.fused_moe_*`. `value` is whole-job TFLOP/s with
 the inputs resident in HBM (algorithmic FLOPs 3*P*K*N, P = T*top_k; padding rows do not count);
 `e2e` is the same metric with the step's activations, routing ids and routing weights copied from pinned
-host memory and `out` copied back inside the timed region (weights stay resident, as in a model).
+host memory and `out` copied back inside the timed region (weights stay resident, as in a model); the copies
+of neighbouring steps run on their own streams beside the kernels (two sets of device buffers), as a caller
+feeding the layer from host memory would do. Both arms use the same harness.
 
 `--impl reference` times the UNMODIFIED reference (pip-installed into baseline/_ref from the reference
 checkout) through its own public API on the same workload, its best accepted knob setting chosen during
@@ -15,8 +17,9 @@ warm-up. The reference has no CPU implementation of this path - its product is s
 arm runs on the GPU too; the reference's only CPU code for the path, the PyTorch MoE of its tests, is
 timed as `cpu_baseline` (and alone with `--impl cpu`).
 
-N > 1 (torchrun): every rank runs its own batch on its own GPU against a full replica of the experts
-(no collective on the data path, weak scaling), or the expert-parallel mode with `--parallel ep`.
+N > 1 (torchrun): expert-parallel mode when the experts divide over the ranks (`--parallel ep`, the default
+then: NCCL all-to-all dispatch / combine), else every rank runs its own batch against a full replica of the
+experts (`--parallel replica`, no collective on the data path). Weak scaling either way.
 """
 from __future__ import annotations
 
@@ -416,30 +419,51 @@ def run_gpu_arm(args, impl):
     value = ref_world * flops / (ms_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers, copies inside the timed region ----
+    # What a caller feeding the layer from host memory does: two sets of device buffers, the H2D copy of step
+    # i+1 and the D2H copy of step i-1 run on their own streams beside the kernels of step i. Every step's inputs
+    # come from pinned host memory and every step's result is read back to pinned host memory.
     hx = tuple(t.cpu().pin_memory() for t in xin) if mx else (x.cpu().pin_memory(),)
     hids, hwts = ids_cpu.pin_memory(), wts_cpu.pin_memory()
-    hout = torch.empty(T, K, dtype=torch.bfloat16).pin_memory()
-    dx = tuple(torch.empty_like(t, device=device) for t in hx)
-    dids, dwts = torch.empty_like(ids), torch.empty_like(wts)
+    houts = [torch.empty(T, K, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dxs = [tuple(torch.empty_like(t, device=device) for t in hx) for _ in range(2)]
+    didss, dwtss = [torch.empty_like(ids) for _ in range(2)], [torch.empty_like(wts) for _ in range(2)]
+    outs = [torch.empty_like(out) for _ in range(2)]
+    s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
 
-    def e2e_step():
-        for d_, h_ in zip(dx, hx):
-            d_.copy_(h_, non_blocking=True)
-        dids.copy_(hids, non_blocking=True)
-        dwts.copy_(hwts, non_blocking=True)
-        step(dx if mx else dx[0], dids, dwts, out)
-        hout.copy_(out, non_blocking=True)
+    def e2e_run(n):
+        in_done, comp_done, out_done = {}, {}, {}
+        for i in range(n):
+            j = i & 1
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(comp_done[i - 2])            # the kernels of step i-2 are done with buffer j
+                for d_, h_ in zip(dxs[j], hx):
+                    d_.copy_(h_, non_blocking=True)
+                didss[j].copy_(hids, non_blocking=True)
+                dwtss[j].copy_(hwts, non_blocking=True)
+                in_done[i] = s_in.record_event()
+            s_main.wait_event(in_done[i])
+            if i >= 2:
+                s_main.wait_event(out_done[i - 2])               # result buffer j has been read back
+            step(dxs[j] if mx else dxs[j][0], didss[j], dwtss[j], outs[j])
+            comp_done[i] = s_main.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(comp_done[i])
+                houts[j].copy_(outs[j], non_blocking=True)
+                out_done[i] = s_out.record_event()
+        s_main.wait_stream(s_in)
+        s_main.wait_stream(s_out)
+
     e2e_steps = max(5, min(args.steps, 50))
-    for _ in range(3):
-        e2e_step()
+    e2e_run(3)
     barrier_sync(ref_world)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     b.record()
     barrier_sync(ref_world)
     e2e_ms = max_over_ranks(a.elapsed_time(b), ref_world, device) / e2e_steps
+    hout = houts[0]
     h2d = sum(t.numel() * t.element_size() for t in hx) + hids.numel() * 4 + hwts.numel() * 4
     d2h = hout.numel() * 2
     e2e = {"value": ref_world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
