@@ -117,12 +117,9 @@ int a_operand_mode() {   // read on every call: tests switch modes inside one pr
     return -1;   // auto: chosen per call from the layer width and the routed rows per expert
 }
 
-int down_bulk_reduce_mode() {
-    static const int m = [] {
-        const char *e = getenv("PMOE_DOWN_BULK");
-        return e ? (e[0] == '0' ? 0 : 1) : -1;
-    }();
-    return m;
+int down_bulk_reduce_mode() {   // read on every call: tests switch modes inside one process
+    const char *e = getenv("PMOE_DOWN_BULK");
+    return e ? (e[0] == '0' ? 0 : 1) : -1;
 }
 
 static int g_l2_ahead = -1;
@@ -133,6 +130,11 @@ int l2_prefetch_distance() {
         g_l2_ahead = v < 0 ? 0 : (v > 64 ? 64 : v);
     }
     return g_l2_ahead;
+}
+
+int narrow_tiles_mode() {
+    const char *e = getenv("PMOE_NARROW");
+    return e ? (e[0] == '0' ? 0 : 1) : -1;
 }
 
 int short_boxes_mode() {
