@@ -132,11 +132,6 @@ int l2_prefetch_distance() {
     return g_l2_ahead;
 }
 
-int narrow_tiles_mode() {
-    const char *e = getenv("PMOE_NARROW");
-    return e ? (e[0] == '0' ? 0 : 1) : -1;
-}
-
 int short_boxes_mode() {
     const char *e = getenv("PMOE_SHORT_A");
     return e ? atoi(e) & 3 : 3;
