@@ -216,7 +216,7 @@ def time_cpu_oracle(x, w1, w2, ids, wts, sample_tokens):
     return flops / dt / 1e12, dt, torch.get_num_threads()
 
 
-def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tflops):
+def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tflops, flush_buf=None):
     """Gate/up kernel of the mxfp8 split pipeline timed alone (profiling hook). No fp8 peak was measured on
     this pool: the denominator is 2 x the measured bf16 burst peak, stated as an assumption."""
     import torch
@@ -234,16 +234,7 @@ def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tf
     per_kernel = {}
     for name, mask in (("gather_rows_mxfp8", 1), ("moe_up_mxfp8", 2), ("moe_down_mxfp8", 4)):
         lib.pmoe_debug_set_phase_mask(mask)
-        for _ in range(3):
-            call()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(20):
-            call()
-        b.record()
-        torch.cuda.synchronize()
-        per_kernel[name] = a.elapsed_time(b) / 20
+        per_kernel[name] = time_calls(call, 20, flush_buf)
     lib.pmoe_debug_set_phase_mask(7)
     call()
     torch.cuda.synchronize()
@@ -254,6 +245,57 @@ def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tf
             "frac": achieved / peak, "peak_source": source,
             "traffic": 0.6565e9 if (args.config == "c2" and not args.tokens) else None,   # from the ncu capture summarised under profiles/
             "kernel_ms": per_kernel, "whole_op_frac": whole_tflops / peak}
+
+
+def time_calls(call, reps, flush_buf=None):
+    """Mean milliseconds of `call` on the current stream: one pair of events around `reps` back-to-back calls,
+    or - with a flush buffer - a pair per call with the L2 flushed (buffer rewritten) before each."""
+    import torch
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    if flush_buf is None:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            call()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+    pairs = []
+    for _ in range(reps):
+        flush_buf.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        call()
+        b.record()
+        pairs.append((a, b))
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in pairs) / reps
+
+
+def weight_streaming_roofline(roof, cfg, ids, per_kernel_up_ms, ms_step, peaks, mx, traffic):
+    """Calls with fewer than 256 routed rows per expert are bound by streaming the weights of the experts
+    actually routed to, not by the tensor pipe: restate the roofline of the gate/up kernel against the
+    measured HBM copy bandwidth. Algorithmic bytes of that kernel: w1 of the touched experts (+ scales),
+    the routed rows of x, the activation written, `out` zeroed."""
+    T, K, E, N, k, _ = cfg
+    if T * k >= 256 * E:
+        return roof
+    touched = int(ids.unique().numel())
+    wbytes = 1.0 + 1.0 / 32 if mx else 2.0
+    abytes = 1.0 + 1.0 / 32 if mx else 2.0
+    up_bytes = touched * N * K * wbytes + T * k * K * abytes + T * k * (N // 2) * abytes + T * K * 2
+    op_bytes = touched * (N * K + K * (N // 2)) * wbytes + T * K * abytes + T * K * 2
+    achieved = up_bytes / (per_kernel_up_ms * 1e-3) / 1e9
+    roof = dict(roof)
+    roof.update({"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                 "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"] + " (STREAM-style copy)",
+                 "traffic": traffic, "algorithmic_bytes": up_bytes, "experts_touched": touched,
+                 "whole_op_frac": op_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                 })
+    roof.pop("frac_of_sustained", None)
+    return roof
 
 
 def measure_mxfp8_peak(device):
@@ -403,18 +445,36 @@ def run_gpu_arm(args, impl):
         _, step, knobs = best
 
     ref_world = 1 if impl == "reference" else world
+    # bytes of the weights one step reads: experts actually routed to x (w1 + w2)
+    touched_weight_bytes = int(ids_cpu.unique().numel()) * (N * K + K * (N // 2)) * (1 if mx else 2)
+    flush_l2 = touched_weight_bytes < (256 << 20)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device) if flush_l2 else None
     # ---- device-resident timing ----
     for _ in range(max(args.warmup, 3)):
         step(xin, ids, wts, out)
     barrier_sync(ref_world)
     with ClockSampler(local) as clocks:
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            step(xin, ids, wts, out)
-        b.record()
-        barrier_sync(ref_world)
-        ms_total = max_over_ranks(a.elapsed_time(b), ref_world, device)
+        if flush_l2:
+            # the weights a step touches would stay in the 126 MB L2 from one step to the next: write a 256 MB
+            # buffer between steps and time every step with its own pair of events (the flush is not timed)
+            pairs = []
+            for _ in range(args.steps):
+                flush_buf.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                step(xin, ids, wts, out)
+                b.record()
+                pairs.append((a, b))
+            barrier_sync(ref_world)
+            ms_total = max_over_ranks(sum(a.elapsed_time(b) for a, b in pairs), ref_world, device)
+        else:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                step(xin, ids, wts, out)
+            b.record()
+            barrier_sync(ref_world)
+            ms_total = max_over_ranks(a.elapsed_time(b), ref_world, device)
     ms_step = ms_total / args.steps
     value = ref_world * flops / (ms_step * 1e-3) / 1e12
 
@@ -472,7 +532,10 @@ def run_gpu_arm(args, impl):
     peaks = measured_peaks()
     roofline = None
     if impl == "ours" and args.split and mx and not ep_mode:
-        roofline = roofline_mxfp8(args, capi, ops, (xq, xs, w1q, w1s, w2q, w2s), ids, wts, out, cfg, peaks, value / world)
+        roofline = roofline_mxfp8(args, capi, ops, (xq, xs, w1q, w1s, w2q, w2s), ids, wts, out, cfg, peaks, value / world,
+                                  flush_buf if flush_l2 else None)
+        roofline = weight_streaming_roofline(roofline, cfg, ids, roofline["kernel_ms"]["moe_up_mxfp8"], ms_step, peaks, True,
+                                             431.8e6 if (args.config == "c2" and args.tokens == 128) else None)
     if impl == "ours" and args.split and not mx and not ep_mode:
         # dominant kernel = the gate/up GEMM (2/3 of the FLOPs); timed alone through the profiling hook
         lib = capi.lib()
@@ -488,17 +551,7 @@ def run_gpu_arm(args, impl):
         per_kernel = {}
         for name, mask in (("gather_rows", 1), ("moe_up_bf16", 2), ("moe_down_bf16", 4)):
             lib.pmoe_debug_set_phase_mask(mask)
-            for _ in range(3):
-                call()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 20
-            a.record()
-            for _ in range(reps):
-                call()
-            b.record()
-            torch.cuda.synchronize()
-            per_kernel[name] = a.elapsed_time(b) / reps
+            per_kernel[name] = time_calls(call, 20, flush_buf if flush_l2 else None)
         lib.pmoe_debug_set_phase_mask(7)
         call()
         torch.cuda.synchronize()
@@ -513,6 +566,8 @@ def run_gpu_arm(args, impl):
                     "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
                     "traffic": traffic, "algorithmic_bytes": float(E * N * K * 2 + T * k * K * 2 + T * k * N + T * K * 2),
                     "kernel_ms": per_kernel, "whole_op_frac": value / world / peaks["bf16_tflops"]}
+        roofline = weight_streaming_roofline(roofline, cfg, ids, per_kernel["moe_up_bf16"], ms_step, peaks, False,
+                                             835.3e6 if (args.config == "c2" and args.tokens == 128) else None)
         assert capi.device_status() == 0, "a kernel recorded an error status"
 
     cpu_baseline = None
@@ -535,8 +590,10 @@ def run_gpu_arm(args, impl):
             "config": {"workload": f"{args.config}: T={T} K={K} E={E} N={N} top_k={k} routing={routing} "
                                    f"(per GPU), moe_align + fused_moe_{args.dtype}",
                        "knobs": knobs, "parallelism": f"{args.parallel}{ref_world}",
-                       "l2": "weights (>= 1 GB) exceed the 126 MB L2, no flush between steps" if
-                             E * N * K * 3 > 256e6 else "inputs smaller than L2; steps are back to back"},
+                       "l2": (f"a step touches {touched_weight_bytes / 1e6:.0f} MB of weights: L2 flushed (256 MB "
+                              "written) between steps, every step timed with its own events") if flush_l2 else
+                             (f"a step reads {touched_weight_bytes / 1e6:.0f} MB of weights, more than the 126 MB L2: "
+                              "no flush between steps")},
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": (launches_per_step or 0) * args.steps,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
