@@ -132,6 +132,11 @@ int l2_prefetch_distance() {
     return g_l2_ahead;
 }
 
+int dual_blocks_mode() {
+    const char *e = getenv("PMOE_DUAL");
+    return e ? (e[0] == '0' ? 0 : 1) : -1;
+}
+
 int short_boxes_mode() {
     const char *e = getenv("PMOE_SHORT_A");
     return e ? atoi(e) & 3 : 3;

@@ -63,7 +63,10 @@ int l2_prefetch_distance();
 
 // PMOE_SHORT_A=0 switches off the short TMA boxes (row blocks with few routed rows move only those rows of the
 // A operand and of the activation tile); read on every call so that tests can compare both settings
-int short_boxes_mode();   // bit 0: loads, bit 1: activation stores
+int short_boxes_mode();
+
+// PMOE_DUAL=0/1 forces one / two row blocks per tile in the one-CTA bf16 gate/up kernel; unset = -1 = by size
+int dual_blocks_mode();   // bit 0: loads, bit 1: activation stores
 
 // which launches of a split pipeline run (pmoe_debug_set_phase_mask): 1 gather, 2 gate/up, 4 down
 int phase_mask();

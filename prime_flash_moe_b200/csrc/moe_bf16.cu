@@ -509,6 +509,321 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 }
 
 // ---------------------------------------------------------------------------------------------
+// gate/up kernel with TWO row blocks per tile (one CTA, no counterpart in the reference): the consecutive
+// blocks 2q and 2q+1, when they belong to one expert, share every weight slot of the ring - 64 KB per
+// k-step feed 2 x (128 x 256 x 64) MACs instead of 2 x 48 KB, the same operand traffic per MAC as the CTA
+// pairs but on routing tables padded to 128 rows and with the in-kernel LSU row gather. Block 2q
+// accumulates in TMEM columns [0,256), block 2q+1 in [256,512); the epilogue drains them one after the
+// other and the next tile's MMAs start on each accumulator as soon as it is free. Blocks 2q, 2q+1 of
+// different experts (and an odd last block) run as single-block passes with their own weight loads.
+//   misc barriers: 0,1 tmem_full[acc] | 2,3 tmem_empty[acc] | 4 staged | 5 stage_free
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t DUAL_STAGE_BYTES = 2 * A_BYTES + B_BYTES;   // 64 KB
+constexpr int DUAL_MAX_STAGES = 3;
+
+struct SmemDual {
+    uint32_t ring, act, bars;
+    __device__ __forceinline__ uint32_t a(int s, int h) const { return ring + s * DUAL_STAGE_BYTES + h * A_BYTES; }
+    __device__ __forceinline__ uint32_t b(int s) const { return ring + s * DUAL_STAGE_BYTES + 2 * A_BYTES; }
+    __device__ __forceinline__ uint32_t full(int s) const { return bars + 8 * s; }
+    __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8 * (DUAL_MAX_STAGES + s); }
+    __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * DUAL_MAX_STAGES + i); }
+    __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * DUAL_MAX_STAGES + 8); }
+};
+__device__ __forceinline__ SmemDual carve_dual(const uint8_t *raw, int stages) {
+    SmemDual s;
+    s.ring = (smem_u32(raw) + 1023u) & ~1023u;
+    s.act = s.ring + stages * DUAL_STAGE_BYTES;
+    s.bars = s.act + ACT_TILE_BYTES;
+    return s;
+}
+size_t smem_bytes_dual(int stages) { return 1024 + static_cast<size_t>(stages) * DUAL_STAGE_BYTES + ACT_TILE_BYTES + BAR_BYTES; }
+
+struct Pass {
+    int blk[2];   // row blocks of the pass (blk[1] = -1 for a single-block pass)
+    int nblk;
+    int expert;
+};
+// the one or two passes of tile pair q; identical in every role of the CTA
+__device__ __forceinline__ int tile_passes(const Args &a, int q, int m_blocks, Pass (&p)[2]) {
+    const int b0 = 2 * q, b1 = b0 + 1;
+    const int e0 = a.expert_ids[b0];
+    p[0].blk[0] = b0;
+    p[0].blk[1] = -1;
+    p[0].nblk = 1;
+    p[0].expert = e0;
+    if (b1 >= m_blocks) return 1;
+    const int e1 = a.expert_ids[b1];
+    if (e1 == e0) {
+        p[0].blk[1] = b1;
+        p[0].nblk = 2;
+        return 1;
+    }
+    p[1].blk[0] = b1;
+    p[1].blk[1] = -1;
+    p[1].nblk = 1;
+    p[1].expert = e1;
+    return 2;
+}
+
+__global__ void __launch_bounds__(MAX_THREADS, 1)
+moe_up_dual_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
+                        const __grid_constant__ CUtensorMap map_act, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const SmemDual sm = carve_dual(smem_raw, a.stages);
+    int *status = &g_status_bf16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int epi_threads = a.epi_warps * 32;
+    const bool lsu = a.pregathered == 2;
+    const int gather_threads = static_cast<int>(blockDim.x) - 64 - epi_threads;   // 0, 128 or 256
+
+    pdl_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(sm.full(s), lsu ? 1 + gather_threads : 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), 1);
+        mbar_init(sm.misc(2), epi_threads);
+        mbar_init(sm.misc(3), epi_threads);
+        mbar_init(sm.misc(4), epi_threads);
+        mbar_init(sm.misc(5), 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w1);
+        tma_prefetch_desc(&map_act);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    if (a.use_pdl) pdl_wait_primary();   // launched as a programmatic dependent of the row-gather kernel
+
+    const int m_blocks = num_row_blocks(a);
+    const int m_pairs = (m_blocks + 1) / 2;
+    const int n_tiles = a.H / 128;
+    const int num_tiles = m_pairs * n_tiles;
+    const int ksteps = a.K / BK;
+
+    if (warp == 0) {
+        // ---------------- producer: weight slots (and the pre-gathered A tiles) by TMA ----------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Coord c = tile_coord(t, m_pairs, n_tiles);
+                Pass ps[2];
+                const int np = tile_passes(a, c.m_blk, m_blocks, ps);
+                for (int pi = 0; pi < np && ok; ++pi) {
+                    const Pass &p = ps[pi];
+                    const int row_gate = p.expert * a.N + c.n_tile * 128;
+                    const int row_up = row_gate + a.H;
+                    const uint32_t bytes = B_BYTES + (lsu ? 0u : static_cast<uint32_t>(p.nblk) * A_BYTES);
+                    for (int ks = 0; ks < ksteps; ++ks) {
+                        ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(sm.full(s), bytes);
+                        tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
+                        tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
+                        if (!lsu) {
+                            tma_load_2d(sm.a(s, 0), &map_x, sm.full(s), ks * BK, p.blk[0] * BM);
+                            if (p.nblk == 2) tma_load_2d(sm.a(s, 1), &map_x, sm.full(s), ks * BK, p.blk[1] * BM);
+                        }
+                        if (++s == a.stages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t uses[2] = {0, 0};   // completed passes per accumulator
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Coord c = tile_coord(t, m_pairs, n_tiles);
+                Pass ps[2];
+                const int np = tile_passes(a, c.m_blk, m_blocks, ps);
+                for (int pi = 0; pi < np && ok; ++pi) {
+                    const int nblk = ps[pi].nblk;
+                    ok = mbar_wait(sm.misc(2), (uses[0] & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                    tc_fence_after();
+                    for (int ks = 0; ks < ksteps; ++ks) {
+                        ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_f16(tmem_base, smem_desc_sw128(sm.a(s, 0) + k * 32), smem_desc_sw128(sm.b(s) + k * 32),
+                                     idesc, (ks | k) != 0);
+                        if (nblk == 2) {
+                            if (ks == 0) {   // the second accumulator is waited for as late as possible
+                                ok = mbar_wait(sm.misc(3), (uses[1] & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                                if (!ok) break;
+                                tc_fence_after();
+                            }
+#pragma unroll
+                            for (int k = 0; k < BK / 16; ++k)
+                                umma_f16(tmem_base + 256, smem_desc_sw128(sm.a(s, 1) + k * 32),
+                                         smem_desc_sw128(sm.b(s) + k * 32), idesc, (ks | k) != 0);
+                        }
+                        umma_commit(sm.empty(s));
+                        if (++s == a.stages) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(sm.misc(0));
+                    ++uses[0];
+                    if (nblk == 2) {
+                        umma_commit(sm.misc(1));
+                        ++uses[1];
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 2 + a.epi_warps) {
+        // ---------------- LSU gather warps (mode 2): the A rows of both blocks straight from x ----------------
+        // as in moe_up_bf16_kernel: 8 lanes per 128-byte row segment, a thread serves rows (g>>3) + 16*i of a
+        // block, lagged wait_group + proxy fence before its arrival on the slot's full barrier. With eight
+        // gather warps the first four serve block 2q and the last four block 2q+1; with four, every thread
+        // serves both blocks.
+        const int g = (threadIdx.x - 64 - epi_threads) & 127;
+        const int serve = gather_threads == 256 ? (static_cast<int>(threadIdx.x) - 64 - epi_threads) >> 7 : -1;   // -1: both blocks
+        const int q = g >> 3, chunk = g & 7;
+        // a slot is published while the NEXT one is being issued: with three slots a lag of two would make
+        // every k-step wait for the MMAs of the previous one
+        const int lag = min(1, a.stages - 1);
+        int s = 0, s_done = 0;
+        uint32_t ph = 0;
+        long long issued = 0, arrived = 0;
+        auto publish = [&](int pending_allowed) {
+            if (pending_allowed >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else if (pending_allowed == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            fence_proxy_async_smem();
+            while (arrived < issued - pending_allowed) {
+                mbar_arrive(sm.full(s_done));
+                if (++s_done == a.stages) s_done = 0;
+                ++arrived;
+            }
+        };
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const Coord c = tile_coord(t, m_pairs, n_tiles);
+            Pass ps[2];
+            const int np = tile_passes(a, c.m_blk, m_blocks, ps);
+            for (int pi = 0; pi < np && ok; ++pi) {
+                const Pass &p = ps[pi];
+                const char *src[2][8];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int pair = h < p.nblk ? a.sorted_ids[p.blk[h] * BM + q + 16 * i] : -1;
+                        int tok = pair >= 0 ? pair / a.top_k : 0;
+                        if (tok >= a.M) tok = 0;
+                        src[h][i] = reinterpret_cast<const char *>(a.x + static_cast<size_t>(tok) * a.K) + chunk * 16;
+                    }
+                }
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    const uint32_t off = q * 128 + ((chunk ^ (q & 7)) << 4);
+                    if (serve != 1) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) cp_async_16(sm.a(s, 0) + off + i * 16 * 128, src[0][i] + ks * 128);
+                    }
+                    if (p.nblk == 2 && serve != 0) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) cp_async_16(sm.a(s, 1) + off + i * 16 * 128, src[1][i] + ks * 128);
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                    if (issued - arrived > lag) publish(lag);
+                }
+            }
+        }
+        publish(0);
+        cp_async_wait_all();
+    } else {
+        // ---------------- epilogue: thread = accumulator row, one accumulator after the other ----------------
+        const int ew = warp - 2;
+        const int et = threadIdx.x - 64;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int ncg = a.epi_warps / 4;
+        const int cg = ew / 4;
+        if (a.zero_out) {
+            int4 *o4 = reinterpret_cast<int4 *>(a.out);
+            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const int4 z = make_int4(0, 0, 0, 0);
+            for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
+                 i += static_cast<long long>(gridDim.x) * epi_threads)
+                o4[i] = z;
+        }
+        uint32_t uses[2] = {0, 0};
+        uint32_t stores = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const Coord c = tile_coord(t, m_pairs, n_tiles);
+            Pass ps[2];
+            const int np = tile_passes(a, c.m_blk, m_blocks, ps);
+            for (int pi = 0; pi < np && ok; ++pi) {
+                for (int h = 0; h < ps[pi].nblk && ok; ++h) {
+                    ok = mbar_wait(sm.misc(h), uses[h] & 1, status, ST_TIMEOUT_TMEM_FULL) &&
+                         mbar_wait(sm.misc(5), (stores & 1) ^ 1, status, ST_TIMEOUT_ACT);   // staging tile free
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t acc = tmem_base + h * 256;
+                    for (int ch = cg * (4 / ncg); ch < (cg + 1) * (4 / ncg); ++ch)
+                        swiglu_chunk_to_smem(acc, lane_base, row, ch, sm.act);
+                    tc_fence_before();
+                    mbar_arrive(sm.misc(2 + h));   // accumulator drained
+                    fence_proxy_async_smem();
+                    mbar_arrive(sm.misc(4));       // staging tile written
+                    if (et == 0) {
+                        ok = mbar_wait(sm.misc(4), stores & 1, status, ST_TIMEOUT_ACT);
+                        if (!ok) break;
+                        tma_store_2d(&map_act, sm.act, c.n_tile * 128, ps[pi].blk[h] * BM);
+                        tma_store_2d(&map_act, sm.act + ACT_TILE_BYTES / 2, c.n_tile * 128 + 64, ps[pi].blk[h] * BM);
+                        tma_store_commit();
+                        tma_store_wait_read<0>();
+                        mbar_arrive(sm.misc(5));
+                    }
+                    ++uses[h];
+                    ++stores;
+                }
+            }
+        }
+        if (et == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // down kernel (split pipeline, second launch)
 //   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2]
 // ---------------------------------------------------------------------------------------------
@@ -1292,7 +1607,35 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         }
         return PMOE_OK;
     }
-    if (phases & 2) {
+    // two row blocks per tile (shared weight slots): PMOE_DUAL=0/1, unset = for calls with >= 1024 routed rows per
+    // expert on average (measured: gate/up kernel -4..-5 % there with the in-kernel gather, -13..-15 % when fed by
+    // TMA from the row-gathered copy; +5 % at 512 rows per expert, where more pairs straddle two experts)
+    const int dual_env = dual_blocks_mode();
+    const bool dual = a_mode != 0 && (dual_env < 0 ? static_cast<long long>(p.M) * p.top_k >= 1024ll * p.E : dual_env != 0);
+    if ((phases & 2) && dual) {
+        Args up = a;
+        up.zero_out = 1;
+        up.pregathered = a_mode;
+        up.x = static_cast<const __nv_bfloat16 *>(p.x);
+        up.stages = std::min(a.stages, DUAL_MAX_STAGES);
+        // LSU mode: eight gather warps (four per row block) beside four epilogue warps, else four for both blocks
+        const int threads = 64 + 32 * a.epi_warps + (a_mode == 2 ? (a.epi_warps == 4 ? 2 : 1) * GATHER_THREADS : 0);
+        const size_t smem = smem_bytes_dual(up.stages);
+        if (int rc = set_smem(moe_up_dual_bf16_kernel, smem)) return rc;
+        const int tiles = ((max_blocks + 1) / 2) * (H / 128);
+        up.use_pdl = (pdl_enabled() && pregather && (phases & 1)) ? 1 : 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(std::min(tiles, sms));
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = up.use_pdl ? 1 : 0;
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_dual_bf16_kernel, map_x, map_w1, map_act, up));
+    } else if (phases & 2) {
         Args up = a;
         up.zero_out = 1;
         up.pregathered = a_mode;

@@ -268,3 +268,24 @@ def test_short_row_blocks(T, K, E, N, k, agather, monkeypatch):
     assert O.max_rel_to_peak(short, ref) <= TOL
     assert O.max_rel_to_peak(full, ref) <= TOL
     assert O.max_rel_to_peak(short, full.float()) <= TOL / 2
+
+
+@pytest.mark.parametrize("agather", ["pre", "lsu"])
+@pytest.mark.parametrize("bn,wn,stages", [(64, 4, 1), (64, 4, 4), (32, 8, 2)])
+@pytest.mark.parametrize("T,K,E,N,k", [(8, 128, 1, 256, 1), (300, 512, 4, 512, 2), (256, 4096, 8, 512, 4),
+                                        (1000, 1024, 16, 768, 8), (700, 256, 3, 1024, 1), (2048, 2048, 32, 2048, 4)])
+def test_dual_block_tiles(T, K, E, N, k, bn, wn, stages, agather, monkeypatch):
+    """Gate/up kernel with two row blocks per tile (consecutive blocks of one expert share the weight slots;
+    blocks of different experts and an odd last block run as single passes) against one block per tile: the
+    same arithmetic per routed row, so the outputs differ only by the order of the bf16 reductions."""
+    monkeypatch.setenv("PMOE_AGATHER", agather)
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=T + stages)
+    ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
+    monkeypatch.setenv("PMOE_DUAL", "1")
+    dual = run_mine(x, w1, w2, ids, wts, True, stages=stages, bn=bn, wn=wn)
+    monkeypatch.setenv("PMOE_DUAL", "0")
+    one = run_mine(x, w1, w2, ids, wts, True, stages=stages, bn=bn, wn=wn)
+    assert torch.isfinite(dual.float()).all()
+    assert O.max_rel_to_peak(dual, ref) <= TOL
+    assert O.max_rel_to_peak(one, ref) <= TOL
+    assert O.max_rel_to_peak(dual, one.float()) <= TOL
