@@ -389,7 +389,8 @@ def run_gpu_arm(args, impl):
         from prime_flash_moe_b200 import capi
         ops = torch.ops.prime_moe
         (bn, wn), stages, split, bpc = ((64, 4) if args.warp_n == 4 else (32, 8)), args.stages, bool(args.split), args.bpc
-        launches_per_step = (3 if T * k > 4096 else 1) + 3   # align kernels + gather, gate/up|fused, down|finalize
+        # align kernels + gather, gate/up|fused, down|finalize (+ pair classification and the two tail launches, bpc=2)
+        launches_per_step = (3 if T * k > 4096 else 1) + 3 + (3 if (bpc == 2 and split and not mx) else 0)
 
         def step(x_, ids_, wts_, out_):
             s, e, n = ops.moe_align(ids_, E, 128, bpc)

@@ -137,6 +137,11 @@ int dual_blocks_mode() {
     return e ? (e[0] == '0' ? 0 : 1) : -1;
 }
 
+bool pair_tails_enabled() {
+    const char *e = getenv("PMOE_PAIR_TAILS");   // read on every call: tests compare both settings
+    return !(e && e[0] == '0');
+}
+
 int short_boxes_mode() {
     const char *e = getenv("PMOE_SHORT_A");
     return e ? atoi(e) & 3 : 3;

@@ -65,6 +65,10 @@ int l2_prefetch_distance();
 // A operand and of the activation tile); read on every call so that tests can compare both settings
 int short_boxes_mode();
 
+// bpc = 2 runs the half-empty last pair of an expert as a single block on the one-CTA kernels (PMOE_PAIR_TAILS=0:
+// as a pair, like every other one)
+bool pair_tails_enabled();
+
 // PMOE_DUAL=0/1 forces one / two row blocks per tile in the one-CTA bf16 gate/up kernel; unset = -1 = by size
 int dual_blocks_mode();   // bit 0: loads, bit 1: activation stores
 

@@ -97,6 +97,11 @@ struct Args {
     int pregathered; // gate/up A operand: 0 = TMA gather4 from x, 1 = plain tiles from a row-gathered copy,
                      // 2 = gathered from x by four LSU warps (cp.async), no pre-pass
     const __nv_bfloat16 *x;   // mode 2: the activation matrix [M, K]
+    // bpc == 2 with tail splitting: the pair kernels run the pairs of `pair_list` (both blocks hold routed rows),
+    // the one-CTA kernels the first blocks of the pairs of `tail_list` (second block empty); counts = {pairs, tails}
+    const int32_t *pair_list;
+    const int32_t *tail_list;
+    const int32_t *list_counts;
     int short_boxes; // one-CTA split kernels: row blocks with <= SHORT_ROWS routed rows move only those rows of
                      // the A operand and of the activation tile (the rest of a 128-row block is padding)
 };
@@ -113,6 +118,53 @@ __device__ __forceinline__ int num_row_blocks(const Args &a) {
     int npp = *a.npp;
     npp = max(0, min(npp, a.sorted_num));
     return npp / BM;
+}
+
+// one-CTA kernels: number of row blocks to run and the block behind tile row i
+__device__ __forceinline__ int num_tile_rows(const Args &a) {
+    return a.tail_list ? a.list_counts[1] : num_row_blocks(a);
+}
+__device__ __forceinline__ int tile_row_block(const Args &a, int i) { return a.tail_list ? 2 * a.tail_list[i] : i; }
+
+// bpc == 2: ordered lists of the pairs whose second block holds routed rows and of those whose second block is
+// empty (the last pair of an expert with at most 128 rows left). One CTA; counts[0] = pairs, counts[1] = tails.
+__global__ void __launch_bounds__(256)
+classify_pairs_kernel(const int32_t *__restrict__ sorted_ids, const int32_t *__restrict__ npp, int sorted_num,
+                      int32_t *__restrict__ pair_list, int32_t *__restrict__ tail_list, int32_t *__restrict__ counts) {
+    __shared__ int s_warp[8];
+    __shared__ int s_base[2];
+    int n = *npp;
+    n = max(0, min(n, sorted_num)) / (2 * BM);
+    if (threadIdx.x == 0) s_base[0] = s_base[1] = 0;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i0 = 0; i0 < n; i0 += 256) {
+        const int i = i0 + threadIdx.x;
+        const bool in = i < n;
+        const bool full = in && sorted_ids[(2 * i + 1) * BM] >= 0;
+        const uint32_t b = __ballot_sync(0xffffffffu, full);
+        if (lane == 0) s_warp[warp] = __popc(b);
+        __syncthreads();
+        int before = __popc(b & ((1u << lane) - 1u));
+        for (int w = 0; w < warp; ++w) before += s_warp[w];
+        int total = 0;
+        for (int w = 0; w < 8; ++w) total += s_warp[w];
+        const int base_full = s_base[0], base_tail = s_base[1];
+        if (in) {
+            if (full) pair_list[base_full + before] = i;
+            else tail_list[base_tail + (threadIdx.x - before)] = i;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            s_base[0] = base_full + total;
+            s_base[1] = base_tail + (min(256, n - i0) - total);
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        counts[0] = s_base[0];
+        counts[1] = s_base[1];
+    }
 }
 
 // Shared-memory carve-up (offsets from the 1024-byte aligned base):
@@ -327,7 +379,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 
     if (a.use_pdl) pdl_wait_primary();   // launched as a programmatic dependent of the row-gather kernel
 
-    const int m_blocks = num_row_blocks(a);
+    const int m_blocks = num_tile_rows(a);
     const int n_tiles = a.H / 128;
     const int num_tiles = m_blocks * n_tiles;
     const int ksteps = a.K / BK;
@@ -340,12 +392,13 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             const Coord c = tile_coord(t, m_blocks, n_tiles);
-            const int e = a.expert_ids[c.m_blk];
+            const int mb = tile_row_block(a, c.m_blk);
+            const int e = a.expert_ids[mb];
             int r[4];
-            gather_rows(a, c.m_blk, lane, r);
+            gather_rows(a, mb, lane, r);
             const int row_gate = e * a.N + c.n_tile * 128;
             const int row_up = row_gate + a.H;
-            const bool short_a = a.pregathered != 2 && block_is_short(a, c.m_blk);
+            const bool short_a = a.pregathered != 2 && block_is_short(a, mb);
             const uint32_t fill_bytes =
                 a.pregathered == 2 ? B_BYTES : (short_a ? B_BYTES + SHORT_A_BYTES : STAGE_BYTES);
             for (int ks = 0; ks < ksteps; ++ks) {
@@ -357,7 +410,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BK, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BK, row_up);
                     if (a.pregathered == 1)
-                        tma_load_2d(sm.a(s), short_a ? &map_x_short : &map_x, sm.full(s), ks * BK, c.m_blk * BM);
+                        tma_load_2d(sm.a(s), short_a ? &map_x_short : &map_x, sm.full(s), ks * BK, mb * BM);
                     if (a.l2_ahead && ks + a.l2_ahead < ksteps) {
                         tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_gate);
                         tma_prefetch_l2_2d(&map_w1, (ks + a.l2_ahead) * BK, row_up);
@@ -434,10 +487,11 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int mb = tile_row_block(a, c.m_blk);
             const char *src[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const int pair = a.sorted_ids[c.m_blk * BM + q + 16 * i];
+                const int pair = a.sorted_ids[mb * BM + q + 16 * i];
                 int tok = pair >= 0 ? pair / a.top_k : 0;
                 if (tok >= a.M) tok = 0;
                 src[i] = reinterpret_cast<const char *>(a.x + static_cast<size_t>(tok) * a.K) + chunk * 16;
@@ -479,6 +533,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int mb = tile_row_block(a, c.m_blk);
             const int buf = it & 1;
             if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
             if (!mbar_wait(sm.misc(5), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;  // staging tile free
@@ -492,9 +547,9 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             mbar_arrive(sm.misc(4));        // staging tile written
             if (et == 0) {
                 if (!mbar_wait(sm.misc(4), it & 1, status, ST_TIMEOUT_ACT)) break;
-                const CUtensorMap *st = block_is_short(a, c.m_blk, 2) ? &map_act_short : &map_act;
-                tma_store_2d(st, sm.act, c.n_tile * 128, c.m_blk * BM);
-                tma_store_2d(st, sm.act + ACT_TILE_BYTES / 2, c.n_tile * 128 + 64, c.m_blk * BM);
+                const CUtensorMap *st = block_is_short(a, mb, 2) ? &map_act_short : &map_act;
+                tma_store_2d(st, sm.act, c.n_tile * 128, mb * BM);
+                tma_store_2d(st, sm.act + ACT_TILE_BYTES / 2, c.n_tile * 128 + 64, mb * BM);
                 tma_store_commit();
                 tma_store_wait_read<0>();
                 mbar_arrive(sm.misc(5));
@@ -858,7 +913,7 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
 
     if (a.use_pdl) pdl_wait_primary();  // activations and the zeroed `out` come from the up kernel
 
-    const int m_blocks = num_row_blocks(a);
+    const int m_blocks = num_tile_rows(a);
     const int n_tiles = (a.K + 255) / 256;
     const int num_tiles = m_blocks * n_tiles;
     const int ksteps = a.H / BK;
@@ -871,14 +926,15 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const Coord c = tile_coord(t, m_blocks, n_tiles);
-                const int e = a.expert_ids[c.m_blk];
+            const int mb = tile_row_block(a, c.m_blk);
+                const int e = a.expert_ids[mb];
                 const int w2_row = e * a.K + c.n_tile * 256;
-                const bool short_a = block_is_short(a, c.m_blk);
+                const bool short_a = block_is_short(a, mb);
                 for (int ks = 0; ks < ksteps; ++ks) {
                     ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
                     mbar_arrive_expect_tx(sm.full(s), short_a ? B_BYTES + SHORT_A_BYTES : STAGE_BYTES);
-                    tma_load_2d(sm.a(s), short_a ? &map_act_short : &map_act, sm.full(s), ks * BK, c.m_blk * BM);
+                    tma_load_2d(sm.a(s), short_a ? &map_act_short : &map_act, sm.full(s), ks * BK, mb * BM);
                     tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BK, w2_row);
                     if (a.l2_ahead && ks + a.l2_ahead < ksteps) tma_prefetch_l2_2d(&map_w2, (ks + a.l2_ahead) * BK, w2_row);
                     ++issued;
@@ -931,8 +987,9 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const int mb = tile_row_block(a, c.m_blk);
             const int buf = it & 1;
-            const int pair = a.sorted_ids[c.m_blk * BM + row];
+            const int pair = a.sorted_ids[mb * BM + row];
             const int tok = pair >= 0 ? pair / a.top_k : 0;
             const bool valid = pair >= 0 && tok < a.M;
             const float wgt = valid ? a.topk_weights[pair] : 0.f;
@@ -1247,7 +1304,7 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 
     if (a.use_pdl) pdl_wait_primary();   // up: after the row-gather kernel; down: after the gate/up kernel
 
-    const int m_pairs = num_row_blocks(a) / 2;
+    const int m_pairs = a.pair_list ? a.list_counts[0] : num_row_blocks(a) / 2;
     const int n_tiles = kUp ? a.H / 128 : (a.K + 255) / 256;
     const int num_tiles = m_pairs * n_tiles;
     const int ksteps = (kUp ? a.K : a.H) / BK;
@@ -1260,9 +1317,10 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             bool ok = true;
             for (int t = first; t < num_tiles && ok; t += step) {
                 const Coord c = tile_coord(t, m_pairs, n_tiles);
-                const int blk = 2 * c.m_blk + static_cast<int>(rank);
-                const int e = a.expert_ids[2 * c.m_blk];
-                if (leader && a.expert_ids[2 * c.m_blk + 1] != e) atomicCAS(status, 0, ST_BAD_PAIR);
+            const int pr = a.pair_list ? a.pair_list[c.m_blk] : c.m_blk;   // pair of row blocks 2*pr, 2*pr+1
+                const int blk = 2 * pr + static_cast<int>(rank);
+                const int e = a.expert_ids[2 * pr];
+                if (leader && a.expert_ids[2 * pr + 1] != e) atomicCAS(status, 0, ST_BAD_PAIR);
                 int b_row;
                 if (kUp) b_row = e * a.N + c.n_tile * 128 + (leader ? 0 : a.H);
                 else b_row = e * a.K + c.n_tile * 256 + static_cast<int>(rank) * 128;
@@ -1330,7 +1388,8 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         int it = 0;
         for (int t = first; t < num_tiles; t += step, ++it) {
             const Coord c = tile_coord(t, m_pairs, n_tiles);
-            const int blk = 2 * c.m_blk + static_cast<int>(rank);
+            const int pr = a.pair_list ? a.pair_list[c.m_blk] : c.m_blk;   // pair of row blocks 2*pr, 2*pr+1
+            const int blk = 2 * pr + static_cast<int>(rank);
             const int buf = it & 1;
             const uint32_t empty_leader = mapa_shared(sm.misc(2 + buf), 0);
             const uint32_t acc = tmem_base + buf * 256;
@@ -1587,6 +1646,34 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
             PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, map_act, args));
             return PMOE_OK;
         };
+        // the last pair of an expert whose second block is empty runs as a single 128-row block on the one-CTA
+        // kernels (tcgen05 does not allow cta_group::1 and ::2 in one kernel, hence own launches); PMOE_PAIR_TAILS=0
+        // runs it as a pair like the others
+        const bool tails = pair_tails_enabled();
+        Args ta = a;    // the one-CTA launches over the tail blocks
+        if (tails) {
+            int32_t *lists = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(workspace) +
+                                                         static_cast<size_t>(p.sorted_num) * (H + p.K) * 2);
+            const int max_pairs = max_blocks / 2;
+            pa.pair_list = lists;
+            pa.list_counts = lists + 2 * max_pairs;
+            ta.tail_list = lists + max_pairs;
+            ta.list_counts = pa.list_counts;
+            ta.pregathered = 1;
+            classify_pairs_kernel<<<1, 256, 0, stream>>>(p.sorted_ids, p.npp, p.sorted_num, lists, lists + max_pairs,
+                                                         lists + 2 * max_pairs);
+            PMOE_CUDA_OK(cudaGetLastError());
+        }
+        auto launch_single = [&](auto kernel, const Args &args, int tiles, size_t smem, auto... maps) -> int {
+            if (int rc = set_smem(kernel, smem)) return rc;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(std::min(tiles, sms));
+            cfg.blockDim = dim3(threads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, maps..., args));
+            return PMOE_OK;
+        };
         if (phases & 2) {
             Args up = pa;
             up.zero_out = 1;
@@ -1594,16 +1681,34 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
             if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128),
                                      ACT_TILE_BYTES, up.use_pdl ? 2 : 1))
                 return rc;
+            if (tails) {   // plain launch: starts when the pair kernel (which zeroes `out`) has finished
+                Args tu = ta;
+                tu.use_pdl = 0;
+                if (int rc = launch_single(moe_up_bf16_kernel, tu, (max_blocks / 2) * (H / 128),
+                                           smem_bytes(tu.stages, ACT_TILE_BYTES), map_x, map_w1, map_act, map_x_short,
+                                           map_act_short))
+                    return rc;
+            }
         }
         if (phases & 4) {
             Args dn = pa;
-            dn.use_pdl = (pdl_enabled() && (phases & 2)) ? 1 : 0;
+            dn.use_pdl = (pdl_enabled() && (phases & 2) && !tails) ? 1 : 0;
             dn.bulk_reduce = bulk_reduce ? 1 : 0;
             if (bulk_reduce) dn.stages = std::min(dn.stages, 5);   // room for the reduction staging tile
             if (int rc = launch_pair(moe_pair_bf16_kernel<false>, map_act, map_w2h, dn,
                                      (max_blocks / 2) * ((p.K + 255) / 256), bulk_reduce ? RED_STAGE_BYTES : 0u,
                                      dn.use_pdl ? 2 : 1))
                 return rc;
+            if (tails) {
+                Args td = ta;
+                td.use_pdl = 0;
+                td.bulk_reduce = bulk_reduce ? 1 : 0;
+                if (bulk_reduce) td.stages = std::min(td.stages, 3);
+                if (int rc = launch_single(moe_down_bf16_kernel, td, (max_blocks / 2) * ((p.K + 255) / 256),
+                                           smem_bytes(td.stages, td.bulk_reduce ? RED_STAGE_BYTES : 0u), map_act, map_w2,
+                                           map_act_short))
+                    return rc;
+            }
         }
         return PMOE_OK;
     }
@@ -1702,7 +1807,8 @@ extern "C" size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int s
     }
     size_t bytes = static_cast<size_t>(sorted_num) * (N / 2) * 2;
     if (pmoe::pregather_enabled()) bytes += static_cast<size_t>(sorted_num) * K * 2;
-    return bytes;
+    bytes += (static_cast<size_t>(sorted_num) / 128 + 8) * sizeof(int32_t);   // pair / tail lists of the bpc = 2 pipeline
+    return (bytes + 1023) & ~static_cast<size_t>(1023);
 }
 
 extern "C" int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *w2, void *out,

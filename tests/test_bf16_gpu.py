@@ -61,11 +61,14 @@ def test_knobs(split, bn, wn, stages):
     assert O.max_rel_to_peak(out, ref) <= TOL
 
 
+@pytest.mark.parametrize("tails", ["1", "0"])
 @pytest.mark.parametrize("bn,wn,stages", [(64, 4, 1), (64, 4, 4), (32, 8, 3)])
 @pytest.mark.parametrize("T,K,E,N,k", [(8, 128, 1, 256, 1), (300, 512, 4, 512, 2), (256, 4096, 8, 512, 4),
-                                        (1000, 1024, 16, 768, 8)])
-def test_two_cta_pipeline(T, K, E, N, k, bn, wn, stages):
-    """bpc = 2: CTA pairs with cta_group::2 MMAs on routing tables padded to 256 rows per expert."""
+                                        (1000, 1024, 16, 768, 8), (700, 256, 3, 1024, 1)])
+def test_two_cta_pipeline(T, K, E, N, k, bn, wn, stages, tails, monkeypatch):
+    """bpc = 2: CTA pairs with cta_group::2 MMAs on routing tables padded to 256 rows per expert; by default the
+    half-empty last pair of an expert runs as a single block on the one-CTA kernels (PMOE_PAIR_TAILS)."""
+    monkeypatch.setenv("PMOE_PAIR_TAILS", tails)
     x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=T + stages)
     ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
     out = run_mine(x, w1, w2, ids, wts, True, stages=stages, bn=bn, wn=wn, bpc=2)
