@@ -17,6 +17,13 @@ warm-up. The reference has no CPU implementation of this path - its product is s
 arm runs on the GPU too; the reference's only CPU code for the path, the PyTorch MoE of its tests, is
 timed as `cpu_baseline` (and alone with `--impl cpu`).
 
+After the headline workload the default single-GPU run measures a short fixed SWEEP of the other benchmark
+configurations (c0; c2 at T = 16, 128, 8192 in bf16 and mxfp8; c3 mxfp8; c4 bf16 and mxfp8; `moe_align` alone at the
+c4 and c3 sizes) and attaches it as `sweep`: per entry the step time, TFLOP/s and the roofline of its dominant
+kernel (tensor-bound entries against the measured tensor peak, weight-streaming ones and `moe_align` against the
+measured HBM copy bandwidth). `--impl reference` measures the same entries with the reference's kernels, so every
+entry has the reference's time beside it. `--no-sweep` skips it.
+
 N > 1 (torchrun): expert-parallel mode when the experts divide over the ranks (`--parallel ep`, the default
 then: NCCL all-to-all dispatch / combine), else every rank runs its own batch against a full replica of the
 experts (`--parallel replica`, no collective on the data path). Weak scaling either way.
@@ -63,6 +70,10 @@ def parse_args():
                     help="N > 1: 'ep' shards the experts over the ranks (NCCL all-to-all dispatch/combine, the "
                          "default when the expert count divides), 'replica' runs N independent copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="headline workload only")
+    ap.add_argument("--ep-combine", default="auto", choices=["auto", "nccl", "peer"],
+                    help="expert-parallel combine: NCCL all-to-all, or this library's kernel storing into the source "
+                         "rank's buffer over NVLink (auto = peer when every rank can map its peers)")
     return ap.parse_args()
 
 
@@ -103,7 +114,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.002)
 
     def __enter__(self):
         if self.nv is not None:
@@ -160,7 +171,7 @@ def max_over_ranks(ms: float, world: int, device) -> float:
     return float(t.item())
 
 
-def make_inputs(cfg, seed, device):
+def make_inputs(cfg, seed, device, weights=True):
     """Seeded synthetic batch: x ~ N(0,1) bf16, w1 ~ N(0,1/K), w2 ~ N(0,1/H) bf16 generated on the device;
     routing (distinct experts per token, uniform or Zipf s=1.2) and softmax weights from the CPU oracle's
     generator so that every arm sees identical routing."""
@@ -170,8 +181,10 @@ def make_inputs(cfg, seed, device):
     T, K, E, N, k, routing = cfg
     g = torch.Generator(device=device).manual_seed(seed)
     x = torch.randn(T, K, device=device, generator=g).to(torch.bfloat16)
-    w1 = torch.randn(E, N, K, device=device, generator=g, dtype=torch.bfloat16) * K ** -0.5
-    w2 = torch.randn(E, K, N // 2, device=device, generator=g, dtype=torch.bfloat16) * (N // 2) ** -0.5
+    w1 = w2 = None
+    if weights:
+        w1 = torch.randn(E, N, K, device=device, generator=g, dtype=torch.bfloat16) * K ** -0.5
+        w2 = torch.randn(E, K, N // 2, device=device, generator=g, dtype=torch.bfloat16) * (N // 2) ** -0.5
     ids, wts = O.make_routing(T, E, k, seed + 1, routing)
     return x, w1, w2, ids, wts
 
@@ -186,6 +199,16 @@ def quantize_mx_device(t, block=32):
     inv = torch.exp2((127 - e).float())
     q = (g * inv.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
     return q.reshape(*t.shape[:-1], k).contiguous(), e.to(torch.uint8).view(torch.float8_e8m0fnu)
+
+
+def quantize_mx_weights(w, chunk=16):
+    """`quantize_mx_device` over a weight tensor [E, rows, cols], a few experts at a time (bounded fp32 temporaries)."""
+    import torch
+    qs, ss = [], []
+    for i in range(0, w.shape[0], chunk):
+        q, sc = quantize_mx_device(w[i:i + chunk])
+        qs.append(q), ss.append(sc)
+    return torch.cat(qs), torch.cat(ss)
 
 
 def pack_scales(scales):
@@ -217,8 +240,8 @@ def time_cpu_oracle(x, w1, w2, ids, wts, sample_tokens):
 
 
 def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tflops, flush_buf=None):
-    """Gate/up kernel of the mxfp8 split pipeline timed alone (profiling hook). No fp8 peak was measured on
-    this pool: the denominator is 2 x the measured bf16 burst peak, stated as an assumption."""
+    """Gate/up kernel of the mxfp8 split pipeline timed alone (profiling hook). The denominator is a cuBLASLt
+    block-scaled mxfp8 GEMM timed in the same run (`measure_mxfp8_peak`)."""
     import torch
     T, K, E, N, k, _ = cfg
     xq, xs, w1q, w1s, w2q, w2s = tensors
@@ -298,10 +321,21 @@ def weight_streaming_roofline(roof, cfg, ids, per_kernel_up_ms, ms_step, peaks, 
     return roof
 
 
+_MX_PEAK = None
+
+
 def measure_mxfp8_peak(device):
+    global _MX_PEAK
+    if _MX_PEAK is None:
+        _MX_PEAK = _measure_mxfp8_peak(device)
+    return _MX_PEAK
+
+
+def _measure_mxfp8_peak(device):
     """MEASURED_PEAKS.json has no fp8 figure, so the denominator is measured here the way the bf16 one was:
     cuBLASLt block-scaled (e4m3 x e8m0/32) 8192^3 through torch._scaled_mm, best of 10 (burst).
-    2930 TFLOP/s was measured on this pool (per-tensor-scaled fp8: 3151); used if the call is unavailable."""
+    2930 TFLOP/s (an earlier B200 measurement of the same GEMM; per-tensor-scaled fp8: 3151) is used if the call is
+    unavailable, and the line says so."""
     import torch
     try:
         n = 8192
@@ -323,7 +357,278 @@ def measure_mxfp8_peak(device):
             best = min(best, s.elapsed_time(e))
         return 2.0 * n ** 3 / best / 1e9, "measured in this run (cuBLASLt mxfp8 block-scaled 8192^3, burst)"
     except Exception:
-        return 2930.0, "measured earlier on this pool (cuBLASLt mxfp8 block-scaled 8192^3, burst)"
+        return 2930.0, "earlier B200 measurement (cuBLASLt mxfp8 block-scaled 8192^3, burst); torch._scaled_mm unavailable here"
+
+
+
+# ------------------------------------------------------------------------------------------------
+# sweep: the other benchmark configurations, short runs, one compact entry each
+# ------------------------------------------------------------------------------------------------
+SWEEP = [
+    # (configuration, T override or 0, dtype)
+    ("c0", 0, "bf16"),
+    ("c2", 16, "bf16"), ("c2", 16, "mxfp8"), ("c2", 128, "bf16"), ("c2", 128, "mxfp8"),
+    ("c2", 8192, "bf16"), ("c2", 8192, "mxfp8"),
+    ("c3", 0, "mxfp8"),
+    ("c4", 0, "bf16"), ("c4", 0, "mxfp8"),
+]
+SWEEP_ALIGN = ["c4", "c3"]
+
+
+def build_sweep_case(name, tokens, dtype, device):
+    """Seeded inputs of one sweep entry, generated on the device 16 experts at a time so that the bf16 originals of
+    a large mxfp8 layer never exist all at once. Both arms call this, so they see identical tensors."""
+    import torch
+    sys.path.insert(0, str(ROOT))
+    from oracle import moe_oracle as O
+    T, K, E, N, k, routing = CONFIGS[name]
+    if tokens:
+        T = tokens
+    seed = 4321 + sorted(CONFIGS).index(name)
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(T, K, device=device, generator=g).to(torch.bfloat16)
+    mx = dtype == "mxfp8"
+    w1p, w2p, w1sp, w2sp = [], [], [], []
+    for e0 in range(0, E, 16):
+        n = min(16, E - e0)
+        a = torch.randn(n, N, K, device=device, generator=g, dtype=torch.bfloat16) * K ** -0.5
+        b = torch.randn(n, K, N // 2, device=device, generator=g, dtype=torch.bfloat16) * (N // 2) ** -0.5
+        if mx:
+            q, sc = quantize_mx_device(a)
+            w1p.append(q), w1sp.append(pack_scales(sc))
+            q, sc = quantize_mx_device(b)
+            w2p.append(q), w2sp.append(pack_scales(sc))
+        else:
+            w1p.append(a), w2p.append(b)
+    ids, wts = O.make_routing(T, E, k, seed + 1, routing)
+    case = {"cfg": (T, K, E, N, k, routing), "ids_cpu": ids, "ids": ids.to(device), "wts": wts.to(device), "x": x,
+            "w1": torch.cat(w1p), "w2": torch.cat(w2p)}
+    if mx:
+        case["w1s"], case["w2s"] = torch.cat(w1sp), torch.cat(w2sp)
+        case["xq"], case["xs"] = quantize_mx_device(x)
+    return case
+
+
+def time_steps(step, steps, flush_buf):
+    """Mean ms of `step` (3 warm-up calls first): back to back, or with the L2 flushed before every timed call."""
+    return time_calls(step, steps, flush_buf)
+
+
+def sweep_entry_ours(name, tokens, dtype, device, peaks, stages):
+    import torch
+    from prime_flash_moe_b200 import capi
+    ops = torch.ops.prime_moe
+    mx = dtype == "mxfp8"
+    c = build_sweep_case(name, tokens, dtype, device)
+    T, K, E, N, k, routing = c["cfg"]
+    bpc = 2 if (not mx and N >= 8192) else 1
+    out = torch.empty(T, K, dtype=torch.bfloat16, device=device)
+    touched = int(c["ids_cpu"].unique().numel())
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device) if \
+        touched * (N * K + K * (N // 2)) * (1 if mx else 2) < (256 << 20) else None
+
+    def step():
+        s, e, n = ops.moe_align(c["ids"], E, 128, bpc)
+        if mx:
+            ops.fused_moe_mxfp8(c["xq"], c["xs"], c["w1"], c["w1s"], c["w2"], c["w2s"], s, e, n, c["wts"], out, k, 128, 64, 4,
+                                stages, bpc, True)
+        else:
+            ops.fused_moe_bf16(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k, 128, 64, 4, stages, bpc, 1, True)
+
+    flops = 3.0 * T * k * K * N
+    steps = 20 if flops < 5e12 else 8
+    ms = time_steps(step, steps, flush_buf)
+    # the gate/up kernel alone (2/3 of the FLOPs, and of the weight bytes) through the profiling hook
+    lib = capi.lib()
+    s, e, n = ops.moe_align(c["ids"], E, 128, bpc)
+    wsb = (lib.pmoe_fused_moe_mxfp8_workspace_bytes if mx else lib.pmoe_fused_moe_bf16_workspace_bytes)(T, K, N, s.numel(), 1)
+    ws = torch.empty(wsb + 1024, dtype=torch.uint8, device=device)
+    off = (-ws.data_ptr()) % 1024
+    ws = ws[off:off + wsb]
+    if mx:
+        call = lambda: capi.fused_moe_mxfp8(c["xq"], c["xs"], c["w1"], c["w1s"], c["w2"], c["w2s"], s, e, n, c["wts"], out, k,
+                                            128, 64, 4, stages, bpc, True, workspace=ws)
+    else:
+        call = lambda: capi.fused_moe_bf16(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k, 128, 64, 4, stages, bpc, 1,
+                                           True, workspace=ws)
+    lib.pmoe_debug_set_phase_mask(2)
+    up_ms = time_calls(call, 10, flush_buf)
+    lib.pmoe_debug_set_phase_mask(4)
+    down_ms = time_calls(call, 10, flush_buf)
+    lib.pmoe_debug_set_phase_mask(7)
+    call()
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0, "a kernel recorded an error status"
+    wb = (1.0 + 1.0 / 32) if mx else 2.0
+    up_bytes = touched * N * K * wb + T * k * K * wb + T * k * (N // 2) * wb + T * K * 2
+    kernel = ("moe_up_mxfp8_kernel" if mx else ("moe_pair_bf16_kernel<up>" if bpc == 2 else "moe_up_bf16_kernel (or its "
+              "two-block variant)"))
+    if T * k >= 256 * E:       # compute-bound call: tensor roofline of the gate/up kernel
+        peak, src = measure_mxfp8_peak(device) if mx else (peaks["bf16_tflops"], peaks["source"] + " (burst cuBLAS bf16)")
+        ach = 2.0 * T * k * K * N / (up_ms * 1e-3) / 1e12
+        roof = {"kernel": kernel, "bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                "peak_source": src, "traffic": None, "algorithmic_bytes": up_bytes}
+    else:                      # weight streaming: the experts actually routed to, at the measured copy bandwidth
+        ach = up_bytes / (up_ms * 1e-3) / 1e9
+        roof = {"kernel": kernel, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"] + " (STREAM-style copy)", "traffic": None,
+                "algorithmic_bytes": up_bytes, "experts_touched": touched}
+    roof["kernel_ms"] = {"up": up_ms, "down": down_ms}
+    del c, ws, out, flush_buf
+    torch.cuda.empty_cache()
+    return {"config": name, "tokens": T, "dtype": dtype, "ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "tokens_per_s": T / (ms * 1e-3), "l2_flushed": touched * (N * K + K * (N // 2)) * (1 if mx else 2) < (256 << 20),
+            "roofline": roof}
+
+
+def sweep_entry_reference(name, tokens, dtype, device, ref_pkg):
+    import torch
+    ops = torch.ops.prime_moe
+    mx = dtype == "mxfp8"
+    c = build_sweep_case(name, tokens, dtype, device)
+    T, K, E, N, k, routing = c["cfg"]
+    out = torch.zeros(T, K, dtype=torch.bfloat16, device=device)
+    touched = int(c["ids_cpu"].unique().numel())
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device) if \
+        touched * (N * K + K * (N // 2)) * (1 if mx else 2) < (256 << 20) else None
+    flops = 3.0 * T * k * K * N
+    best = None
+    for split in (True, False):
+        for bn, wn in ((64, 4), (32, 8)):
+            for stages in (1, 2, 3, 4):
+                def cand(split=split, bn=bn, wn=wn, stages=stages):
+                    s, e, n = ops.moe_align(c["ids"], E, 128, 1)
+                    if not split:
+                        out.zero_()
+                    if mx:
+                        ref_pkg.fused_moe_mxfp8(c["xq"], c["xs"], c["w1"], c["w1s"], c["w2"], c["w2s"], s, e, n, c["wts"], out, k,
+                                                128, bn, wn, stages, 1, split)
+                    else:
+                        ref_pkg.fused_moe_bf16(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k, 128, bn, wn, stages, 1, 1, split)
+                try:
+                    cand()
+                    torch.cuda.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(2):
+                        cand()
+                    b.record()
+                    torch.cuda.synchronize()
+                    ms = a.elapsed_time(b) / 2
+                except Exception:
+                    continue
+                if best is None or ms < best[0]:
+                    best = (ms, cand, {"block_n": bn, "warp_n": wn, "stages": stages, "split": split})
+    if best is None:
+        return {"config": name, "tokens": T, "dtype": dtype, "unavailable": "every knob setting of the reference failed"}
+    ms = time_steps(best[1], 20 if flops < 5e12 else 8, flush_buf)
+    del c, out, flush_buf
+    torch.cuda.empty_cache()
+    return {"config": name, "tokens": T, "dtype": dtype, "ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "tokens_per_s": T / (ms * 1e-3), "knobs": best[2]}
+
+
+def sweep_align_entry(name, device, peaks, kernel_name):
+    """`moe_align` alone on the routing table of a configuration: L2 flushed before every call, achieved GB/s
+    over its algorithmic bytes 4n read + 4(max_padded + max_blocks + 1) written."""
+    import torch
+    sys.path.insert(0, str(ROOT))
+    from oracle import moe_oracle as O
+    ops = torch.ops.prime_moe
+    T, K, E, N, k, routing = CONFIGS[name]
+    ids, _ = O.make_routing(T, E, k, 4321 + sorted(CONFIGS).index(name) + 1, routing)
+    ids = ids.to(device)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    ms = time_calls(lambda: ops.moe_align(ids, E, 128, 1), 30, flush_buf)
+    n = T * k
+    max_padded = (n + E * 127 + 127) // 128 * 128
+    nbytes = 4.0 * n + 4.0 * (max_padded + max_padded // 128 + 1)
+    ach = nbytes / (ms * 1e-3) / 1e9
+    del flush_buf
+    torch.cuda.empty_cache()
+    return {"config": name, "op": "moe_align", "n": n, "num_experts": E, "dtype": "int32", "ms_per_step": ms,
+            "value": ach, "unit": "GB/s",
+            "roofline": {"kernel": kernel_name, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"] + " (STREAM-style copy)",
+                         "traffic": None, "algorithmic_bytes": nbytes}}
+
+
+def ep_sweep_entry(name, dtype, rank, world, device, args):
+    """One expert-parallel entry beside the headline of an N-GPU run: configuration 3 (DeepSeek-V3 layer, mxfp8),
+    T tokens per rank, E / N experts per rank. Every rank generates only its own experts (16 at a time, seeded by
+    the chunk's global index, so the layer is the same whatever N is)."""
+    import torch
+    sys.path.insert(0, str(ROOT))
+    from oracle import moe_oracle as O
+    from prime_flash_moe_b200 import ep
+    T, K, E, N, k, routing = CONFIGS[name]
+    per = E // world
+    w1q, w1s, w2q, w2s = [], [], [], []
+    for e0 in range(rank * per, (rank + 1) * per, 16):
+        n = min(16, (rank + 1) * per - e0)
+        g = torch.Generator(device=device).manual_seed(777 + e0)
+        a = torch.randn(n, N, K, device=device, generator=g, dtype=torch.bfloat16) * K ** -0.5
+        b = torch.randn(n, K, N // 2, device=device, generator=g, dtype=torch.bfloat16) * (N // 2) ** -0.5
+        q, sc = quantize_mx_device(a)
+        w1q.append(q), w1s.append(pack_scales(sc))
+        q, sc = quantize_mx_device(b)
+        w2q.append(q), w2s.append(pack_scales(sc))
+        del a, b
+    experts = ep.LocalExperts(torch.cat(w1q), torch.cat(w2q), torch.cat(w1s), torch.cat(w2s), stages=args.stages)
+    layer = ep.ExpertParallelMoE(E, experts, combine=args.ep_combine)
+    g = torch.Generator(device=device).manual_seed(888 + rank)
+    xq, xs = quantize_mx_device(torch.randn(T, K, device=device, generator=g).to(torch.bfloat16))
+    ids, wts = O.make_routing(T, E, k, 889 + rank, routing)
+    ids, wts = ids.to(device), wts.to(device)
+    for _ in range(3):
+        out = layer(xq, ids, wts, xs)
+    barrier_sync(world)
+    steps = 10
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        out = layer(xq, ids, wts, xs)
+    b.record()
+    barrier_sync(world)
+    ms = max_over_ranks(a.elapsed_time(b), world, device) / steps
+    flops = 3.0 * T * k * K * N
+    return {"config": name, "tokens": T, "dtype": dtype, "parallelism": f"ep{world}", "ms_per_step": ms,
+            "value": world * flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "tokens_per_s": world * T / (ms * 1e-3),
+            "experts_per_rank": per, "rows_computed_by_rank0": layer.last_recv_rows, "rows_sent_by_rank0": layer.last_sent_rows,
+            "combine": layer.combine_mode, "finite": bool(torch.isfinite(out.float()).all())}
+
+
+def run_sweep(impl, device, peaks, stages, ref_pkg=None):
+    entries = []
+    for name, tokens, dtype in SWEEP:
+        try:
+            if impl == "ours":
+                entries.append(sweep_entry_ours(name, tokens, dtype, device, peaks, stages))
+            else:
+                entries.append(sweep_entry_reference(name, tokens, dtype, device, ref_pkg))
+        except Exception as exc:            # an entry that fails is reported, not hidden
+            entries.append({"config": name, "tokens": tokens, "dtype": dtype, "error": f"{type(exc).__name__}: {exc}"[:200]})
+    for name in SWEEP_ALIGN:
+        try:
+            entries.append(sweep_align_entry(name, device, peaks, "moe_align_{hist,scan,scatter}_kernel" if impl == "ours"
+                                             else "the reference's moe_align_kernel"))
+        except Exception as exc:
+            entries.append({"config": name, "op": "moe_align", "error": f"{type(exc).__name__}: {exc}"[:200]})
+    return entries
+
+
+def sweep_summary(entries):
+    """One short string per entry for readers that keep scalar fields only."""
+    parts = []
+    for e in entries:
+        tag = f"{e['config']}" + (f"/T{e['tokens']}" if e.get("tokens") else "") + f"/{e.get('op', e.get('dtype'))}"
+        if "ms_per_step" not in e:
+            parts.append(f"{tag}: failed")
+            continue
+        r = e.get("roofline")
+        parts.append(f"{tag}: {e['ms_per_step'] * 1e3:.0f}us {e['value']:.0f}{e['unit']}" +
+                     (f" {r['bound']} frac {r['frac']:.2f}" if r else ""))
+    return "; ".join(parts)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -341,19 +646,20 @@ def run_gpu_arm(args, impl):
         cfg[0] = args.tokens
     T, K, E, N, k, routing = cfg
     mx = args.dtype == "mxfp8"
-    x, w1, w2, ids_cpu, wts_cpu = make_inputs(cfg, 1234 + rank, device)
+    ep_mode = impl == "ours" and args.parallel == "ep"
+    x, w1, w2, ids_cpu, wts_cpu = make_inputs(cfg, 1234 + rank, device, weights=not ep_mode)
     ids, wts = ids_cpu.to(device), wts_cpu.to(device)
     out = torch.zeros(T, K, dtype=torch.bfloat16, device=device)
     flops = 3.0 * T * k * K * N
     if mx:
         # OCP-MX operands computed from the bf16 tensors: e4m3 values + e8m0 scale per 32 K-elements
         xq, xs = quantize_mx_device(x)
-        w1q, w1s = quantize_mx_device(w1)
-        w2q, w2s = quantize_mx_device(w2)
-        w1s, w2s = pack_scales(w1s), pack_scales(w2s)
+        if not ep_mode:
+            w1q, w1s = quantize_mx_weights(w1)
+            w2q, w2s = quantize_mx_weights(w2)
+            w1s, w2s = pack_scales(w1s), pack_scales(w2s)
 
     xin = (xq, xs) if mx else x      # what a step consumes as its activation input
-    ep_mode = impl == "ours" and args.parallel == "ep"
     if ep_mode:
         # expert parallel: every rank generated the SAME full weights (seed 99), keeps its E/world experts,
         # and runs its own T tokens; dispatch / combine are NCCL all-to-alls (prime_flash_moe_b200/ep.py)
@@ -364,15 +670,31 @@ def run_gpu_arm(args, impl):
         w1 = torch.randn(E, N, K, device=device, generator=gw, dtype=torch.bfloat16) * K ** -0.5
         w2 = torch.randn(E, K, N // 2, device=device, generator=gw, dtype=torch.bfloat16) * (N // 2) ** -0.5
         if mx:
-            w1q, w1s = quantize_mx_device(ep.shard_experts(w1, rank, world))
-            w2q, w2s = quantize_mx_device(ep.shard_experts(w2, rank, world))
+            w1q, w1s = quantize_mx_weights(ep.shard_experts(w1, rank, world))
+            w2q, w2s = quantize_mx_weights(ep.shard_experts(w2, rank, world))
             experts = ep.LocalExperts(w1q, w2q, pack_scales(w1s), pack_scales(w2s), stages=args.stages)
         else:
             experts = ep.LocalExperts(ep.shard_experts(w1, rank, world), ep.shard_experts(w2, rank, world),
                                       stages=args.stages)
+        # correctness figure carried by every expert-parallel line: the first 64 tokens of this rank through the plain
+        # single-GPU operator on the FULL weights, compared below with the same rows of the expert-parallel result
+        ops = torch.ops.prime_moe
+        np_ = min(64, T)
+        par_ref = torch.empty(np_, K, dtype=torch.bfloat16, device=device)
+        ps, pe, pn = ops.moe_align(ids[:np_].contiguous(), E, 128, 1)
+        if mx:
+            fw1q, fw1s = quantize_mx_weights(w1)
+            fw2q, fw2s = quantize_mx_weights(w2)
+            ops.fused_moe_mxfp8(xq[:np_].contiguous(), xs[:np_].contiguous(), fw1q, pack_scales(fw1s), fw2q, pack_scales(fw2s),
+                                ps, pe, pn, wts[:np_].contiguous().view(-1), par_ref, k, 128, 64, 4, args.stages, 1, True)
+            del fw1q, fw1s, fw2q, fw2s
+        else:
+            ops.fused_moe_bf16(x[:np_].contiguous(), w1, w2, ps, pe, pn, wts[:np_].contiguous().view(-1), par_ref, k, 128, 64,
+                               4, args.stages, 1, 1, True)
+        torch.cuda.synchronize()
         del w1, w2
         torch.cuda.empty_cache()
-        layer = ep.ExpertParallelMoE(E, experts)
+        layer = ep.ExpertParallelMoE(E, experts, combine=args.ep_combine)
         launches_per_step = None
         ep_rows = []
 
@@ -559,7 +881,8 @@ def run_gpu_arm(args, impl):
         up_flops = 2.0 * T * k * K * N
         achieved = up_flops / (per_kernel["moe_up_bf16"] * 1e-3) / 1e12
         # DRAM bytes of one launch of that kernel, from the ncu captures summarised under profiles/
-        traffic = {("c1", 2): 5.379e9, ("c2", 1): 1.112e9}.get((args.config, args.bpc)) if not args.tokens else None
+        traffic = {("c1", 2): 5.379e9, ("c2", 1): 1.112e9}.get((args.config, args.bpc)) \
+            if (not args.tokens and args.stages == 4 and args.warp_n == 4) else None
         roofline = {"kernel": "moe_pair_bf16_kernel<up>" if args.bpc == 2 else "moe_up_bf16_kernel", "bound": "tensor",
                     "achieved": achieved,
                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
@@ -579,9 +902,28 @@ def run_gpu_arm(args, impl):
                         "sample": f"first {sample} of {T} tokens of the same batch, torch CPU grouped_mm oracle, "
                                   f"{secs:.2f} s", "host_cpus": os.cpu_count()}
 
+    ep_parity = None
     if ep_mode:
         # kernels of this package per step: plan (3) + moe_align (1 or 3) + row gather, gate/up, down (3) + combine (1)
         launches_per_step = 3 + (3 if (ep_rows[-1] if ep_rows else 0) * k > 4096 else 1) + 3 + 1
+        step(xin, ids, wts, out)
+        torch.cuda.synchronize()
+        a_, b_ = out[:np_].float(), par_ref.float()
+        ep_parity = max_over_ranks(float((a_ - b_).abs().max() / b_.abs().max().clamp_min(1e-30)), world, device)
+    sweep = None
+    default_run = (args.config == "c1" and not args.tokens and args.dtype == "bf16" and args.split and world == 1)
+    if default_run and not args.no_sweep:
+        # the other configurations, after the headline's tensors are gone
+        x = w1 = w2 = xin = out = outs = dxs = houts = hx = flush_buf = None
+        if impl == "ours":
+            ws = call = None
+        torch.cuda.empty_cache()
+        sweep = run_sweep(impl, device, peaks, args.stages, ref_pkg if impl == "reference" else None)
+    elif ep_mode and not args.no_sweep and args.config == "c1" and CONFIGS["c3"][2] % world == 0:
+        x = xin = out = outs = dxs = houts = hx = flush_buf = layer = experts = None
+        torch.cuda.empty_cache()
+        sweep = [ep_sweep_entry("c3", "mxfp8", rank, world, device, args)]
+
     if rank == 0:
         line = {
             "metric": "moe_ffn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": ref_world, "steps": args.steps,
@@ -602,10 +944,18 @@ def run_gpu_arm(args, impl):
             line["config"]["ep"] = {"rows_computed_by_rank0_last_step": ep_rows[-1] if ep_rows else None,
                                     "rows_sent_by_rank0_last_step": layer.last_sent_rows, "routes_per_rank": T * k,
                                     "tokens_per_rank": T,
+                                    "parity": ep_parity,
+                                    "parity_what": "max over ranks of max|ep_out - single_gpu_out| / max|single_gpu_out| on each "
+                                                   "rank's first 64 tokens (single-GPU operator on the full weights)",
+                                    "combine": layer.combine_mode,
                                     "collective": "NCCL all-to-all (dispatch + combine), one row per (token, rank) visit"}
         if impl == "reference":
             line["impl"] = "reference"
             line["gpu_launches"] = None
+        line["clocks"]["ms_per_step_x_sm_mhz"] = (ms_step * line["clocks"]["sm_mhz"]) if line["clocks"]["sm_mhz"] else None
+        if sweep is not None:
+            line["config"]["sweep"] = sweep_summary(sweep)
+            line["sweep"] = sweep          # last key of the line
         print(json.dumps(line))
 
 

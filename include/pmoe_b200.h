@@ -147,6 +147,30 @@ int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, 
                             size_t workspace_bytes, pmoe_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The two steps that precede the fused MoE FFN in a model. Neither has a counterpart in the reference, which
+ * leaves both to the caller: routing ("routing comes from your gate", README.md:147; the op contract for the two
+ * tensors is prime_moe/csrc/torch_interface.cpp:77-110, :112-180) and activation quantisation (README.md:110-113;
+ * the arithmetic matched bit for bit is the reference's test quantiser, test/test_mxfp8.py:21-38).
+ *
+ * pmoe_route_topk: router logits [T, num_experts] (fp32 or bf16, row major) -> topk_ids int32[T, top_k] and
+ *   topk_weights fp32[T, top_k], one pass over the logits. Experts are listed by descending logit; equal logits
+ *   go to the lower expert index. renormalize != 0: weights = softmax over the top_k selected logits (they sum
+ *   to 1, the convention of the benchmark configurations); renormalize == 0: the selected entries of the softmax
+ *   over all experts. top_k <= min(32, num_experts), num_experts <= 1024.
+ *
+ * pmoe_quantize_mx: bf16 rows -> OCP-MX: q e4m3[rows, K] and scales e8m0[rows, K/32] (row major, one scale per
+ *   32 elements: e = clamp(exponent(amax) - 8, 0, 254), q = satfinite_e4m3(v * 2^(127 - e))), the layout
+ *   pmoe_fused_moe_mxfp8 takes as x / x_scales. row_index == NULL: output row r is x[r] (rows <= src_rows).
+ *   row_index int32[rows]: output row r is x[row_index[r]] - the expert-parallel dispatch gather and the
+ *   quantiser in one pass; an index outside [0, src_rows) yields a row of zeros. K % 32 == 0; x 16-byte and
+ *   q 8-byte aligned. */
+enum { PMOE_DTYPE_F32 = 0, PMOE_DTYPE_BF16 = 1 };
+int pmoe_route_topk(const void *logits, int logits_dtype, int T, int num_experts, int top_k, int renormalize,
+                    int32_t *topk_ids, float *topk_weights, pmoe_stream_t stream);
+int pmoe_quantize_mx(const void *x /* bf16[src_rows, K] */, const int32_t *row_index, int src_rows, void *q,
+                     void *scales, int rows, int K, pmoe_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Expert-parallel glue (no counterpart in the reference, which is single-GPU). Experts are sharded
  * contiguously over `world` ranks (num_experts / world each). The unit of exchange is a VISIT: a (token,
  * destination rank) pair such that at least one of the token's top_k experts lives on that rank.
@@ -174,7 +198,13 @@ int pmoe_ep_combine(const void *y, const int32_t *slot_of, void *out, int T, int
  * device status word and the kernel unwinds. These two calls synchronise the current device.
  * No counterpart in the reference (its waits are unbounded, tcgen05_prelude.cuh:404-414).
  *   pmoe_device_status: *status = first recorded code (0 = none); returns PMOE_OK, or
- *   PMOE_ERR_DEVICE when *status != 0.   pmoe_reset_device_status: clears the word. */
+ *   PMOE_ERR_DEVICE when *status != 0.   pmoe_reset_device_status: clears the word.
+ * The word is STICKY: once a code is recorded, every later kernel on that device gives up any wait that needs
+ * more than a few polls, so its `out` is incomplete although the call returned PMOE_OK. Nothing but these two
+ * calls reads the word (the launch path never synchronises): a host that wants to detect an expired wait calls
+ * pmoe_device_status at a point where a synchronisation is acceptable (end of a step), treats every result
+ * produced since the previous check as invalid when it is non-zero, and calls pmoe_reset_device_status before
+ * going on. */
 int pmoe_device_status(int *status /* host pointer */);
 int pmoe_reset_device_status(void);
 
@@ -188,6 +218,20 @@ int pmoe_debug_set_phase_mask(int mask);
  * shared-memory ring into L2 (0 = off, the default; initial value from PMOE_L2_AHEAD). Returns the
  * previous value. No counterpart in the reference. */
 int pmoe_debug_set_l2_ahead(int ksteps);
+
+/* Test hooks for the bounded waits, per device (the current one). No counterpart in the reference.
+ *   pmoe_debug_set_wait_ns: limit of every in-kernel wait in nanoseconds (default 2 s; 1 us .. 60 s).
+ *   pmoe_debug_wait_probe: launches a one-CTA kernel that waits on a barrier nothing arrives on; after the
+ *   current limit it records status 9 and ends through its normal exit, so pmoe_device_status then reports
+ *   PMOE_ERR_DEVICE until pmoe_reset_device_status. It touches no GEMM kernel and no user memory. */
+int pmoe_debug_set_wait_ns(unsigned long long ns);
+int pmoe_debug_wait_probe(pmoe_stream_t stream);
+
+/* Test hook: the number of workspace bytes the bf16 launcher would touch for this problem under the current
+ * environment (PMOE_PREGATHER, PMOE_AGATHER, PMOE_PAIR_TAILS); never more than
+ * pmoe_fused_moe_bf16_workspace_bytes of the same problem. Host only, no device work. */
+size_t pmoe_debug_bf16_workspace_extent(int M, int K, int N, int num_experts, int top_k, int sorted_num, int bpc,
+                                        int split);
 
 #ifdef __cplusplus
 }

@@ -85,6 +85,21 @@ def moe_align(topk_ids, num_experts, block_m=128, bpc=1):
     return torch.ops.prime_moe.moe_align(topk_ids, num_experts, block_m, bpc)
 
 
+def route_topk(logits, top_k, renormalize=True):
+    """Router: logits ``[T, E]`` (fp32 or bf16) -> ``(topk_ids int32 [T, top_k], topk_weights fp32 [T, top_k])`` in
+    one pass, experts by descending logit (ties to the lower index); ``renormalize`` = softmax over the selected
+    logits, else the selected entries of the softmax over all experts. Not in the reference, which takes both
+    tensors from the caller's gate (README.md:147)."""
+    return torch.ops.prime_moe.route_topk(logits, top_k, renormalize)
+
+
+def quantize_mx(x, row_index=None):
+    """bf16 ``[T, K]`` -> OCP-MX ``(e4m3 [R, K], e8m0 [R, K/32])`` as ``fused_moe_mxfp8`` takes ``x`` / ``x_scales``;
+    with ``row_index`` int32 ``[R]`` output row r is ``x[row_index[r]]``. Bit-identical to the reference's test
+    quantiser (test/test_mxfp8.py:21-38), which the reference leaves to the caller (README.md:110-113)."""
+    return torch.ops.prime_moe.quantize_mx(x, row_index)
+
+
 def pack_scales_blocked(scales: torch.Tensor) -> torch.Tensor:
     """Row-major e8m0 scales ``(..., MN, K/32)`` -> the blocked layout the kernels read
     (prime_moe/__init__.py:106-115): 512-byte tiles covering 128 rows x 4 scale columns, tile index
@@ -99,4 +114,4 @@ def pack_scales_blocked(scales: torch.Tensor) -> torch.Tensor:
     return tiles.reshape(*lead, -1).view(torch.float8_e8m0fnu)
 
 
-__all__ = ["fused_moe_bf16", "fused_moe_mxfp8", "moe_align", "pack_scales_blocked", "BLOCK"]
+__all__ = ["fused_moe_bf16", "fused_moe_mxfp8", "moe_align", "pack_scales_blocked", "route_topk", "quantize_mx", "BLOCK"]

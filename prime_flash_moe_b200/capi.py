@@ -37,6 +37,11 @@ SIGNATURES = {
     "pmoe_reset_device_status": (_i, []),
     "pmoe_debug_set_phase_mask": (_i, [_i]),
     "pmoe_debug_set_l2_ahead": (_i, [_i]),
+    "pmoe_route_topk": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "pmoe_quantize_mx": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
+    "pmoe_debug_set_wait_ns": (_i, [C.c_ulonglong]),
+    "pmoe_debug_wait_probe": (_i, [_vp]),
+    "pmoe_debug_bf16_workspace_extent": (_sz, [_i] * 8),
 }
 
 _lib = None
@@ -115,6 +120,31 @@ def fused_moe_mxfp8(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, e
             _check(lib().pmoe_fused_moe_mxfp8_ws(*common, _p(workspace),
                                                  workspace.numel() * workspace.element_size(), _stream()))
     return out
+
+
+def route_topk(logits: torch.Tensor, top_k: int, renormalize: bool = True):
+    """``(topk_ids int32 [T, top_k], topk_weights fp32 [T, top_k])`` from router logits ``[T, E]`` (fp32 or bf16)."""
+    assert logits.is_cuda and logits.dim() == 2 and logits.is_contiguous()
+    dtype = {torch.float32: 0, torch.bfloat16: 1}[logits.dtype]
+    T, E = logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    wts = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _check(lib().pmoe_route_topk(_p(logits), dtype, T, E, top_k, int(renormalize), _p(ids), _p(wts), _stream()))
+    return ids, wts
+
+
+def quantize_mx(x: torch.Tensor, row_index: torch.Tensor | None = None):
+    """bf16 ``[T, K]`` -> ``(e4m3 [R, K], e8m0 [R, K/32])``; with ``row_index`` int32 ``[R]`` output row r is
+    ``x[row_index[r]]`` (gather and quantiser in one pass), else R = T."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    T, K = x.shape
+    R = T if row_index is None else row_index.numel()
+    q = torch.empty(R, K, dtype=torch.float8_e4m3fn, device=x.device)
+    sc = torch.empty(R, K // 32, dtype=torch.float8_e8m0fnu, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib().pmoe_quantize_mx(_p(x), _p(row_index), T, _p(q), _p(sc), R, K, _stream()))
+    return q, sc
 
 
 def device_status() -> int:

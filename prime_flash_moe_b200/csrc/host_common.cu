@@ -11,7 +11,24 @@
 
 #include <mutex>
 
+#include "ptx.cuh"
+
 namespace pmoe {
+
+// status word of the kernels of this translation unit (the wait probe)
+__device__ int g_status_misc = 0;
+
+// One CTA, one thread: waits on an mbarrier that nothing ever arrives on, so the bounded wait runs out after
+// the current limit (pmoe_debug_set_wait_ns), records ST_TIMEOUT_PROBE and the kernel ends through its normal
+// exit. Exercises exactly the wait every GEMM kernel of this library uses, without involving one.
+__global__ void wait_probe_kernel() {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+        (void)mbar_wait(smem_u32(&bar), 0, &g_status_misc, ST_TIMEOUT_PROBE);
+    }
+}
 
 namespace {
 thread_local char g_error[512] = "";
@@ -150,16 +167,24 @@ int short_boxes_mode() {
 static int g_phase_mask = 7;
 int phase_mask() { return g_phase_mask; }
 
-bool pregather_enabled() {
-    static const bool on = [] {
-        const char *e = getenv("PMOE_PREGATHER");
-        return !(e && e[0] == '0');
-    }();
-    return on;
+bool pregather_enabled() {   // read on every call, like the other per-call switches
+    const char *e = getenv("PMOE_PREGATHER");
+    return !(e && e[0] == '0');
 }
 
 int status_fetch_bf16(int *value, bool reset);
 int status_fetch_mxfp8(int *value, bool reset);
+int wait_ns_store_bf16(unsigned long long ns);
+int wait_ns_store_mxfp8(unsigned long long ns);
+
+static int status_fetch_misc(int *value, bool reset) {
+    if (value) PMOE_CUDA_OK(cudaMemcpyFromSymbol(value, g_status_misc, sizeof(int)));
+    if (reset) {
+        const int zero = 0;
+        PMOE_CUDA_OK(cudaMemcpyToSymbol(g_status_misc, &zero, sizeof(int)));
+    }
+    return PMOE_OK;
+}
 
 }  // namespace pmoe
 
@@ -183,10 +208,11 @@ extern "C" int pmoe_device_status(int *status) {
     using namespace pmoe;
     PMOE_REQUIRE(status != nullptr, PMOE_ERR_BAD_ARG, "pmoe_device_status: null pointer");
     PMOE_CUDA_OK(cudaDeviceSynchronize());
-    int a = 0, b = 0;
+    int a = 0, b = 0, c = 0;
     if (int rc = status_fetch_bf16(&a, false)) return rc;
     if (int rc = status_fetch_mxfp8(&b, false)) return rc;
-    *status = a ? a : b;
+    if (int rc = status_fetch_misc(&c, false)) return rc;
+    *status = a ? a : (b ? b : c);
     if (*status) return set_error(PMOE_ERR_DEVICE, "a kernel gave up a bounded wait (device status %d)", *status);
     return PMOE_OK;
 }
@@ -195,5 +221,23 @@ extern "C" int pmoe_reset_device_status(void) {
     using namespace pmoe;
     PMOE_CUDA_OK(cudaDeviceSynchronize());
     if (int rc = status_fetch_bf16(nullptr, true)) return rc;
-    return status_fetch_mxfp8(nullptr, true);
+    if (int rc = status_fetch_mxfp8(nullptr, true)) return rc;
+    return status_fetch_misc(nullptr, true);
+}
+
+extern "C" int pmoe_debug_set_wait_ns(unsigned long long ns) {
+    using namespace pmoe;
+    PMOE_REQUIRE(ns >= 1000ull && ns <= 60000000000ull, PMOE_ERR_BAD_ARG,
+                 "pmoe_debug_set_wait_ns: the limit must lie between 1 microsecond and 60 seconds");
+    if (int rc = wait_ns_store_bf16(ns)) return rc;
+    if (int rc = wait_ns_store_mxfp8(ns)) return rc;
+    PMOE_CUDA_OK(cudaMemcpyToSymbol(g_wait_ns, &ns, sizeof(ns)));
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_debug_wait_probe(pmoe_stream_t stream) {
+    using namespace pmoe;
+    wait_probe_kernel<<<1, 32, 0, stream>>>();
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
 }

@@ -352,8 +352,6 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_threads = a.epi_warps * 32;
 
-    pdl_launch_dependents();  // the dependent grid still waits for this whole grid before reading
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), a.pregathered == 2 ? 1 + GATHER_THREADS : 1);
@@ -376,6 +374,11 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    // Dependents may be scheduled only now that this CTA holds its tensor memory: a dependent CTA that
+    // shares this SM then blocks in its own allocation until this CTA has freed its columns, never the
+    // other way round (it still waits for this whole grid before it reads any result).
+    pdl_launch_dependents();
 
     if (a.use_pdl) pdl_wait_primary();   // launched as a programmatic dependent of the row-gather kernel
 
@@ -632,8 +635,6 @@ moe_up_dual_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     const bool lsu = a.pregathered == 2;
     const int gather_threads = static_cast<int>(blockDim.x) - 64 - epi_threads;   // 0, 128 or 256
 
-    pdl_launch_dependents();
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), lsu ? 1 + gather_threads : 1);
@@ -656,6 +657,11 @@ moe_up_dual_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    // Dependents may be scheduled only now that this CTA holds its tensor memory: a dependent CTA that
+    // shares this SM then blocks in its own allocation until this CTA has freed its columns, never the
+    // other way round (it still waits for this whole grid before it reads any result).
+    pdl_launch_dependents();
 
     if (a.use_pdl) pdl_wait_primary();   // launched as a programmatic dependent of the row-gather kernel
 
@@ -1035,8 +1041,6 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int epi_threads = a.epi_warps * 32;
 
-    pdl_launch_dependents();  // the finalize kernel still waits for this whole grid before reading
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), 1);
@@ -1061,6 +1065,11 @@ moe_fused_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    // Dependents may be scheduled only now that this CTA holds its tensor memory: a dependent CTA that
+    // shares this SM then blocks in its own allocation until this CTA has freed its columns, never the
+    // other way round (it still waits for this whole grid before it reads any result).
+    pdl_launch_dependents();
 
     const int m_blocks = num_row_blocks(a);
     const int n_tiles = a.H / 128;          // H slices
@@ -1276,8 +1285,6 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
 
-    if (kUp) pdl_launch_dependents();
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), 1);
@@ -1301,6 +1308,11 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    // Dependents may be scheduled only now that this CTA holds its tensor memory: a dependent CTA that
+    // shares this SM then blocks in its own allocation until this CTA has freed its columns, never the
+    // other way round (it still waits for this whole grid before it reads any result).
+    if (kUp) pdl_launch_dependents();
 
     if (a.use_pdl) pdl_wait_primary();   // up: after the row-gather kernel; down: after the gate/up kernel
 
@@ -1491,7 +1503,53 @@ int set_smem(Kernel k, size_t bytes) {
     return PMOE_OK;
 }
 
-int run(const Problem &p, void *workspace, cudaStream_t stream) {
+// Byte offsets of the regions a call may carve out of its workspace. ONE function answers both "how large must
+// the workspace be" and "where does the launcher put each region", whatever PMOE_PREGATHER / PMOE_AGATHER / bpc
+// select at call time: every region is always reserved.
+//   split != 0: activation [sorted_num, H] bf16 | x_sorted [sorted_num, K] bf16 | pair list, tail list, counts
+//   split == 0: fp32 accumulation buffer [M, K] (padded to 1024 bytes) | x_sorted [sorted_num, K] bf16
+struct WorkspaceLayout {
+    size_t x_sorted, lists, total;
+};
+WorkspaceLayout plan_workspace(int M, int K, int N, int sorted_num, int split) {
+    WorkspaceLayout w{};
+    auto up = [](size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); };
+    const size_t rows = static_cast<size_t>(std::max(sorted_num, 0));
+    if (!split) {
+        w.x_sorted = up(static_cast<size_t>(M) * K * sizeof(float));
+        w.lists = w.x_sorted + rows * K * 2;
+        w.total = up(w.lists);
+        return w;
+    }
+    w.x_sorted = rows * (N / 2) * 2;           // a multiple of 1024: sorted_num % 128 == 0 and H % 128 == 0
+    w.lists = w.x_sorted + rows * K * 2;
+    w.total = up(w.lists + (rows / 128 + 8) * sizeof(int32_t));   // two lists of <= blocks/2 entries + two counts
+    return w;
+}
+
+// What the split launcher does with this problem under the current environment; read by run() and by the
+// workspace-extent query so that the two cannot drift apart.
+struct Decisions {
+    int a_mode;       // gate/up A operand: 0 TMA gather4 from x, 1 row-gather pre-pass, 2 LSU gather in the kernel
+    bool pregather;   // x_sorted region written and read
+    bool tails;       // bpc == 2: pair / tail lists written and read
+};
+Decisions decide(const Problem &p) {
+    Decisions d{};
+    d.a_mode = a_operand_mode();
+    // auto: the in-kernel LSU gather pays off when the row-gather pre-pass is a visible share of the step (its
+    // cost is ~250/N of a compute-bound step) and the step is compute-bound (>= 256 routed rows per expert on
+    // average; in the weight-streaming regime the pre-pass with plain tiles streams faster)
+    // (TMA gather4 straight from x - 8 instead of 32 gather4 per k-step for short row blocks - was measured for
+    // calls with <= 32 routed rows per expert: same time as the PDL-chained pre-pass, so it stays an option)
+    if (d.a_mode < 0)
+        d.a_mode = (p.bpc == 1 && p.N < 8192 && static_cast<long long>(p.M) * p.top_k >= 256ll * p.E) ? 2 : 1;
+    d.pregather = d.a_mode == 1 || p.bpc == 2;   // the CTA-pair kernels always take pre-gathered rows
+    d.tails = p.bpc == 2 && pair_tails_enabled();
+    return d;
+}
+
+int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
     const int H = p.N / 2;
     const int max_blocks = p.sorted_num / BM;
     if (max_blocks == 0) {
@@ -1537,9 +1595,12 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
                      "fused_moe_bf16: workspace must be 16-byte aligned");
         a.acc32 = static_cast<float *>(workspace);
         const size_t elems = static_cast<size_t>(p.M) * p.K;
+        const WorkspaceLayout lay = plan_workspace(p.M, p.K, p.N, p.sorted_num, 0);
+        PMOE_REQUIRE(workspace_bytes >= lay.total, PMOE_ERR_BAD_ARG,
+                     "fused_moe_bf16: workspace of %zu bytes required, got %zu", lay.total, workspace_bytes);
         PMOE_CUDA_OK(cudaMemsetAsync(a.acc32, 0, elems * sizeof(float), stream));
         if (pregather_enabled()) {   // x_sorted follows the accumulation buffer (1024-byte aligned)
-            const size_t off = (elems * sizeof(float) + 1023) & ~static_cast<size_t>(1023);
+            const size_t off = lay.x_sorted;
             __nv_bfloat16 *x_sorted = reinterpret_cast<__nv_bfloat16 *>(static_cast<uint8_t *>(workspace) + off);
             PMOE_REQUIRE((reinterpret_cast<uintptr_t>(x_sorted) & 1023) == 0, PMOE_ERR_BAD_ARG,
                          "fused_moe_bf16: workspace must be 1024-byte aligned");
@@ -1574,18 +1635,16 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     // split pipeline: workspace = activation [sorted_num, H] bf16 (+ x_sorted [sorted_num, K] when pre-gathering)
     PMOE_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16: workspace must be 1024-byte aligned");
-    int a_mode = a_operand_mode();                // 0 gather4, 1 row-gather pre-pass, 2 LSU gather in the kernel
-    // auto: the in-kernel LSU gather pays off when the row-gather pre-pass is a visible share of the step (its
-    // cost is ~250/N of a compute-bound step) and the step is compute-bound (>= 256 routed rows per expert on
-    // average; in the weight-streaming regime the pre-pass with plain tiles streams faster)
-    // (TMA gather4 straight from x - 8 instead of 32 gather4 per k-step for short row blocks - was measured for
-    // calls with <= 32 routed rows per expert: same time as the PDL-chained pre-pass, so it stays an option)
-    if (a_mode < 0)
-        a_mode = (p.bpc == 1 && p.N < 8192 && static_cast<long long>(p.M) * p.top_k >= 256ll * p.E) ? 2 : 1;
-    const bool pregather = a_mode == 1 || p.bpc == 2;   // the CTA-pair kernels always take pre-gathered rows
+    const WorkspaceLayout lay = plan_workspace(p.M, p.K, p.N, p.sorted_num, 1);
+    PMOE_REQUIRE(workspace_bytes >= lay.total, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16: workspace of %zu bytes required, got %zu", lay.total, workspace_bytes);
+    uint8_t *const ws_base = static_cast<uint8_t *>(workspace);
+    const Decisions dec = decide(p);
+    const int a_mode = dec.a_mode;
+    const bool pregather = dec.pregather;
     const int phases = phase_mask();  // profiling hook: 1 = gather, 2 = gate/up, 4 = down (default all)
     if (pregather) {
-        __nv_bfloat16 *x_sorted = static_cast<__nv_bfloat16 *>(workspace) + static_cast<size_t>(p.sorted_num) * H;
+        __nv_bfloat16 *x_sorted = reinterpret_cast<__nv_bfloat16 *>(ws_base + lay.x_sorted);
         if (phases & 1) {
             gather_rows_kernel<<<std::min(4 * sms, (p.sorted_num + 7) / 8), 256, 0, stream>>>(
                 static_cast<const __nv_bfloat16 *>(p.x), x_sorted, a);
@@ -1607,8 +1666,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
                               SHORT_ROWS, BK, CU_TENSOR_MAP_SWIZZLE_128B, "act (short box)"))
         return rc;
     if (pregather)
-        if (int rc = make_tmap_2d(&map_x_short, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                                  static_cast<__nv_bfloat16 *>(workspace) + static_cast<size_t>(p.sorted_num) * H,
+        if (int rc = make_tmap_2d(&map_x_short, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ws_base + lay.x_sorted,
                                   p.sorted_num, p.K, SHORT_ROWS, BK, CU_TENSOR_MAP_SWIZZLE_128B, "x_sorted (short box)"))
             return rc;
     a.short_boxes = short_boxes_mode();
@@ -1649,11 +1707,10 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         // the last pair of an expert whose second block is empty runs as a single 128-row block on the one-CTA
         // kernels (tcgen05 does not allow cta_group::1 and ::2 in one kernel, hence own launches); PMOE_PAIR_TAILS=0
         // runs it as a pair like the others
-        const bool tails = pair_tails_enabled();
+        const bool tails = dec.tails;
         Args ta = a;    // the one-CTA launches over the tail blocks
         if (tails) {
-            int32_t *lists = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(workspace) +
-                                                         static_cast<size_t>(p.sorted_num) * (H + p.K) * 2);
+            int32_t *lists = reinterpret_cast<int32_t *>(ws_base + lay.lists);
             const int max_pairs = max_blocks / 2;
             pa.pair_list = lists;
             pa.list_counts = lists + 2 * max_pairs;
@@ -1787,6 +1844,11 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
 
 }  // namespace
 
+int wait_ns_store_bf16(unsigned long long ns) {
+    PMOE_CUDA_OK(cudaMemcpyToSymbol(g_wait_ns, &ns, sizeof(ns)));
+    return PMOE_OK;
+}
+
 int status_fetch_bf16(int *value, bool reset) {
     if (value) PMOE_CUDA_OK(cudaMemcpyFromSymbol(value, g_status_bf16, sizeof(int)));
     if (reset) {
@@ -1799,16 +1861,24 @@ int status_fetch_bf16(int *value, bool reset) {
 }  // namespace pmoe
 
 extern "C" size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int sorted_num, int split) {
-    if (sorted_num <= 0 || N <= 0) return 0;
-    if (!split) {
-        size_t bytes = (static_cast<size_t>(M) * K * sizeof(float) + 1023) & ~static_cast<size_t>(1023);
-        if (pmoe::pregather_enabled()) bytes += static_cast<size_t>(sorted_num) * K * 2;
-        return bytes;
-    }
-    size_t bytes = static_cast<size_t>(sorted_num) * (N / 2) * 2;
-    if (pmoe::pregather_enabled()) bytes += static_cast<size_t>(sorted_num) * K * 2;
-    bytes += (static_cast<size_t>(sorted_num) / 128 + 8) * sizeof(int32_t);   // pair / tail lists of the bpc = 2 pipeline
-    return (bytes + 1023) & ~static_cast<size_t>(1023);
+    if (sorted_num <= 0 || N <= 0 || K <= 0 || M <= 0) return 0;
+    return pmoe::plan_workspace(M, K, N, sorted_num, split).total;
+}
+
+extern "C" size_t pmoe_debug_bf16_workspace_extent(int M, int K, int N, int num_experts, int top_k, int sorted_num,
+                                                   int bpc, int split) {
+    using namespace pmoe;
+    if (sorted_num <= 0 || N <= 0 || K <= 0 || M <= 0) return 0;
+    const WorkspaceLayout lay = plan_workspace(M, K, N, sorted_num, split);
+    const size_t rows = static_cast<size_t>(sorted_num);
+    if (!split) return pregather_enabled() ? lay.x_sorted + rows * K * 2 : static_cast<size_t>(M) * K * sizeof(float);
+    Problem p{};
+    p.M = M, p.K = K, p.N = N, p.E = num_experts, p.top_k = top_k, p.sorted_num = sorted_num, p.bpc = bpc, p.split = 1;
+    const Decisions d = decide(p);
+    size_t end = rows * (N / 2) * 2;                                  // activation
+    if (d.pregather) end = std::max(end, lay.x_sorted + rows * K * 2);
+    if (d.tails) end = std::max(end, lay.lists + (2 * (rows / 256) + 2) * sizeof(int32_t));
+    return end;
 }
 
 extern "C" int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *w2, void *out,
@@ -1825,7 +1895,7 @@ extern "C" int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *
     const size_t need = pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_num, split);
     PMOE_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16: workspace of %zu bytes required, got %zu", need, workspace_bytes);
-    return run(p, workspace, stream);
+    return run(p, workspace, workspace_bytes, stream);
 }
 
 extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2, void *out,
@@ -1843,7 +1913,7 @@ extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2,
     if (need)
         if (int rc = scratch_alloc(&raw, need + 1024, stream)) return rc;
     void *ws = reinterpret_cast<void *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const int rc = run(p, raw ? ws : nullptr, stream);
+    const int rc = run(p, raw ? ws : nullptr, need, stream);
     if (raw)
         if (int rc2 = scratch_free(raw, stream)) return rc2;
     return rc;

@@ -212,8 +212,6 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int epi_threads = EPI_WARPS * 32;
 
-    pdl_launch_dependents();
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), 1);
@@ -234,6 +232,11 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    // Dependents may be scheduled only now that this CTA holds its tensor memory: a dependent CTA that
+    // shares this SM then blocks in its own allocation until this CTA has freed its columns, never the
+    // other way round (it still waits for this whole grid before it reads any result).
+    pdl_launch_dependents();
 
     if (a.use_pdl) pdl_wait_primary();   // launched as a programmatic dependent of the row-gather kernel
 
@@ -581,8 +584,6 @@ moe_pair_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
 
-    if (kUp) pdl_launch_dependents();
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), 1);
@@ -606,6 +607,11 @@ moe_pair_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    // Dependents may be scheduled only now that this CTA holds its tensor memory: a dependent CTA that
+    // shares this SM then blocks in its own allocation until this CTA has freed its columns, never the
+    // other way round (it still waits for this whole grid before it reads any result).
+    if (kUp) pdl_launch_dependents();
 
     if (a.use_pdl) pdl_wait_primary();   // up: after the row-gather kernel; down: after the gate/up kernel
 
@@ -825,8 +831,6 @@ moe_fused_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     constexpr int epi_threads = EPI_WARPS * 32;
     constexpr uint32_t DN_ACC = 384;
 
-    pdl_launch_dependents();
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(sm.full(s), 1);
@@ -849,6 +853,11 @@ moe_fused_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     tc_fence_after();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    // Dependents may be scheduled only now that this CTA holds its tensor memory: a dependent CTA that
+    // shares this SM then blocks in its own allocation until this CTA has freed its columns, never the
+    // other way round (it still waits for this whole grid before it reads any result).
+    pdl_launch_dependents();
 
     if (a.use_pdl) pdl_wait_primary();   // x_sorted / scale tiles come from the gather pre-pass
 
@@ -1337,6 +1346,11 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int wait_ns_store_mxfp8(unsigned long long ns) {
+    PMOE_CUDA_OK(cudaMemcpyToSymbol(g_wait_ns, &ns, sizeof(ns)));
+    return PMOE_OK;
+}
 
 int status_fetch_mxfp8(int *value, bool reset) {
     if (value) PMOE_CUDA_OK(cudaMemcpyFromSymbol(value, g_status_mxfp8, sizeof(int)));

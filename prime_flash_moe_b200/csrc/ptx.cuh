@@ -27,11 +27,19 @@ enum : int {
     ST_TIMEOUT_ACT = 5,         // fused kernel: wait on the on-chip activation tile hand-off
     ST_TIMEOUT_DRAIN = 6,       // teardown waited for copies in flight
     ST_TIMEOUT_PEER = 7,        // 2-CTA kernels: wait on the peer CTA
+    ST_TIMEOUT_PROBE = 9,       // the wait-probe kernel waited on a barrier nobody arrives on (8 = bad CTA pair)
 };
 
 #ifndef PMOE_WAIT_NS
 #define PMOE_WAIT_NS 2000000000ull  // 2 s per wait
 #endif
+
+// Limit of every bounded wait in nanoseconds. One copy per translation unit (no relocatable device code);
+// pmoe_debug_set_wait_ns() stores the same value into all of them on the current device.
+static __device__ unsigned long long g_wait_ns = PMOE_WAIT_NS;
+__device__ __forceinline__ unsigned long long wait_limit_ns() {
+    return *reinterpret_cast<volatile unsigned long long *>(&g_wait_ns);
+}
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
@@ -100,7 +108,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     while (!mbar_try_wait(bar, parity)) {
         if ((++n & 63u) == 0) {
             if (*reinterpret_cast<volatile int *>(status) != 0) return false;
-            if (globaltimer_ns() - t0 > PMOE_WAIT_NS) {
+            if (globaltimer_ns() - t0 > wait_limit_ns()) {
                 atomicCAS(status, 0, code);
                 return false;
             }
@@ -360,7 +368,7 @@ static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t par
     while (!mbar_try_wait_cluster(bar, parity)) {
         if ((++n & 63u) == 0) {
             if (*reinterpret_cast<volatile int *>(status) != 0) return false;
-            if (globaltimer_ns() - t0 > PMOE_WAIT_NS) {
+            if (globaltimer_ns() - t0 > wait_limit_ns()) {
                 atomicCAS(status, 0, code);
                 return false;
             }

@@ -11,6 +11,7 @@
 #include <torch/all.h>
 #include <torch/library.h>
 
+#include <optional>
 #include <tuple>
 
 #include "../../include/pmoe_b200.h"
@@ -31,8 +32,8 @@ void *align1k(void *p) {
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> moe_align(const torch::Tensor &topk_ids,
                                                                   int64_t num_experts, int64_t block_m,
                                                                   int64_t bpc) {
+    at::cuda::OptionalCUDAGuard guard{device_of(topk_ids)};   // first: the stream below must be the current one of the tensors' device
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-    at::cuda::OptionalCUDAGuard guard{device_of(topk_ids)};
     TORCH_CHECK(topk_ids.is_contiguous());
     TORCH_CHECK(topk_ids.dtype() == torch::kInt32);
     TORCH_CHECK(block_m > 0 && bpc > 0 && num_experts > 0);
@@ -66,8 +67,8 @@ void fused_moe_bf16(const torch::Tensor &x, const torch::Tensor &w, const torch:
                     const torch::Tensor &num_tokens_post_padded, const torch::Tensor &topk_weights,
                     torch::Tensor &out, int64_t top_k, int64_t block_m, int64_t block_n, int64_t warp_n,
                     int64_t stages, int64_t bpc, int64_t cpc, bool split) {
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};   // first: the stream below must be the current one of the tensors' device
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-    at::cuda::OptionalCUDAGuard guard{device_of(x)};
     TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w2.dim() == 3);
     TORCH_CHECK(x.size(0));
     TORCH_CHECK(x.size(1) == w.size(2));
@@ -119,8 +120,8 @@ void fused_moe_mxfp8(const torch::Tensor &x, const torch::Tensor &x_scales, cons
                      const torch::Tensor &num_tokens_post_padded, const torch::Tensor &topk_weights,
                      torch::Tensor &out, int64_t top_k, int64_t block_m, int64_t block_n, int64_t warp_n,
                      int64_t stages, int64_t bpc, bool split) {
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};   // first: the stream below must be the current one of the tensors' device
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-    at::cuda::OptionalCUDAGuard guard{device_of(x)};
     TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w2.dim() == 3);
     const int64_t M = x.size(0), K = x.size(1), E = w.size(0), N = w.size(1);
     TORCH_CHECK(M);
@@ -186,8 +187,8 @@ void fused_moe_mxfp8(const torch::Tensor &x, const torch::Tensor &x_scales, cons
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> ep_plan(const torch::Tensor &topk_ids,
                                                                                const torch::Tensor &topk_weights,
                                                                                int64_t num_experts, int64_t world) {
+    at::cuda::OptionalCUDAGuard guard{device_of(topk_ids)};   // first: the stream below must be the current one of the tensors' device
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-    at::cuda::OptionalCUDAGuard guard{device_of(topk_ids)};
     TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous() && topk_ids.dtype() == torch::kInt32,
                 "topk_ids must be a contiguous int32 [T, top_k] tensor");
     TORCH_CHECK(topk_weights.is_contiguous() && topk_weights.dtype() == torch::kFloat32 &&
@@ -214,8 +215,8 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> ep_plan(c
 
 // expert-parallel combine: out[t] = sum over the token's visits of y[slot_of[t, g]] (not in the reference)
 torch::Tensor ep_combine(const torch::Tensor &y, const torch::Tensor &slot_of) {
+    at::cuda::OptionalCUDAGuard guard{device_of(y)};   // first: the stream below must be the current one of the tensors' device
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-    at::cuda::OptionalCUDAGuard guard{device_of(y)};
     TORCH_CHECK(y.dim() == 2 && y.is_contiguous() && y.dtype() == torch::kBFloat16);
     TORCH_CHECK(slot_of.dim() == 2 && slot_of.is_contiguous() && slot_of.dtype() == torch::kInt32);
     const int64_t T = slot_of.size(0), world = slot_of.size(1), K = y.size(1);
@@ -226,9 +227,56 @@ torch::Tensor ep_combine(const torch::Tensor &y, const torch::Tensor &slot_of) {
     return out;
 }
 
+// router (not in the reference: "routing comes from your gate", README.md:147): logits [T, E] fp32 or bf16 ->
+// (topk_ids int32 [T, top_k], topk_weights fp32 [T, top_k]), see pmoe_route_topk
+std::tuple<torch::Tensor, torch::Tensor> route_topk(const torch::Tensor &logits, int64_t top_k, bool renormalize) {
+    at::cuda::OptionalCUDAGuard guard{device_of(logits)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous(), "logits must be a contiguous [T, E] tensor");
+    TORCH_CHECK(logits.dtype() == torch::kFloat32 || logits.dtype() == torch::kBFloat16,
+                "logits must be fp32 or bf16");
+    const int64_t T = logits.size(0), E = logits.size(1);
+    torch::Tensor ids = torch::empty({T, top_k}, logits.options().dtype(torch::kInt32));
+    torch::Tensor wts = torch::empty({T, top_k}, logits.options().dtype(torch::kFloat32));
+    check_status(pmoe_route_topk(logits.const_data_ptr(),
+                                 logits.dtype() == torch::kFloat32 ? PMOE_DTYPE_F32 : PMOE_DTYPE_BF16,
+                                 static_cast<int>(T), static_cast<int>(E), static_cast<int>(top_k), renormalize ? 1 : 0,
+                                 static_cast<int32_t *>(ids.data_ptr()), static_cast<float *>(wts.data_ptr()), stream));
+    return {ids, wts};
+}
+
+// activation quantiser (not in the reference: README.md:110-113 leaves it to the caller): bf16 [T, K] ->
+// (e4m3 [R, K], e8m0 [R, K/32]); with row_index int32 [R] output row r is x[row_index[r]], see pmoe_quantize_mx
+std::tuple<torch::Tensor, torch::Tensor> quantize_mx(const torch::Tensor &x,
+                                                     const std::optional<torch::Tensor> &row_index) {
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.dtype() == torch::kBFloat16,
+                "x must be a contiguous bf16 [T, K] tensor");
+    const int64_t T = x.size(0), K = x.size(1);
+    TORCH_CHECK(K % 32 == 0, "K must be a multiple of 32");
+    int64_t R = T;
+    const int32_t *index = nullptr;
+    if (row_index.has_value()) {
+        TORCH_CHECK(row_index->dtype() == torch::kInt32 && row_index->is_contiguous() && row_index->device() == x.device(),
+                    "row_index must be a contiguous int32 tensor on the device of x");
+        R = row_index->numel();
+        index = static_cast<const int32_t *>(row_index->const_data_ptr());
+    }
+    torch::Tensor q = torch::empty({R, K}, x.options().dtype(torch::kFloat8_e4m3fn));
+    torch::Tensor sc = torch::empty({R, K / 32}, x.options().dtype(torch::kFloat8_e8m0fnu));
+    check_status(pmoe_quantize_mx(x.const_data_ptr(), index, static_cast<int>(T), q.data_ptr(), sc.data_ptr(),
+                                  static_cast<int>(R), static_cast<int>(K), stream));
+    return {q, sc};
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(prime_moe, m) {
+    m.def("route_topk(Tensor logits, int top_k, bool renormalize=True) -> (Tensor, Tensor)");
+    m.impl("route_topk", torch::kCUDA, &route_topk);
+    m.def("quantize_mx(Tensor x, Tensor? row_index=None) -> (Tensor, Tensor)");
+    m.impl("quantize_mx", torch::kCUDA, &quantize_mx);
     m.def("ep_plan(Tensor topk_ids, Tensor topk_weights, int num_experts, int world) -> (Tensor, Tensor, Tensor, Tensor)");
     m.impl("ep_plan", torch::kCUDA, &ep_plan);
     m.def("ep_combine(Tensor y, Tensor slot_of) -> Tensor");

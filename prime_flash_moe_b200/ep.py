@@ -130,13 +130,14 @@ class ExpertParallelMoE:
     visits this rank computed in the last call and ``last_sent_rows`` the number it sent (load imbalance under
     skewed routing and the saving over one row per route show up there)."""
 
-    def __init__(self, num_experts: int, experts: Callable, group=None):
+    def __init__(self, num_experts: int, experts: Callable, group=None, combine: str = "nccl"):
         self.num_experts = num_experts
         self.experts = experts
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.last_recv_rows = 0
         self.last_sent_rows = 0
+        self.combine_mode = "nccl"
 
     def forward(self, x, topk_ids, topk_weights, x_scales=None):
         T, K = x.shape

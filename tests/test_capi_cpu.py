@@ -70,6 +70,47 @@ def test_fused_bf16_argument_errors(lib):
     assert lib.pmoe_fused_moe_bf16_workspace_bytes(8, 256, 512, 512, 1) >= 512 * 256 * 2
 
 
+@pytest.mark.parametrize("pregather", [None, "0", "1"])
+@pytest.mark.parametrize("agather", [None, "tma4", "pre", "lsu"])
+@pytest.mark.parametrize("tails", [None, "0"])
+@pytest.mark.parametrize("bpc", [1, 2])
+def test_bf16_workspace_covers_every_launch_path(lib, monkeypatch, pregather, agather, tails, bpc):
+    """The bytes the bf16 launcher touches (row-gathered copy of x, activation, pair / tail lists) never exceed
+    the size `pmoe_fused_moe_bf16_workspace_bytes` reports, whatever PMOE_PREGATHER / PMOE_AGATHER /
+    PMOE_PAIR_TAILS select at call time (all three are read per call); the reported size depends on none of them."""
+    for name, val in (("PMOE_PREGATHER", pregather), ("PMOE_AGATHER", agather), ("PMOE_PAIR_TAILS", tails)):
+        if val is None:
+            monkeypatch.delenv(name, raising=False)
+        else:
+            monkeypatch.setenv(name, val)
+    shapes = [(4096, 4096, 28672, 8, 2, 10240), (8192, 2048, 1536, 128, 8, 81920), (8, 256, 512, 4, 2, 512),
+              (256, 4096, 512, 8, 4, 2048)]
+    for M, K, N, E, k, sorted_num in shapes:
+        for split in (0, 1):
+            if bpc == 2 and not split:
+                continue
+            size = lib.pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_num, split)
+            touched = lib.pmoe_debug_bf16_workspace_extent(M, K, N, E, k, sorted_num, bpc, split)
+            assert 0 < touched <= size, (M, K, N, sorted_num, split, bpc, touched, size)
+            if split:
+                assert size >= sorted_num * (N // 2 + K) * 2 + (sorted_num // 128 + 2) * 4
+
+
+def test_bf16_ws_entry_point_rejects_a_short_workspace(lib):
+    """The `_ws` entry point checks the caller's size against the full layout before any launch."""
+    buf = (C.c_char * 8192)()
+    p = (C.addressof(buf) + 1023) & ~1023
+    need = lib.pmoe_fused_moe_bf16_workspace_bytes(8, 256, 512, 512, 1)
+    rc = lib.pmoe_fused_moe_bf16_ws(p, p, p, p, p, p, p, p, 2, 8, 256, 512, 4, 512, 128, 64, 4, 2, 2, 1, 1, p, need - 1,
+                                    None)
+    assert rc == 1 and str(need).encode() in lib.pmoe_last_error()
+
+
+def test_wait_limit_argument_range(lib):
+    assert lib.pmoe_debug_set_wait_ns(10) == 1                   # below 1 microsecond
+    assert lib.pmoe_debug_set_wait_ns(10 ** 12) == 1             # above 60 seconds
+
+
 def test_operator_schemas_match_reference():
     import prime_flash_moe_b200  # noqa: F401  (registers the ops)
     s = str(torch.ops.prime_moe.fused_moe_bf16.default._schema)

@@ -4,11 +4,14 @@ Servers that freeze their device-memory budget after start-up, or plugins runnin
 framework's allocator hooks, can neither call cudaMalloc nor lend a workspace. This entry point keeps
 its scratch in a fixed array inside the library. The test drives it through the C ABI, twice in a row
 on different inputs (the array keeps the first call's contents), and requires the three outputs to be
-identical, integer for integer, to those of the allocating entry point `pmoe_moe_align`.
+identical, integer for integer, to those of the allocating entry point `pmoe_moe_align` and to the CPU
+restatement of the reference's algorithm.
 
 Collected last on purpose: a failure here must not hide the result of any other test.
 """
 import ctypes as C
+
+import numpy as np
 
 import pytest
 import torch
@@ -49,6 +52,11 @@ def test_static_scratch_matches_allocating_entry_point_twice():
         assert torch.equal(npp, npp2)
         assert torch.equal(e, e2)
         assert torch.equal(s, s2)
+        # and, directly, to the CPU restatement of the reference's algorithm
+        want_s, want_e, want_n = O.moe_align_spec(ids.cpu().numpy(), E, 128, bpc)
+        assert np.array_equal(s.cpu().numpy(), want_s)
+        assert np.array_equal(e.cpu().numpy(), want_e)
+        assert np.array_equal(npp.cpu().numpy(), want_n)
     # a small problem takes the single-CTA path and needs no scratch at all
     ids, _ = O.make_routing(100, 16, 4, seed=5)
     ids = ids.to(DEV)
