@@ -71,6 +71,8 @@ def parse_args():
                          "default when the expert count divides), 'replica' runs N independent copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="headline workload only")
+    ap.add_argument("--op", default="moe", choices=["moe", "moe_align"],
+                    help="'moe_align' times the routing kernels alone on the routing table of --config (GB/s line)")
     ap.add_argument("--ep-combine", default="auto", choices=["auto", "nccl", "peer"],
                     help="expert-parallel combine: NCCL all-to-all, or this library's kernel storing into the source "
                          "rank's buffer over NVLink (auto = peer when every rank can map its peers)")
@@ -988,6 +990,28 @@ def run_cpu_arm(args):
                       "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+def run_align_only(args):
+    """`--op moe_align`: the routing kernels alone (a few MB of traffic; the command the ncu summary of these
+    kernels under profiles/ was made with)."""
+    import torch
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    sys.path.insert(0, str(ROOT))
+    if args.impl == "reference":
+        sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+        import prime_moe  # noqa: F401
+        name = "the reference's moe_align_kernel"
+    else:
+        import prime_flash_moe_b200  # noqa: F401
+        name = "moe_align_{hist,scan,scatter}_kernel"
+    e = sweep_align_entry(args.config, device, measured_peaks(), name)
+    e.update({"metric": "moe_align_gbs", "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
+              "impl": args.impl})
+    print(json.dumps(e))
+
+
 def main():
     args = parse_args()
     if args.bpc == 0:
@@ -997,7 +1021,9 @@ def main():
     if args.parallel == "auto":
         world = int(os.environ.get("WORLD_SIZE", "1"))
         args.parallel = "ep" if world > 1 and CONFIGS[args.config][2] % world == 0 else "replica"
-    if args.impl == "cpu":
+    if args.op == "moe_align":
+        run_align_only(args)
+    elif args.impl == "cpu":
         run_cpu_arm(args)
     else:
         run_gpu_arm(args, args.impl)
