@@ -705,7 +705,6 @@ def run_gpu_arm(args, impl):
                 out_.copy_(layer(x_[0], ids_, wts_, x_[1]))
             else:
                 out_.copy_(layer(x_, ids_, wts_))
-            ep_rows.append(layer.last_recv_rows)
         knobs = {"stages": args.stages, "split": True, "experts_per_rank": E // world}
     elif impl == "ours":
         sys.path.insert(0, str(ROOT))
@@ -714,7 +713,7 @@ def run_gpu_arm(args, impl):
         ops = torch.ops.prime_moe
         (bn, wn), stages, split, bpc = ((64, 4) if args.warp_n == 4 else (32, 8)), args.stages, bool(args.split), args.bpc
         # align kernels + gather, gate/up|fused, down|finalize (+ pair classification and the two tail launches, bpc=2)
-        launches_per_step = (3 if T * k > 4096 else 1) + 3 + (3 if (bpc == 2 and split and not mx) else 0)
+        launches_per_step = (2 if T * k > 4096 else 1) + 3 + (3 if (bpc == 2 and split and not mx) else 0)
 
         def step(x_, ids_, wts_, out_):
             s, e, n = ops.moe_align(ids_, E, 128, bpc)
@@ -907,9 +906,12 @@ def run_gpu_arm(args, impl):
     ep_parity = None
     if ep_mode:
         # kernels of this package per step: plan (3) + moe_align (1 or 3) + row gather, gate/up, down (3) + combine (1)
-        launches_per_step = 3 + (3 if (ep_rows[-1] if ep_rows else 0) * k > 4096 else 1) + 3 + 1
         step(xin, ids, wts, out)
         torch.cuda.synchronize()
+        ep_rows.append(layer.last_recv_rows)
+        # plan (3) + moe_align (1 or 2) + row gather, gate/up, down (3) + combine (1) (+ publish, push, 2 signals,
+        # prepare, return: 6 in peer mode)
+        launches_per_step = 3 + (2 if ep_rows[-1] * k > 4096 else 1) + 3 + 1 + (6 if layer.combine_mode == "peer" else 0)
         a_, b_ = out[:np_].float(), par_ref.float()
         ep_parity = max_over_ranks(float((a_ - b_).abs().max() / b_.abs().max().clamp_min(1e-30)), world, device)
     sweep = None
@@ -950,7 +952,10 @@ def run_gpu_arm(args, impl):
                                     "parity_what": "max over ranks of max|ep_out - single_gpu_out| / max|single_gpu_out| on each "
                                                    "rank's first 64 tokens (single-GPU operator on the full weights)",
                                     "combine": layer.combine_mode,
-                                    "collective": "NCCL all-to-all (dispatch + combine), one row per (token, rank) visit"}
+                                    "collective": ("none on the data path: rows, slot tables, counts and partial sums are stored "
+                                                   "into the peers' buffers over NVLink by this library's kernels"
+                                                   if layer.combine_mode == "peer" else
+                                                   "NCCL all-to-all (dispatch + combine)") + ", one row per (token, rank) visit"}
         if impl == "reference":
             line["impl"] = "reference"
             line["gpu_launches"] = None

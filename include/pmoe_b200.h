@@ -72,8 +72,8 @@ int pmoe_moe_align_ws(const int32_t *topk_ids, int32_t *sorted_token_ids, int32_
  * another framework's allocator or stream callback, and processes whose device memory already
  * belongs to a pool they do not control cannot call cudaMalloc (nor a stream-ordered or framework
  * allocator) where routing runs, and may have no spare buffer to lend to `pmoe_moe_align_ws`.
- * Same arguments and results as `pmoe_moe_align`; the scratch (per-warp counters and expert offsets)
- * is a fixed 4 MiB array inside the library image, held by every GPU that loads the library until
+ * Same arguments and results as `pmoe_moe_align`; the scratch (one counter per thread block and expert)
+ * is a fixed 256 KiB array inside the library image, held by every GPU that loads the library until
  * the process exits. The call performs no cudaMalloc, cudaFree or any other allocating routine.
  *  - Limit: inputs whose scratch need (`pmoe_moe_align_workspace_bytes(n, num_experts)`) exceeds
  *    `pmoe_moe_align_static_capacity_bytes()` are rejected with PMOE_ERR_UNSUPPORTED and a message
@@ -192,6 +192,49 @@ int pmoe_ep_plan(const int32_t *topk_ids, const float *topk_weights, int T, int 
                  int32_t *counts, int32_t *visit_token, int32_t *visit_meta, int32_t *slot_of, void *workspace,
                  size_t workspace_bytes, pmoe_stream_t stream);
 int pmoe_ep_combine(const void *y, const int32_t *slot_of, void *out, int T, int world, int K, pmoe_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Expert-parallel exchange over peer memory: the dispatch and the combine of a step as kernels of this library
+ * that store straight into the other ranks' buffers over NVLink - no NCCL call and no host synchronisation
+ * inside a step. No counterpart in the reference (single GPU). One process per GPU.
+ *
+ * Every rank allocates ONE buffer of the same size with pmoe_ep_buffer_alloc (cudaMalloc, zero-filled; the
+ * 64-byte handle goes to the other ranks by any host channel), maps its peers' buffers with
+ * pmoe_ep_buffer_open, and keeps the G base pointers (its own at index `rank`) in a DEVICE array `peer_bufs`.
+ * A buffer starts with a header of pmoe_ep_header_bytes() bytes that the peers write (per-phase step flags and
+ * the G x G matrix of visit counts); behind it, at offsets the caller chooses identically on all ranks (16-byte
+ * aligned): the row area [row_cap, row_bytes], the auxiliary row area [row_cap, aux_bytes] (MX scales; aux_bytes
+ * may be 0), the meta area int32[row_cap, 2*top_k] and the return area bf16[ret_cap, K]. row_cap = G * T and
+ * ret_cap = T * min(top_k, G) always suffice (T = tokens per rank, the same on all ranks).
+ * One step, all calls on one stream, `epoch` = 1, 2, 3, ... identical on all ranks:
+ *   pmoe_ep_plan -> pmoe_ep_publish_counts -> pmoe_ep_push_rows -> pmoe_ep_recv_prepare ->
+ *   pmoe_moe_align(local_ids, n = row_cap * top_k) + pmoe_fused_moe_* on x = the row area, M = row_cap,
+ *   topk_weights = local_weights, out = y[row_cap, K] -> pmoe_ep_push_back -> pmoe_ep_combine_peer.
+ * push_rows waits until every rank has published its counts, recv_prepare until every rank's rows have arrived
+ * (then local_ids[row_cap, top_k] / local_weights hold the routing of the rows that arrived, -1 / 0 beyond, and
+ * num_rows[0] their number), combine_peer until every rank has returned its partial sums; out[t] is then the
+ * fp32 sum of the token's visit rows. All waits are bounded like the GEMM kernels' (pmoe_device_status codes
+ * 10-12); after an expired wait the step's result is invalid. Only plain loads / stores and release / acquire
+ * flag accesses touch peer memory (no TMA, no multicast, no library kernel). A rank may start step e+1 as soon
+ * as its own step e has been enqueued: it writes into a peer only after that peer has returned step e. */
+size_t pmoe_ep_header_bytes(void);
+int pmoe_ep_buffer_alloc(size_t bytes, void **ptr, void *ipc_handle /* host, 64 bytes out */);
+int pmoe_ep_buffer_open(const void *ipc_handle /* host, 64 bytes */, void **ptr);
+int pmoe_ep_buffer_close(void *ptr);
+int pmoe_ep_buffer_free(void *ptr);
+int pmoe_ep_publish_counts(const int32_t *counts, void *const *peer_bufs, int rank, int world, int epoch,
+                           pmoe_stream_t stream);
+int pmoe_ep_push_rows(const void *x, int row_bytes, const void *aux, int aux_bytes, const int32_t *visit_token,
+                      const int32_t *visit_meta, int top_k, int T, void *const *peer_bufs, size_t rows_off,
+                      size_t aux_off, size_t meta_off, int row_cap, int rank, int world, int epoch,
+                      pmoe_stream_t stream);
+int pmoe_ep_recv_prepare(const void *local_buf, size_t meta_off, int top_k, int row_cap, int32_t *local_ids,
+                         float *local_weights, int32_t *num_rows, int rank, int world, int epoch,
+                         pmoe_stream_t stream);
+int pmoe_ep_push_back(const void *y, int K, void *const *peer_bufs, size_t y_off, int row_cap, int ret_cap, int rank,
+                      int world, int epoch, pmoe_stream_t stream);
+int pmoe_ep_combine_peer(const void *local_buf, size_t y_off, const int32_t *slot_of, void *out, int T, int world,
+                         int K, int epoch, pmoe_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Device status. Every wait inside the kernels is bounded; a wait that expires records a code in a

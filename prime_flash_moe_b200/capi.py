@@ -37,6 +37,16 @@ SIGNATURES = {
     "pmoe_reset_device_status": (_i, []),
     "pmoe_debug_set_phase_mask": (_i, [_i]),
     "pmoe_debug_set_l2_ahead": (_i, [_i]),
+    "pmoe_ep_header_bytes": (_sz, []),
+    "pmoe_ep_buffer_alloc": (_i, [_sz, C.POINTER(_vp), _vp]),
+    "pmoe_ep_buffer_open": (_i, [_vp, C.POINTER(_vp)]),
+    "pmoe_ep_buffer_close": (_i, [_vp]),
+    "pmoe_ep_buffer_free": (_i, [_vp]),
+    "pmoe_ep_publish_counts": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "pmoe_ep_push_rows": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _vp]),
+    "pmoe_ep_recv_prepare": (_i, [_vp, _sz, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pmoe_ep_push_back": (_i, [_vp, _i, _vp, _sz, _i, _i, _i, _i, _i, _vp]),
+    "pmoe_ep_combine_peer": (_i, [_vp, _sz, _vp, _vp, _i, _i, _i, _i, _vp]),
     "pmoe_route_topk": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "pmoe_quantize_mx": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "pmoe_debug_set_wait_ns": (_i, [C.c_ulonglong]),

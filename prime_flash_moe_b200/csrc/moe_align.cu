@@ -7,13 +7,16 @@
 //   num_experts-1 for blocks past the end; num_tokens_post_padded[0] = sum of padded counts.
 // The reference runs ONE CTA with shared-memory atomics and a serial scan, and leaves the order
 // inside an expert to the atomics. Here the ids are cut into contiguous per-warp segments; a warp
-// counts its segment with __match_any_sync groups (no atomics at all, counters are private to the
-// warp), a scan kernel turns the per-warp counts into per-warp write cursors, and the scatter pass
-// replays the segments in order - so the result is deterministic and ascending inside each expert.
+// counts its segment with __match_any_sync groups (counters private to the warp, in shared memory),
+// the per-CTA sums go to a small counts[cta][expert] matrix, and the scatter pass - which scans that
+// matrix itself - replays the segments in order, so the result is deterministic and ascending inside
+// each expert.
 //
-// HBM traffic: 2 x 4n bytes of ids read, 4*max_padded written twice at most (-1 fill + scatter),
-// plus the E x (#warps) counter matrix (scratch).
+// HBM traffic: 4n bytes of ids read (a second time from L2), 4*max_padded written twice at most
+// (-1 fill + scatter), plus the (#CTAs <= #SMs) x E counter matrix (scratch).
 #include <stdio.h>
+
+#include <algorithm>
 
 #include "host_common.h"
 
@@ -23,7 +26,6 @@ namespace {
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 constexpr int kSmallN = 4096;      // up to here a single CTA does everything, no scratch
-constexpr int kIdsPerWarpMin = 256;
 constexpr int kMaxExperts = 1024;
 
 __device__ __forceinline__ unsigned lanemask_lt() {
@@ -33,17 +35,27 @@ __device__ __forceinline__ unsigned lanemask_lt() {
 }
 
 // Count the ids of [begin, end) into cnt[0..E) (private to the calling warp, already zeroed).
+// Four 32-id groups are loaded ahead of their match rounds so that the loads overlap.
 __device__ __forceinline__ void warp_histogram(const int32_t *__restrict__ ids, int begin, int end, int E,
                                                int *cnt) {
     const int lane = threadIdx.x & 31;
-    for (int base = begin; base < end; base += 32) {
-        const int i = base + lane;
-        int id = (i < end) ? ids[i] : -1;
-        const bool valid = id >= 0 && id < E;
-        if (!valid) id = -1;
-        const unsigned peers = __match_any_sync(0xffffffffu, id);
-        if (valid && (peers & lanemask_lt()) == 0) cnt[id] += __popc(peers);
-        __syncwarp();
+    for (int base = begin; base < end; base += 128) {
+        int v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = base + 32 * u + lane;
+            v[u] = (i < end) ? __ldg(ids + i) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (base + 32 * u >= end) break;     // uniform per warp
+            int id = v[u];
+            const bool valid = id >= 0 && id < E;
+            if (!valid) id = -1;
+            const unsigned peers = __match_any_sync(0xffffffffu, id);
+            if (valid && (peers & lanemask_lt()) == 0) cnt[id] += __popc(peers);
+            __syncwarp();
+        }
     }
 }
 
@@ -51,21 +63,31 @@ __device__ __forceinline__ void warp_histogram(const int32_t *__restrict__ ids, 
 __device__ __forceinline__ void warp_scatter(const int32_t *__restrict__ ids, int begin, int end, int E,
                                              int *cur, int32_t *__restrict__ sorted, int max_padded) {
     const int lane = threadIdx.x & 31;
-    for (int base = begin; base < end; base += 32) {
-        const int i = base + lane;
-        int id = (i < end) ? ids[i] : -1;
-        const bool valid = id >= 0 && id < E;
-        if (!valid) id = -1;
-        const unsigned peers = __match_any_sync(0xffffffffu, id);
-        const int rank = __popc(peers & lanemask_lt());
-        int pos = 0;
-        if (valid) pos = cur[id] + rank;
-        __syncwarp();
-        if (valid) {
-            if (pos < max_padded) sorted[pos] = i;
-            if (rank == 0) cur[id] += __popc(peers);
+    for (int base = begin; base < end; base += 128) {
+        int v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = base + 32 * u + lane;
+            v[u] = (i < end) ? __ldg(ids + i) : -1;
         }
-        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (base + 32 * u >= end) break;     // uniform per warp
+            const int i = base + 32 * u + lane;
+            int id = v[u];
+            const bool valid = id >= 0 && id < E;
+            if (!valid) id = -1;
+            const unsigned peers = __match_any_sync(0xffffffffu, id);
+            const int rank = __popc(peers & lanemask_lt());
+            int pos = 0;
+            if (valid) pos = cur[id] + rank;
+            __syncwarp();
+            if (valid) {
+                if (pos < max_padded) sorted[pos] = i;
+                if (rank == 0) cur[id] += __popc(peers);
+            }
+            __syncwarp();
+        }
     }
 }
 
@@ -152,7 +174,13 @@ __global__ void __launch_bounds__(kThreads) moe_align_small_kernel(
     block_offsets(tot, offs, wsum, E, pad_to);
     const int total = offs[E];
     if (threadIdx.x == 0) npp[0] = total;
-    for (int i = threadIdx.x; i < max_padded; i += kThreads) sorted[i] = -1;
+    {   // -1 fill, 16 bytes per store (sorted_token_ids is 16-byte aligned)
+        int4 *s4 = reinterpret_cast<int4 *>(sorted);
+        const int n4 = max_padded >> 2;
+        const int4 m1 = make_int4(-1, -1, -1, -1);
+        for (int i = threadIdx.x; i < n4; i += kThreads) s4[i] = m1;
+        if (threadIdx.x < (max_padded & 3)) sorted[(n4 << 2) + threadIdx.x] = -1;
+    }
     for (int j = threadIdx.x; j < max_blocks; j += kThreads) {
         const int row = j * block_m;
         expert_ids[j] = row >= total ? E - 1 : find_expert(offs, E, row);
@@ -166,21 +194,32 @@ __global__ void __launch_bounds__(kThreads) moe_align_small_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
-// general n: histogram (grid) -> scan (1 CTA) -> scatter (grid)
-//   counts is [E][num_warps] (expert-major, so the scan reads rows contiguously)
+// general n: two launches. The ids are cut into one contiguous segment per CTA (and per warp inside it).
+//   histogram kernel   per-warp private counters in shared memory -> counts[cta][e] (coalesced), and the
+//                      -1 fill of sorted_token_ids
+//   scatter kernel     every CTA rebuilds its per-warp counters (its ids come back from L2), reads the
+//                      counts of ALL CTAs - at most #SM x E integers, L2-resident - to get each expert's
+//                      total and the number of its ids in lower CTAs, scans the padded totals itself and
+//                      replays its segment. The scan is thus done redundantly by every CTA instead of by a
+//                      one-CTA kernel in between; expert_ids is written by all CTAs in turns, npp by CTA 0.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads) moe_align_hist_kernel(
-    const int32_t *__restrict__ ids, int n, int E, int seg, int num_warps, int *__restrict__ counts,
+    const int32_t *__restrict__ ids, int n, int E, int seg, int *__restrict__ counts,
     int32_t *__restrict__ sorted, int max_padded) {
     extern __shared__ int sm[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int *cnt = sm + warp * E;
-    for (int e = lane; e < E; e += 32) cnt[e] = 0;
-    __syncwarp();
+    const int warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < kWarpsPerCta * E; i += kThreads) sm[i] = 0;
+    __syncthreads();
     const int gw = blockIdx.x * kWarpsPerCta + warp;
     const int begin = min(gw * seg, n), end = min(begin + seg, n);
-    warp_histogram(ids, begin, end, E, cnt);
-    for (int e = lane; e < E; e += 32) counts[static_cast<size_t>(e) * num_warps + gw] = cnt[e];
+    warp_histogram(ids, begin, end, E, sm + warp * E);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += kThreads) {
+        int t = 0;
+#pragma unroll
+        for (int w = 0; w < kWarpsPerCta; ++w) t += sm[w * E + e];
+        counts[static_cast<size_t>(blockIdx.x) * E + e] = t;
+    }
     // -1 everywhere; the scatter kernel (later in stream order) overwrites the valid slots
     int4 *s4 = reinterpret_cast<int4 *>(sorted);
     const int n4 = max_padded >> 2;
@@ -189,72 +228,75 @@ __global__ void __launch_bounds__(kThreads) moe_align_hist_kernel(
     if (blockIdx.x == 0 && threadIdx.x < (max_padded & 3)) sorted[(n4 << 2) + threadIdx.x] = -1;
 }
 
-__global__ void __launch_bounds__(1024) moe_align_scan_kernel(
-    int *__restrict__ counts, int num_warps, int E, int block_m, int pad_to, int *__restrict__ offs_out,
-    int32_t *__restrict__ npp, int32_t *__restrict__ expert_ids, int max_blocks) {
+__global__ void __launch_bounds__(kThreads) moe_align_scatter_kernel(
+    const int32_t *__restrict__ ids, int n, int E, int seg, const int *__restrict__ counts, int block_m,
+    int pad_to, int32_t *__restrict__ sorted, int32_t *__restrict__ expert_ids, int32_t *__restrict__ npp,
+    int max_padded, int max_blocks) {
     extern __shared__ int sm[];
-    int *tot = sm;            // [E]
-    int *offs = tot + E;      // [E + 1]
-    int *wsum = offs + E + 1; // [32]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = warp; e < E; e += 32) {
-        int *row = counts + static_cast<size_t>(e) * num_warps;
-        int carry = 0;
-        for (int base = 0; base < num_warps; base += 32) {
-            const int idx = base + lane;
-            const int v = idx < num_warps ? row[idx] : 0;
-            int incl = v;
-            for (int d = 1; d < 32; d <<= 1) {
-                const int u = __shfl_up_sync(0xffffffffu, incl, d);
-                if (lane >= d) incl += u;
-            }
-            if (idx < num_warps) row[idx] = carry + incl - v;
-            carry += __shfl_sync(0xffffffffu, incl, 31);
+    int *cnt = sm;                       // [kWarpsPerCta][E] per-warp counts, later per-warp write cursors
+    int *tot = cnt + kWarpsPerCta * E;   // [E] ids of expert e in all CTAs
+    int *pre = tot + E;                  // [E] ids of expert e in lower CTAs
+    int *offs = pre + E;                 // [E + 1]
+    int *wsum = offs + E + 1;            // [kWarpsPerCta]
+    const int warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < kWarpsPerCta * E + 2 * E; i += kThreads) sm[i] = 0;
+    __syncthreads();
+    const int gw = blockIdx.x * kWarpsPerCta + warp;
+    const int begin = min(gw * seg, n), end = min(begin + seg, n);
+    warp_histogram(ids, begin, end, E, cnt + warp * E);
+    // column sums of counts[cta][e]: `parts` threads share one expert when there are fewer experts than threads
+    const int ctas = gridDim.x, me = blockIdx.x;
+    const int parts = max(1, kThreads / E);
+    for (int idx = threadIdx.x; idx < E * parts; idx += kThreads) {   // consecutive threads, consecutive experts
+        const int e = idx % E, part = idx / E;
+        int t = 0, p = 0;
+#pragma unroll 8
+        for (int c = part; c < ctas; c += parts) {
+            const int v = __ldg(counts + static_cast<size_t>(c) * E + e);
+            t += v;
+            p += c < me ? v : 0;
         }
-        if (lane == 0) tot[e] = carry;
+        atomicAdd(&tot[e], t);   // shared-memory integer adds: the sum does not depend on their order
+        atomicAdd(&pre[e], p);
     }
     __syncthreads();
     block_offsets(tot, offs, wsum, E, pad_to);
     const int total = offs[E];
-    if (threadIdx.x == 0) npp[0] = total;
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) offs_out[e] = offs[e];
-    for (int j = threadIdx.x; j < max_blocks; j += blockDim.x) {
+    if (me == 0 && threadIdx.x == 0) npp[0] = total;
+    for (int j = me * kThreads + threadIdx.x; j < max_blocks; j += ctas * kThreads) {
         const int row = j * block_m;
         expert_ids[j] = row >= total ? E - 1 : find_expert(offs, E, row);
     }
-}
-
-__global__ void __launch_bounds__(kThreads) moe_align_scatter_kernel(
-    const int32_t *__restrict__ ids, int n, int E, int seg, int num_warps, const int *__restrict__ counts,
-    const int *__restrict__ offs, int32_t *__restrict__ sorted, int max_padded) {
-    extern __shared__ int sm[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int *cur = sm + warp * E;
-    const int gw = blockIdx.x * kWarpsPerCta + warp;
-    for (int e = lane; e < E; e += 32) cur[e] = counts[static_cast<size_t>(e) * num_warps + gw] + offs[e];
-    __syncwarp();
-    const int begin = min(gw * seg, n), end = min(begin + seg, n);
-    warp_scatter(ids, begin, end, E, cur, sorted, max_padded);
+    for (int e = threadIdx.x; e < E; e += kThreads) {
+        int run = offs[e] + pre[e];
+#pragma unroll
+        for (int w = 0; w < kWarpsPerCta; ++w) {
+            const int c = cnt[w * E + e];
+            cnt[w * E + e] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    warp_scatter(ids, begin, end, E, cnt + warp * E, sorted, max_padded);
 }
 
 struct Plan {
     int ctas;       // grid of the histogram / scatter kernels (0 = single-CTA path)
-    int num_warps;
     int seg;        // ids per warp (multiple of 32)
-    size_t ws_ints; // scratch ints
+    size_t ws_ints; // scratch ints: counts[ctas][E]
 };
+
+constexpr int kIdsPerCtaMin = 2048;
 
 Plan make_plan(int n, int E) {
     Plan p{};
     if (n <= kSmallN) return p;
-    int warps = (n + kIdsPerWarpMin - 1) / kIdsPerWarpMin;
-    int ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
-    const int max_ctas = 2 * sm_count();
-    if (ctas > max_ctas) ctas = max_ctas;
+    int ctas = (n + kIdsPerCtaMin - 1) / kIdsPerCtaMin;
+    ctas = std::max(1, std::min(ctas, sm_count()));
     p.ctas = ctas;
-    p.num_warps = ctas * kWarpsPerCta;
-    p.seg = ((n + p.num_warps - 1) / p.num_warps + 31) & ~31;
-    p.ws_ints = static_cast<size_t>(E) * p.num_warps + E + 1;
+    const int warps = ctas * kWarpsPerCta;
+    p.seg = ((n + warps - 1) / warps + 31) & ~31;
+    p.ws_ints = static_cast<size_t>(E) * ctas;
     return p;
 }
 
@@ -287,17 +329,13 @@ int launch(const int32_t *topk_ids, int32_t *sorted, int32_t *expert_ids, int32_
         return PMOE_OK;
     }
     int *counts = ws;
-    int *offs = ws + static_cast<size_t>(E) * p.num_warps;
-    const size_t smem_w = static_cast<size_t>(kWarpsPerCta) * E * sizeof(int);
-    moe_align_hist_kernel<<<p.ctas, kThreads, smem_w, stream>>>(topk_ids, n, E, p.seg, p.num_warps, counts,
-                                                                sorted, max_padded);
+    const size_t smem_h = static_cast<size_t>(kWarpsPerCta) * E * sizeof(int);
+    moe_align_hist_kernel<<<p.ctas, kThreads, smem_h, stream>>>(topk_ids, n, E, p.seg, counts, sorted, max_padded);
     PMOE_CUDA_OK(cudaGetLastError());
-    const size_t smem_s = (2 * static_cast<size_t>(E) + 1 + 32) * sizeof(int);
-    moe_align_scan_kernel<<<1, 1024, smem_s, stream>>>(counts, p.num_warps, E, block_m, pad_to, offs, npp,
-                                                       expert_ids, max_blocks);
-    PMOE_CUDA_OK(cudaGetLastError());
-    moe_align_scatter_kernel<<<p.ctas, kThreads, smem_w, stream>>>(topk_ids, n, E, p.seg, p.num_warps, counts,
-                                                                   offs, sorted, max_padded);
+    const size_t smem_s = (static_cast<size_t>(kWarpsPerCta) * E + 3 * static_cast<size_t>(E) + 1 + kWarpsPerCta) *
+                          sizeof(int);
+    moe_align_scatter_kernel<<<p.ctas, kThreads, smem_s, stream>>>(topk_ids, n, E, p.seg, counts, block_m, pad_to,
+                                                                   sorted, expert_ids, npp, max_padded, max_blocks);
     PMOE_CUDA_OK(cudaGetLastError());
     return PMOE_OK;
 }
@@ -351,9 +389,9 @@ extern "C" int pmoe_moe_align(const int32_t *topk_ids, int32_t *sorted_token_ids
 // runs: an inference server whose memory budget is fixed after start-up and which forbids further
 // driver allocations, a plugin running inside another framework's stream callback or allocator
 // hook, a process whose whole device memory has already been handed to a pool it does not own.
-// For them the per-warp counter matrix and the offset table live in a fixed array that is part of
-// the library image. Every GPU that loads the library carries these 4 MiB until the process exits.
-#define PMOE_STATIC_SCRATCH_INTS (1u << 20)  /* 4 MiB: the stated maximum */
+// For them the per-CTA counter matrix lives in a fixed array that is part of
+// the library image. Every GPU that loads the library carries these 256 KiB until the process exits.
+#define PMOE_STATIC_SCRATCH_INTS (1u << 16)  /* 256 KiB: the stated maximum */
 static __device__ __align__(256) int g_align_static_scratch[PMOE_STATIC_SCRATCH_INTS];
 
 namespace pmoe {
@@ -399,7 +437,7 @@ extern "C" int pmoe_moe_align_static(const int32_t *topk_ids, int32_t *sorted_to
     if (p.ws_ints)
         if (int rc = static_scratch_ptr(&scratch)) return rc;
     // Nothing in the scratch has to start at zero: the histogram pass writes every counter of the
-    // matrix and the scan pass writes every offset before anything reads them.
+    // matrix before the scatter pass reads any of them.
     return launch(topk_ids, sorted_token_ids, expert_ids, num_tokens_post_padded, n, num_experts, block_m, pad_to,
                   max_padded, max_blocks, p, scratch, stream);
 }

@@ -14,6 +14,7 @@
 // ep_combine: out[t, :] = bf16( sum over the token's visits of y[visit, :] ), fp32 accumulation; one pass,
 //   HBM-bound: V*K*2 bytes read + T*K*2 written.
 #include <cuda_bf16.h>
+#include <string.h>
 
 #include <algorithm>
 
@@ -194,6 +195,386 @@ extern "C" int pmoe_ep_combine(const void *y, const int32_t *slot_of, void *out,
     if (T == 0) return PMOE_OK;
     ep_combine_kernel<<<std::min(T, 8 * sm_count()), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16 *>(y), slot_of, static_cast<__nv_bfloat16 *>(out), T, world, K);
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+// =============================================================================================
+// Device-driven exchange over peer memory (no NCCL call, no host synchronisation in a step)
+//
+// Every rank owns ONE buffer of identical layout (allocated by pmoe_ep_buffer_alloc, mapped into the peers
+// through CUDA IPC). It starts with a header the PEERS write into,
+//     int32 cnt_flag[32] | disp_flag[32] | comb_flag[32] | M[32][32]
+// (M[s][g] = number of visits rank s sends to rank g in the current step; flag[s] = the last step for which
+// rank s has finished the corresponding phase), followed at caller-chosen offsets by the row area (token rows
+// received), an optional auxiliary row area (their MX scales), the meta area (top_k local expert ids + top_k
+// routing weights per received row) and the return area (one bf16 row per visit this rank SENT).
+// One step on rank `me`, all on one stream, step number `epoch` (1, 2, ...):
+//   publish   my counts row -> M[me][.] of every rank, then cnt_flag[me] = epoch on every rank
+//   push      wait until cnt_flag[s] >= epoch for all s (now M is complete and identical everywhere); visit v to
+//             rank g is the j-th of my visits to g -> row  sum_{s<me} M[s][g] + j  of g's row / aux / meta areas
+//             (plain 16-byte stores to peer memory); then disp_flag[me] = epoch on every rank
+//   prepare   wait for disp_flag[s] >= epoch for all s; R = sum_s M[s][me] rows arrived; split the meta area into
+//             the id table (rows >= R masked with -1) and the weight table for moe_align / the fused kernels
+//   (moe_align + fused MoE FFN on the local experts -> y[R, K])
+//   return    row i (the j-th row from source s) -> return area of s at  sum_{g<me} M[s][g] + j ; comb_flag[me] =
+//             epoch on every rank
+//   combine   wait for comb_flag[g] >= epoch for all g; out[t] = sum of the token's visit rows (fp32)
+// A rank writes into a peer's areas for step e+1 only after its own combine of step e, which waited for that
+// peer's return of step e - and the peer returns only after it has consumed the rows, meta and counts of step
+// e. So one set of areas is enough. Only plain loads / stores and release / acquire flag accesses touch peer
+// memory: no TMA, no multicast, no library kernel. Every wait is bounded (status word, pmoe_device_status).
+// =============================================================================================
+namespace pmoe {
+
+__device__ int g_status_ep = 0;
+__device__ unsigned long long g_ep_wait_ns = 2000000000ull;
+
+namespace {
+
+constexpr int kHdrFlagInts = 32;
+constexpr int kHdrInts = 3 * kHdrFlagInts + kMaxRanks * kMaxRanks;
+constexpr int ST_TIMEOUT_EP_COUNTS = 10, ST_TIMEOUT_EP_DISPATCH = 11, ST_TIMEOUT_EP_RETURN = 12;
+
+struct Header {
+    int32_t cnt_flag[kHdrFlagInts], disp_flag[kHdrFlagInts], comb_flag[kHdrFlagInts];
+    int32_t M[kMaxRanks][kMaxRanks];
+};
+static_assert(sizeof(Header) == kHdrInts * 4, "header layout");
+
+__device__ __forceinline__ int ld_acquire_sys(const int32_t *p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int32_t *p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// counts written by the peers: read past L1
+__device__ __forceinline__ int ld_count(const int32_t *p) { return *reinterpret_cast<const volatile int32_t *>(p); }
+__device__ __forceinline__ unsigned long long timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Threads 0..world-1 of the CTA wait until flag[s] >= epoch; every thread then continues. Returns false
+// (after recording `code`) when the limit ran out - the caller goes on with whatever has arrived, so that the
+// kernel still ends; the step's result is then invalid and the status word says so.
+__device__ bool wait_flags(const int32_t *flag, int world, int epoch, int code) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const unsigned long long limit = *reinterpret_cast<volatile unsigned long long *>(&g_ep_wait_ns);
+        const unsigned long long t0 = timer_ns();
+        unsigned n = 0;
+        while (ld_acquire_sys(flag + threadIdx.x) - epoch < 0) {
+            if ((++n & 63u) == 0) {
+                if (*reinterpret_cast<volatile int *>(&g_status_ep) != 0 || timer_ns() - t0 > limit) {
+                    atomicCAS(&g_status_ep, 0, code);
+                    s_ok = 0;
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    return s_ok != 0;
+}
+
+__global__ void __launch_bounds__(32)
+ep_publish_counts_kernel(const int32_t *__restrict__ counts, void *const *__restrict__ peers, int me, int world,
+                         int epoch) {
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    Header *h = static_cast<Header *>(peers[p]);
+    for (int g = 0; g < world; ++g) h->M[me][g] = counts[g];
+    __threadfence_system();
+    st_release_sys(&h->cnt_flag[me], epoch);
+}
+
+// which: 1 = disp_flag, 2 = comb_flag. Runs after the kernel whose stores it announces (stream order).
+__global__ void __launch_bounds__(32)
+ep_signal_kernel(void *const *__restrict__ peers, int me, int world, int epoch, int which) {
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    Header *h = static_cast<Header *>(peers[p]);
+    __threadfence_system();
+    st_release_sys(which == 1 ? &h->disp_flag[me] : &h->comb_flag[me], epoch);
+}
+
+struct PushArgs {
+    const uint8_t *x;            // [T, row_bytes]
+    const uint8_t *aux;          // [T, aux_bytes] or null
+    const int32_t *visit_token;  // [V]
+    const int32_t *visit_meta;   // [V, meta_ints]
+    void *const *peers;
+    size_t rows_off, aux_off, meta_off;
+    int row_bytes, aux_bytes, meta_ints, T, me, world, epoch, row_cap;
+};
+
+__global__ void __launch_bounds__(256)
+ep_push_rows_kernel(const PushArgs a) {
+    __shared__ int s_send_base[kMaxRanks + 1];   // first visit of mine to rank g
+    __shared__ int s_dst_base[kMaxRanks];        // first row of mine in rank g's areas
+    const Header *h = static_cast<const Header *>(a.peers[a.me]);
+    wait_flags(h->cnt_flag, a.world, a.epoch, ST_TIMEOUT_EP_COUNTS);
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int g = 0; g < a.world; ++g) {
+            s_send_base[g] = run;
+            run += ld_count(&h->M[a.me][g]);
+            int before = 0;
+            for (int s = 0; s < a.me; ++s) before += ld_count(&h->M[s][g]);
+            s_dst_base[g] = before;
+        }
+        s_send_base[a.world] = run;
+    }
+    __syncthreads();
+    const int V = min(s_send_base[a.world], a.T * a.world);
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    for (int v = blockIdx.x * warps + (threadIdx.x >> 5); v < V; v += gridDim.x * warps) {
+        int g = 0;
+        while (g + 1 < a.world && s_send_base[g + 1] <= v) ++g;
+        const long long row = static_cast<long long>(s_dst_base[g]) + (v - s_send_base[g]);
+        if (row >= a.row_cap) continue;            // cannot happen with a row_cap of world * T; never write past an area
+        const int tok = a.visit_token[v];
+        if (tok < 0 || tok >= a.T) continue;
+        uint8_t *base = static_cast<uint8_t *>(a.peers[g]);
+        const int4 *src = reinterpret_cast<const int4 *>(a.x + static_cast<size_t>(tok) * a.row_bytes);
+        int4 *dst = reinterpret_cast<int4 *>(base + a.rows_off + static_cast<size_t>(row) * a.row_bytes);
+        for (int c = lane; c < a.row_bytes / 16; c += 32) dst[c] = __ldg(src + c);
+        if (a.aux) {
+            const int32_t *asrc = reinterpret_cast<const int32_t *>(a.aux + static_cast<size_t>(tok) * a.aux_bytes);
+            int32_t *adst = reinterpret_cast<int32_t *>(base + a.aux_off + static_cast<size_t>(row) * a.aux_bytes);
+            for (int c = lane; c < a.aux_bytes / 4; c += 32) adst[c] = __ldg(asrc + c);
+        }
+        const int32_t *msrc = a.visit_meta + static_cast<size_t>(v) * a.meta_ints;
+        int32_t *mdst = reinterpret_cast<int32_t *>(base + a.meta_off) + static_cast<size_t>(row) * a.meta_ints;
+        for (int c = lane; c < a.meta_ints; c += 32) mdst[c] = msrc[c];
+    }
+}
+
+// ids[i, j] = local expert id of slot j of received row i (-1 for rows that did not arrive), wts[i, j] its
+// routing weight; num_rows[0] = rows that arrived.
+__global__ void __launch_bounds__(256)
+ep_recv_prepare_kernel(const void *local_buf, size_t meta_off, int top_k, int row_cap, int32_t *__restrict__ ids,
+                       float *__restrict__ wts, int32_t *__restrict__ num_rows, int me, int world, int epoch) {
+    const Header *h = static_cast<const Header *>(local_buf);
+    wait_flags(h->disp_flag, world, epoch, ST_TIMEOUT_EP_DISPATCH);
+    int R = 0;
+    for (int s = 0; s < world; ++s) R += ld_count(&h->M[s][me]);
+    R = min(R, row_cap);
+    if (blockIdx.x == 0 && threadIdx.x == 0) num_rows[0] = R;
+    const int32_t *meta = reinterpret_cast<const int32_t *>(static_cast<const uint8_t *>(local_buf) + meta_off);
+    const long long total = static_cast<long long>(row_cap) * top_k;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / top_k), j = static_cast<int>(i - static_cast<long long>(row) * top_k);
+        const bool live = row < R;
+        ids[i] = live ? __ldcg(meta + static_cast<size_t>(row) * 2 * top_k + j) : -1;
+        wts[i] = live ? __int_as_float(__ldcg(meta + static_cast<size_t>(row) * 2 * top_k + top_k + j)) : 0.f;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+ep_push_back_kernel(const __nv_bfloat16 *__restrict__ y, int K, void *const *__restrict__ peers, size_t y_off, int me,
+                    int world, int row_cap, int ret_cap) {
+    __shared__ int s_recv_base[kMaxRanks + 1];   // first local row that came from rank s
+    __shared__ int s_ret_base[kMaxRanks];        // first visit of rank s that went to me (index in s's return area)
+    const Header *h = static_cast<const Header *>(peers[me]);
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int s = 0; s < world; ++s) {
+            s_recv_base[s] = run;
+            run += ld_count(&h->M[s][me]);
+            int before = 0;
+            for (int g = 0; g < me; ++g) before += ld_count(&h->M[s][g]);
+            s_ret_base[s] = before;
+        }
+        s_recv_base[world] = run;
+    }
+    __syncthreads();
+    const int R = min(s_recv_base[world], row_cap);
+    const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+    for (int i = blockIdx.x * warps + (threadIdx.x >> 5); i < R; i += gridDim.x * warps) {
+        int s = 0;
+        while (s + 1 < world && s_recv_base[s + 1] <= i) ++s;
+        const long long v = static_cast<long long>(s_ret_base[s]) + (i - s_recv_base[s]);
+        if (v >= ret_cap) continue;
+        const int4 *src = reinterpret_cast<const int4 *>(y + static_cast<size_t>(i) * K);
+        int4 *dst = reinterpret_cast<int4 *>(static_cast<uint8_t *>(peers[s]) + y_off) + static_cast<size_t>(v) * (K / 8);
+        for (int c = lane; c < K / 8; c += 32) dst[c] = src[c];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+ep_combine_peer_kernel(const void *local_buf, size_t y_off, const int32_t *__restrict__ slot_of,
+                       __nv_bfloat16 *__restrict__ out, int T, int world, int K, int epoch) {
+    const Header *h = static_cast<const Header *>(local_buf);
+    wait_flags(h->comb_flag, world, epoch, ST_TIMEOUT_EP_RETURN);
+    const __nv_bfloat16 *y = reinterpret_cast<const __nv_bfloat16 *>(static_cast<const uint8_t *>(local_buf) + y_off);
+    const int chunks = K / 8;
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int g = 0; g < world; ++g) {
+                const int slot = slot_of[static_cast<long long>(t) * world + g];
+                if (slot < 0) continue;
+                // written by a peer during this step: bypass L1 (no stale line from an earlier step)
+                const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(y + static_cast<long long>(slot) * K) + c);
+                const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[2 * i] += __low2float(hh[i]);
+                    acc[2 * i + 1] += __high2float(hh[i]);
+                }
+            }
+            uint4 r;
+            __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&r);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * K)[c] = r;
+        }
+    }
+}
+
+int check_world(int me, int world, const char *what) {
+    PMOE_REQUIRE(world >= 1 && world <= kMaxRanks && me >= 0 && me < world, PMOE_ERR_BAD_ARG,
+                 "%s: 0 <= rank < world <= %d required", what, kMaxRanks);
+    return PMOE_OK;
+}
+
+}  // namespace
+
+int status_fetch_ep(int *value, bool reset) {
+    if (value) PMOE_CUDA_OK(cudaMemcpyFromSymbol(value, g_status_ep, sizeof(int)));
+    if (reset) {
+        const int zero = 0;
+        PMOE_CUDA_OK(cudaMemcpyToSymbol(g_status_ep, &zero, sizeof(int)));
+    }
+    return PMOE_OK;
+}
+int wait_ns_store_ep(unsigned long long ns) {
+    PMOE_CUDA_OK(cudaMemcpyToSymbol(g_ep_wait_ns, &ns, sizeof(ns)));
+    return PMOE_OK;
+}
+
+}  // namespace pmoe
+
+extern "C" size_t pmoe_ep_header_bytes(void) { return 8192; }   // sizeof(Header) rounded up; areas start behind it
+
+extern "C" int pmoe_ep_buffer_alloc(size_t bytes, void **ptr, void *ipc_handle) {
+    using namespace pmoe;
+    PMOE_REQUIRE(ptr && ipc_handle && bytes >= pmoe_ep_header_bytes(), PMOE_ERR_BAD_ARG,
+                 "ep_buffer_alloc: null pointer or a buffer smaller than its header");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void *p = nullptr;
+    PMOE_CUDA_OK(cudaMalloc(&p, bytes));
+    PMOE_CUDA_OK(cudaMemset(p, 0, bytes));
+    PMOE_CUDA_OK(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t h;
+    PMOE_CUDA_OK(cudaIpcGetMemHandle(&h, p));
+    memcpy(ipc_handle, &h, sizeof(h));
+    *ptr = p;
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_buffer_open(const void *ipc_handle, void **ptr) {
+    using namespace pmoe;
+    PMOE_REQUIRE(ptr && ipc_handle, PMOE_ERR_BAD_ARG, "ep_buffer_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handle, sizeof(h));
+    PMOE_CUDA_OK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_buffer_close(void *ptr) {
+    using namespace pmoe;
+    PMOE_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_buffer_free(void *ptr) {
+    using namespace pmoe;
+    PMOE_CUDA_OK(cudaFree(ptr));
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_publish_counts(const int32_t *counts, void *const *peer_bufs, int rank, int world, int epoch,
+                                      pmoe_stream_t stream) {
+    using namespace pmoe;
+    PMOE_REQUIRE(counts && peer_bufs, PMOE_ERR_BAD_ARG, "ep_publish_counts: null pointer");
+    if (int rc = check_world(rank, world, "ep_publish_counts")) return rc;
+    ep_publish_counts_kernel<<<1, 32, 0, stream>>>(counts, peer_bufs, rank, world, epoch);
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_push_rows(const void *x, int row_bytes, const void *aux, int aux_bytes,
+                                 const int32_t *visit_token, const int32_t *visit_meta, int top_k, int T,
+                                 void *const *peer_bufs, size_t rows_off, size_t aux_off, size_t meta_off, int row_cap,
+                                 int rank, int world, int epoch, pmoe_stream_t stream) {
+    using namespace pmoe;
+    PMOE_REQUIRE(x && visit_token && visit_meta && peer_bufs, PMOE_ERR_BAD_ARG, "ep_push_rows: null pointer");
+    if (int rc = check_world(rank, world, "ep_push_rows")) return rc;
+    PMOE_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0 && aux_bytes >= 0 && aux_bytes % 4 == 0 && top_k > 0 && T >= 0,
+                 PMOE_ERR_BAD_ARG, "ep_push_rows: rows must be multiples of 16 bytes, auxiliary rows of 4 bytes");
+    PMOE_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(aux) | rows_off | aux_off | meta_off) & 15) == 0,
+                 PMOE_ERR_BAD_ARG, "ep_push_rows: x, aux and the area offsets must be 16-byte aligned");
+    PushArgs a{static_cast<const uint8_t *>(x), aux_bytes ? static_cast<const uint8_t *>(aux) : nullptr, visit_token,
+               visit_meta, peer_bufs, rows_off, aux_off, meta_off, row_bytes, aux_bytes, 2 * top_k, T, rank, world, epoch,
+               row_cap};
+    const int grid = std::max(1, std::min(8 * sm_count(), (T * std::min(top_k, world) + 7) / 8));
+    ep_push_rows_kernel<<<grid, 256, 0, stream>>>(a);
+    PMOE_CUDA_OK(cudaGetLastError());
+    ep_signal_kernel<<<1, 32, 0, stream>>>(peer_bufs, rank, world, epoch, 1);
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_recv_prepare(const void *local_buf, size_t meta_off, int top_k, int row_cap, int32_t *local_ids,
+                                    float *local_weights, int32_t *num_rows, int rank, int world, int epoch,
+                                    pmoe_stream_t stream) {
+    using namespace pmoe;
+    PMOE_REQUIRE(local_buf && local_ids && local_weights && num_rows, PMOE_ERR_BAD_ARG, "ep_recv_prepare: null pointer");
+    if (int rc = check_world(rank, world, "ep_recv_prepare")) return rc;
+    PMOE_REQUIRE(top_k > 0 && row_cap > 0, PMOE_ERR_BAD_ARG, "ep_recv_prepare: top_k and row_cap must be positive");
+    const long long total = static_cast<long long>(row_cap) * top_k;
+    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(4 * sm_count(), (total + 255) / 256)));
+    ep_recv_prepare_kernel<<<grid, 256, 0, stream>>>(local_buf, meta_off, top_k, row_cap, local_ids, local_weights, num_rows,
+                                                     rank, world, epoch);
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_push_back(const void *y, int K, void *const *peer_bufs, size_t y_off, int row_cap, int ret_cap,
+                                 int rank, int world, int epoch, pmoe_stream_t stream) {
+    using namespace pmoe;
+    PMOE_REQUIRE(y && peer_bufs, PMOE_ERR_BAD_ARG, "ep_push_back: null pointer");
+    if (int rc = check_world(rank, world, "ep_push_back")) return rc;
+    PMOE_REQUIRE(K > 0 && K % 8 == 0 && ((reinterpret_cast<uintptr_t>(y) | y_off) & 15) == 0, PMOE_ERR_BAD_ARG,
+                 "ep_push_back: K must be a multiple of 8, y and the return area 16-byte aligned");
+    const int grid = std::max(1, std::min(8 * sm_count(), (row_cap + 7) / 8));
+    ep_push_back_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(y), K, peer_bufs, y_off, rank, world,
+                                                  row_cap, ret_cap);
+    PMOE_CUDA_OK(cudaGetLastError());
+    ep_signal_kernel<<<1, 32, 0, stream>>>(peer_bufs, rank, world, epoch, 2);
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_combine_peer(const void *local_buf, size_t y_off, const int32_t *slot_of, void *out, int T,
+                                    int world, int K, int epoch, pmoe_stream_t stream) {
+    using namespace pmoe;
+    PMOE_REQUIRE(local_buf && slot_of && out, PMOE_ERR_BAD_ARG, "ep_combine_peer: null pointer");
+    PMOE_REQUIRE(T >= 0 && world > 0 && world <= kMaxRanks && K > 0 && K % 8 == 0, PMOE_ERR_BAD_ARG,
+                 "ep_combine_peer: T >= 0, 1 <= world <= %d and K a positive multiple of 8 required", kMaxRanks);
+    PMOE_REQUIRE(((reinterpret_cast<uintptr_t>(out) | y_off) & 15) == 0, PMOE_ERR_BAD_ARG,
+                 "ep_combine_peer: out and the return area must be 16-byte aligned");
+    ep_combine_peer_kernel<<<std::max(1, std::min(T, 8 * sm_count())), 256, 0, stream>>>(
+        local_buf, y_off, slot_of, static_cast<__nv_bfloat16 *>(out), T, world, K, epoch);
     PMOE_CUDA_OK(cudaGetLastError());
     return PMOE_OK;
 }

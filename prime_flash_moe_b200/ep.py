@@ -18,6 +18,13 @@ The unit of exchange is a VISIT: a (token, destination rank) pair such that at l
 4. **combine**: the reverse all-to-all of the bf16 partial sums, then each token's visits are added in fp32 at
    the source rank (``pmoe_ep_combine``).
 
+With ``combine="peer"`` (``"auto"`` picks it when every rank can map its peers' memory) steps 1-4 run without NCCL and
+without any host synchronisation: every rank owns one buffer that its peers map through CUDA IPC at set-up
+(``PeerExchange``), and the kernels of ``csrc/moe_ep.cu`` store the visiting rows, their slot tables and, on the way
+back, the partial sums straight into the destination rank's buffer over NVLink, with per-phase step flags in the
+buffer's header (release / acquire, every wait bounded). The visit counts travel the same way (a ``G x G`` matrix in
+every header), so each rank computes where its rows land and no split sizes are needed on the host.
+
 The plan has a plain, device-agnostic torch version used for CPU tensors (ranks over ``gloo`` in the tests)
 and as the checker of the CUDA one; the expert compute is a callable, by default the CUDA kernels
 (``LocalExperts``), which raises without a GPU - there is no CPU implementation of the kernels in this package.
@@ -123,6 +130,87 @@ class LocalExperts:
         return out
 
 
+class _DeviceBytes:
+    """``nbytes`` of device memory at ``ptr`` for ``torch.as_tensor`` (zero-copy view through the CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerExchange:
+    """The symmetric buffers of the peer-memory exchange: one ``cudaMalloc`` per rank (``pmoe_ep_buffer_alloc``), mapped
+    into every other rank through CUDA IPC; handles travel once over the process group at set-up. Layout per rank:
+    header | rows [row_cap, row_bytes] | auxiliary rows [row_cap, aux_bytes] | meta int32 [row_cap, 2*top_k] | return
+    bf16 [ret_cap, K], with ``row_cap = G * T`` and ``ret_cap = T * min(top_k, G)`` (``T`` = tokens per rank)."""
+
+    def __init__(self, T: int, K: int, top_k: int, row_bytes: int, aux_bytes: int, group=None, device=None):
+        import ctypes as C
+
+        from . import capi
+        self.lib = capi.lib()
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.T, self.K, self.top_k, self.row_bytes, self.aux_bytes = T, K, top_k, row_bytes, aux_bytes
+        self.row_cap, self.ret_cap = self.world * T, T * min(top_k, self.world)
+        up = lambda v: (v + 1023) // 1024 * 1024
+        self.rows_off = up(self.lib.pmoe_ep_header_bytes())
+        self.aux_off = up(self.rows_off + self.row_cap * row_bytes)
+        self.meta_off = up(self.aux_off + self.row_cap * aux_bytes)
+        self.y_off = up(self.meta_off + self.row_cap * 2 * top_k * 4)
+        self.nbytes = up(self.y_off + self.ret_cap * K * 2)
+        with torch.cuda.device(self.device):
+            ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+            capi._check(self.lib.pmoe_ep_buffer_alloc(self.nbytes, C.byref(ptr), handle))
+            self.local_ptr = ptr.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self.peer_ptrs = []
+            for g, h in enumerate(handles):
+                if g == self.rank:
+                    self.peer_ptrs.append(self.local_ptr)
+                    continue
+                q = C.c_void_p()
+                capi._check(self.lib.pmoe_ep_buffer_open(C.create_string_buffer(h, 64), C.byref(q)))
+                self.peer_ptrs.append(q.value)
+        self.table = torch.tensor(self.peer_ptrs, dtype=torch.int64, device=self.device)
+        self.buf = torch.as_tensor(_DeviceBytes(self.local_ptr, self.nbytes), device=self.device)
+        self.epoch = 0
+        dist.barrier(group=group)        # every rank has mapped every buffer before the first store
+
+    def area(self, off: int, rows: int, row_bytes: int) -> torch.Tensor:
+        return self.buf[off:off + rows * row_bytes].view(rows, row_bytes)
+
+    def close(self):
+        """Unmaps the peers and frees the local buffer; collective (no rank frees while a peer may still store)."""
+        if self.local_ptr is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for g, q in enumerate(self.peer_ptrs):
+                if g != self.rank:
+                    self.lib.pmoe_ep_buffer_close(q)
+            dist.barrier(group=self.group)
+            self.buf = None
+            self.lib.pmoe_ep_buffer_free(self.local_ptr)
+        self.local_ptr = None
+
+
+def peer_exchange_possible(group=None) -> bool:
+    """True when this process group is one process per GPU on one node and every GPU can map every other one."""
+    if not (dist.is_initialized() and torch.cuda.is_available()) or dist.get_backend(group) == "gloo":
+        return False
+    world = dist.get_world_size(group)
+    if world < 2 or world > torch.cuda.device_count() or world > 32:
+        return False
+    me = torch.cuda.current_device()
+    ok = all(g == me or torch.cuda.can_device_access_peer(me, g) for g in range(torch.cuda.device_count()))
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(flag.item())
+
+
 class ExpertParallelMoE:
     """``out = layer(x, topk_ids, topk_weights[, x_scales])`` with GLOBAL expert ids in ``topk_ids``.
 
@@ -135,11 +223,66 @@ class ExpertParallelMoE:
         self.experts = experts
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.last_recv_rows = 0
-        self.last_sent_rows = 0
-        self.combine_mode = "nccl"
+        self._recv_rows = 0
+        self._sent_rows = 0
+        assert combine in ("nccl", "peer", "auto")
+        if combine == "auto":
+            combine = "peer" if (self.world > 1 and peer_exchange_possible(group)) else "nccl"
+        self.combine_mode = combine if self.world > 1 else "nccl"
+        self.exchange: Optional[PeerExchange] = None
+
+    # rows this rank computed / sent in the last call; in peer mode the counts stay on the device until asked for
+    @property
+    def last_recv_rows(self) -> int:
+        return int(self._recv_rows.item()) if torch.is_tensor(self._recv_rows) else self._recv_rows
+
+    @property
+    def last_sent_rows(self) -> int:
+        return int(self._sent_rows.sum().item()) if torch.is_tensor(self._sent_rows) else self._sent_rows
+
+    def _forward_peer(self, x, topk_ids, topk_weights, x_scales=None):
+        from . import capi
+        T, K = x.shape
+        top_k = topk_ids.shape[1]
+        row_bytes = K * x.element_size()
+        aux_bytes = 0 if x_scales is None else x_scales.shape[1] * x_scales.element_size()
+        ex = self.exchange
+        if ex is None or (ex.T, ex.K, ex.top_k, ex.row_bytes, ex.aux_bytes) != (T, K, top_k, row_bytes, aux_bytes):
+            if ex is not None:
+                ex.close()
+            ex = self.exchange = PeerExchange(T, K, top_k, row_bytes, aux_bytes, self.group, x.device)
+            self._ids = torch.empty(ex.row_cap, top_k, dtype=torch.int32, device=x.device)
+            self._wts = torch.empty(ex.row_cap, top_k, dtype=torch.float32, device=x.device)
+            self._num_rows = torch.zeros(1, dtype=torch.int32, device=x.device)
+        lib, G, me = ex.lib, self.world, ex.rank
+        plan = make_dispatch_plan(topk_ids, topk_weights, self.num_experts, G)
+        ex.epoch += 1
+        e, tab, st = ex.epoch, ex.table.data_ptr(), torch.cuda.current_stream().cuda_stream
+        x = x.contiguous()
+        aux = None if x_scales is None else x_scales.contiguous()
+        with torch.cuda.device(x.device):
+            capi._check(lib.pmoe_ep_publish_counts(plan.counts.data_ptr(), tab, me, G, e, st))
+            capi._check(lib.pmoe_ep_push_rows(x.data_ptr(), row_bytes, 0 if aux is None else aux.data_ptr(), aux_bytes,
+                                              plan.visit_token.data_ptr(), plan.visit_meta.data_ptr(), top_k, T, tab,
+                                              ex.rows_off, ex.aux_off, ex.meta_off, ex.row_cap, me, G, e, st))
+            capi._check(lib.pmoe_ep_recv_prepare(ex.local_ptr, ex.meta_off, top_k, ex.row_cap, self._ids.data_ptr(),
+                                                 self._wts.data_ptr(), self._num_rows.data_ptr(), me, G, e, st))
+            rows = ex.area(ex.rows_off, ex.row_cap, row_bytes).view(x.dtype)
+            if aux is None:
+                y = self.experts(rows, self._ids, self._wts)
+            else:
+                y = self.experts(rows, self._ids, self._wts, ex.area(ex.aux_off, ex.row_cap, aux_bytes).view(aux.dtype))
+            capi._check(lib.pmoe_ep_push_back(y.data_ptr(), K, tab, ex.y_off, ex.row_cap, ex.ret_cap, me, G, e, st))
+            out = torch.empty(T, K, dtype=torch.bfloat16, device=x.device)
+            capi._check(lib.pmoe_ep_combine_peer(ex.local_ptr, ex.y_off, plan.slot_of.data_ptr(), out.data_ptr(), T, G, K,
+                                                 e, st))
+        self._recv_rows, self._sent_rows = self._num_rows, plan.counts
+        self._keep = (plan, y, x, aux)     # alive until the next call: the kernels above may still be running
+        return out
 
     def forward(self, x, topk_ids, topk_weights, x_scales=None):
+        if self.combine_mode == "peer" and x.is_cuda:
+            return self._forward_peer(x, topk_ids, topk_weights, x_scales)
         T, K = x.shape
         top_k = topk_ids.shape[1]
         plan = make_dispatch_plan(topk_ids, topk_weights, self.num_experts, self.world)
@@ -160,7 +303,7 @@ class ExpertParallelMoE:
             scales = _all_to_all_rows(send_scales, send, recv, self.group) if x_scales is not None else None
         else:
             rows, scales = send_rows, send_scales
-        self.last_sent_rows, self.last_recv_rows = V, rows.shape[0]
+        self._sent_rows, self._recv_rows = V, rows.shape[0]
         local_ids = meta[:, :top_k].contiguous()
         weights = meta[:, top_k:].contiguous().view(torch.float32)
         y = (self.experts(rows, local_ids, weights, scales) if scales is not None

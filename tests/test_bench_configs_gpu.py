@@ -160,9 +160,13 @@ def test_c4_zipf_shape(dtype):
     -1 padding rows, a few experts with thousands of rows."""
     import prime_flash_moe_b200 as P
     T, K, E, N, k = 8192, 4096, 128, 3072, 8
-    x, w1, w2, ids, wts = device_case(T, K, E, N, k, seed=44, dist="zipf")
+    x, w1, w2, _, wts = device_case(T, K, E, N, k, seed=44, dist="zipf")
+    # Zipf over 120 of the 128 experts, placed by a seeded permutation: eight experts receive nothing
+    ids120, _ = O.make_routing(T, 120, k, 45, "zipf")
+    place = torch.randperm(E, generator=torch.Generator().manual_seed(46))[:120].to(torch.int32)
+    ids = place[ids120.long()].contiguous()
     counts = torch.bincount(ids.reshape(-1).long(), minlength=E)
-    assert int((counts == 0).sum()) > 0 and int(counts.max()) > 2048, "the case must hold empty and hot experts"
+    assert int((counts == 0).sum()) == 8 and int(counts.max()) > 2048, "the case must hold empty and hot experts"
     toks = spread(T, 24)
     if dtype == "bf16":
         out = run_bf16(x, w1, w2, ids, wts)

@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, mx, ret):
+def _worker(rank, world, port, mx, combine, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -35,27 +35,39 @@ def _worker(rank, world, port, mx, ret):
             experts = ep.LocalExperts(ep.shard_experts(w1q, rank, world).to(dev), ep.shard_experts(w2q, rank, world).to(dev),
                                       P.pack_scales_blocked(ep.shard_experts(w1s, rank, world)).to(dev),
                                       P.pack_scales_blocked(ep.shard_experts(w2s, rank, world)).to(dev))
-            layer = ep.ExpertParallelMoE(E, experts)
+            layer = ep.ExpertParallelMoE(E, experts, combine=combine)
+            assert layer.combine_mode == combine
+            # a first step on other routing, then the checked one: the buffers, flags and counts are reused
+            layer(xq[lo:hi].to(dev), ids[lo:hi].flip(0).contiguous().to(dev), wts[lo:hi].to(dev), xs[lo:hi].to(dev))
             out = layer(xq[lo:hi].to(dev), ids[lo:hi].to(dev), wts[lo:hi].to(dev), xs[lo:hi].to(dev))
             ref = O.moe_ref_fp32(O.dequantize_mx(xq, xs), O.dequantize_mx(w1q, w1s), O.dequantize_mx(w2q, w2s), ids, wts,
                                  requant_act=True)[lo:hi]
         else:
             experts = ep.LocalExperts(ep.shard_experts(w1, rank, world).to(dev), ep.shard_experts(w2, rank, world).to(dev))
-            layer = ep.ExpertParallelMoE(E, experts)
+            layer = ep.ExpertParallelMoE(E, experts, combine=combine)
+            assert layer.combine_mode == combine
+            layer(x[lo:hi].to(dev), ids[lo:hi].flip(0).contiguous().to(dev), wts[lo:hi].to(dev))
             out = layer(x[lo:hi].to(dev), ids[lo:hi].to(dev), wts[lo:hi].to(dev))
             ref = O.moe_ref_fp32(x, w1, w2, ids, wts)[lo:hi]
         torch.cuda.synchronize()
+        from prime_flash_moe_b200 import capi
+        assert capi.device_status() == 0
         ret[rank] = (O.max_rel_to_peak(out.cpu(), ref), layer.last_recv_rows, layer.last_sent_rows)
+        if layer.exchange is not None:
+            layer.exchange.close()
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("combine", ["nccl", "peer"])
 @pytest.mark.parametrize("mx", [False, True])
-def test_ep_two_gpus(mx):
+def test_ep_two_gpus(mx, combine):
+    """`nccl`: all-to-all dispatch / combine; `peer`: this library's kernels store rows, slot tables, counts and
+    partial sums into the other rank's buffer over NVLink (no NCCL call and no host sync inside a step)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, _free_port(), mx, ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), mx, combine, ret), nprocs=2, join=True)
     assert len(ret) == 2
     _, _, _, ids, _ = O.make_case(300 * 2, 1024, 16, 1024, 4, seed=11, dist="zipf")
     visits = sum(len(set(int(e) // 8 for e in row)) for row in ids.tolist())      # distinct (token, rank) pairs

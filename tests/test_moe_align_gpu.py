@@ -33,6 +33,7 @@ CASES = [
     (4096, 8, 2, 1, "uniform"), (4096, 8, 2, 2, "uniform"),
     (16384, 256, 8, 1, "uniform"), (65536, 128, 8, 1, "zipf"), (65536, 128, 8, 2, "zipf"),
     (3000, 1024, 8, 1, "uniform"), (5000, 1, 1, 1, "uniform"), (777, 37, 9, 1, "zipf"),
+    (40000, 1024, 8, 1, "uniform"), (20000, 300, 8, 1, "zipf"), (9000, 3, 2, 1, "uniform"),   # one CTA per SM; odd E
 ]
 
 

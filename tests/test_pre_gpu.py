@@ -99,9 +99,10 @@ def test_route_topk_matches_torch(T, E, k, dtype, renorm):
     from prime_flash_moe_b200 import capi
     g = torch.Generator().manual_seed(T * 7 + E)
     if dtype == torch.bfloat16:
-        # distinct bf16 values per row so that the selection is unique: a random permutation of a grid
-        base = (torch.arange(E, dtype=torch.float32) - E / 2) / 16.0
-        logits = torch.stack([base[torch.randperm(E, generator=g)] for _ in range(T)]).to(dtype)
+        # distinct bf16 values per row so that the selection is unique: E consecutive bf16 bit patterns
+        # (values from 2^-7 upwards), randomly permuted per row
+        base = (0x3C00 + torch.arange(E, dtype=torch.int32)).to(torch.int16).view(torch.bfloat16)
+        logits = torch.stack([base[torch.randperm(E, generator=g)] for _ in range(T)])
     else:
         logits = torch.randn(T, E, generator=g)
     ids, wts = capi.route_topk(logits.to(DEV), k, renorm)

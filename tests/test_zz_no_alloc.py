@@ -37,7 +37,7 @@ def _call(fn, ids, E, block_m=128, bpc=1):
 def test_static_scratch_matches_allocating_entry_point_twice():
     from prime_flash_moe_b200 import capi
     lib = capi.lib()
-    assert lib.pmoe_moe_align_static_capacity_bytes() == 4 << 20
+    assert lib.pmoe_moe_align_static_capacity_bytes() == 256 << 10
     # two different problems, both large enough to need scratch (n > 4096), run back to back
     problems = [(8192, 128, 8, 1, "uniform", 21), (20000, 64, 4, 2, "zipf", 22), (8192, 128, 8, 1, "uniform", 23)]
     for T, E, k, bpc, dist, seed in problems:
@@ -71,7 +71,7 @@ def test_static_scratch_matches_allocating_entry_point_twice():
 def test_static_scratch_rejects_oversized_problems():
     from prime_flash_moe_b200 import capi
     lib = capi.lib()
-    T, E, k = 40000, 1024, 8           # 1024 experts x thousands of warps: more than 4 MiB of counters
+    T, E, k = 40000, 1024, 8           # 1024 experts x one counter per thread block: more than the 256 KiB array holds
     ids = torch.randint(0, E, (T, k), dtype=torch.int32, device=DEV)
     need = lib.pmoe_moe_align_workspace_bytes(ids.numel(), E)
     assert need > lib.pmoe_moe_align_static_capacity_bytes()
