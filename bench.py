@@ -594,10 +594,20 @@ def ep_sweep_entry(name, dtype, rank, world, device, args):
     barrier_sync(world)
     ms = max_over_ranks(a.elapsed_time(b), world, device) / steps
     flops = 3.0 * T * k * K * N
-    return {"config": name, "tokens": T, "dtype": dtype, "parallelism": f"ep{world}", "ms_per_step": ms,
-            "value": world * flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "tokens_per_s": world * T / (ms * 1e-3),
-            "experts_per_rank": per, "rows_computed_by_rank0": layer.last_recv_rows, "rows_sent_by_rank0": layer.last_sent_rows,
-            "combine": layer.combine_mode, "finite": bool(torch.isfinite(out.float()).all())}
+    phases = None
+    if layer.combine_mode == "peer":
+        layer.profile = True
+        for _ in range(3):
+            out = layer(xq, ids, wts, xs)
+        phases = {k_: round(v_, 4) for k_, v_ in layer.phase_ms().items()}
+    entry = {"config": name, "tokens": T, "dtype": dtype, "parallelism": f"ep{world}", "ms_per_step": ms,
+             "value": world * flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "tokens_per_s": world * T / (ms * 1e-3),
+             "experts_per_rank": per, "rows_computed_by_rank0": layer.last_recv_rows,
+             "rows_sent_by_rank0": layer.last_sent_rows, "combine": layer.combine_mode, "phase_ms_rank0": phases,
+             "finite": bool(torch.isfinite(out.float()).all())}
+    if layer.exchange is not None:
+        layer.exchange.close()
+    return entry
 
 
 def run_sweep(impl, device, peaks, stages, ref_pkg=None):
@@ -909,11 +919,35 @@ def run_gpu_arm(args, impl):
         step(xin, ids, wts, out)
         torch.cuda.synchronize()
         ep_rows.append(layer.last_recv_rows)
+        ep_phases = None
+        if layer.combine_mode == "peer":      # phase times of five more steps (CUDA events on this rank's stream)
+            layer.profile = True
+            for _ in range(5):
+                step(xin, ids, wts, out)
+            ep_phases = {k_: round(v_, 4) for k_, v_ in layer.phase_ms().items()}
+            layer.profile = False
         # plan (3) + moe_align (1 or 2) + row gather, gate/up, down (3) + combine (1) (+ publish, push, 2 signals,
         # prepare, return: 6 in peer mode)
         launches_per_step = 3 + (2 if ep_rows[-1] * k > 4096 else 1) + 3 + 1 + (6 if layer.combine_mode == "peer" else 0)
         a_, b_ = out[:np_].float(), par_ref.float()
         ep_parity = max_over_ranks(float((a_ - b_).abs().max() / b_.abs().max().clamp_min(1e-30)), world, device)
+    ep_info = None
+    if ep_mode:
+        ep_info = {"rows_computed_by_rank0_last_step": ep_rows[-1] if ep_rows else None,
+                   "rows_sent_by_rank0_last_step": layer.last_sent_rows, "routes_per_rank": T * k,
+                   "tokens_per_rank": T,
+                   "parity": ep_parity,
+                   "parity_what": "max over ranks of max|ep_out - single_gpu_out| / max|single_gpu_out| on each "
+                                  "rank's first 64 tokens (single-GPU operator on the full weights)",
+                   "combine": layer.combine_mode, "phase_ms_rank0": ep_phases,
+                   "collective": ("none on the data path: rows, slot tables, counts and partial sums are stored "
+                                  "into the peers' buffers over NVLink by this library's kernels"
+                                  if layer.combine_mode == "peer" else
+                                  "NCCL all-to-all (dispatch + combine)") + ", one row per (token, rank) visit"}
+        if layer.exchange is not None:
+            layer.exchange.close()
+            layer.exchange = None
+
     sweep = None
     default_run = (args.config == "c1" and not args.tokens and args.dtype == "bf16" and args.split and world == 1)
     if default_run and not args.no_sweep:
@@ -945,17 +979,7 @@ def run_gpu_arm(args, impl):
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
         if ep_mode:
-            line["config"]["ep"] = {"rows_computed_by_rank0_last_step": ep_rows[-1] if ep_rows else None,
-                                    "rows_sent_by_rank0_last_step": layer.last_sent_rows, "routes_per_rank": T * k,
-                                    "tokens_per_rank": T,
-                                    "parity": ep_parity,
-                                    "parity_what": "max over ranks of max|ep_out - single_gpu_out| / max|single_gpu_out| on each "
-                                                   "rank's first 64 tokens (single-GPU operator on the full weights)",
-                                    "combine": layer.combine_mode,
-                                    "collective": ("none on the data path: rows, slot tables, counts and partial sums are stored "
-                                                   "into the peers' buffers over NVLink by this library's kernels"
-                                                   if layer.combine_mode == "peer" else
-                                                   "NCCL all-to-all (dispatch + combine)") + ", one row per (token, rank) visit"}
+            line["config"]["ep"] = ep_info
         if impl == "reference":
             line["impl"] = "reference"
             line["gpu_launches"] = None

@@ -111,6 +111,18 @@ int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2, void *out,
                         int K, int N, int num_experts, int sorted_num, int block_m, int block_n, int warp_n,
                         int stages, int bpc, int cpc, int split, pmoe_stream_t stream);
 size_t pmoe_fused_moe_bf16_workspace_bytes(int M, int K, int N, int sorted_num, int split);
+/* `_ex`: the `_ws` call with two optional device-side extras (no counterpart in the reference; NULL = off):
+ *   live_rows  int32[1]: only the first *live_rows rows of x / out are in use (a buffer sized for the worst case
+ *              of an expert-parallel step): the library zeroes only those rows of `out`;
+ *   out_rows   uint64[M] (bf16, split only): row i of the output lives at address out_rows[i], which may be another
+ *              GPU's memory mapped into this process; results are ADDED there with plain vector reductions and
+ *              nothing is zeroed by the library (`out` itself is then unused but must still be a valid pointer). */
+int pmoe_fused_moe_bf16_ex(const void *x, const void *w, const void *w2, void *out, const int32_t *sorted_token_ids,
+                           const int32_t *expert_ids, const int32_t *num_tokens_post_padded,
+                           const float *topk_weights, int top_k, int M, int K, int N, int num_experts, int sorted_num,
+                           int block_m, int block_n, int warp_n, int stages, int bpc, int cpc, int split,
+                           void *workspace, size_t workspace_bytes, const int32_t *live_rows,
+                           const unsigned long long *out_rows, pmoe_stream_t stream);
 int pmoe_fused_moe_bf16_ws(const void *x, const void *w, const void *w2, void *out,
                            const int32_t *sorted_token_ids, const int32_t *expert_ids,
                            const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
@@ -138,6 +150,12 @@ int pmoe_fused_moe_mxfp8(const void *x, const void *x_scales, const void *w, con
                          int sorted_num, int block_m, int block_n, int warp_n, int stages, int bpc, int split,
                          pmoe_stream_t stream);
 size_t pmoe_fused_moe_mxfp8_workspace_bytes(int M, int K, int N, int sorted_num, int split);
+int pmoe_fused_moe_mxfp8_ex(const void *x, const void *x_scales, const void *w, const void *w_scales, const void *w2,
+                            const void *w2_scales, void *out, const int32_t *sorted_token_ids,
+                            const int32_t *expert_ids, const int32_t *num_tokens_post_padded,
+                            const float *topk_weights, int top_k, int M, int K, int N, int num_experts, int sorted_num,
+                            int block_m, int block_n, int warp_n, int stages, int bpc, int split, void *workspace,
+                            size_t workspace_bytes, const int32_t *live_rows /* as for bf16 */, pmoe_stream_t stream);
 int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, const void *w_scales,
                             const void *w2, const void *w2_scales, void *out,
                             const int32_t *sorted_token_ids, const int32_t *expert_ids,
@@ -233,6 +251,13 @@ int pmoe_ep_recv_prepare(const void *local_buf, size_t meta_off, int top_k, int 
                          pmoe_stream_t stream);
 int pmoe_ep_push_back(const void *y, int K, void *const *peer_bufs, size_t y_off, int row_cap, int ret_cap, int rank,
                       int world, int epoch, pmoe_stream_t stream);
+/* Direct return: out_rows[i] = address of received row i's slot in the return area of the rank it came from (0
+ * beyond the rows that arrived). Passed to pmoe_fused_moe_bf16_ex, the down kernels add their results straight
+ * into the source ranks' return areas (vector reductions over NVLink, overlapped with the GEMM) and
+ * pmoe_ep_push_back is called with y == NULL (it then only signals). The owner of a return area zeroes it
+ * (cudaMemsetAsync) before its pmoe_ep_publish_counts of the step. Call after pmoe_ep_recv_prepare. */
+int pmoe_ep_return_table(void *const *peer_bufs, size_t y_off, int K, int row_cap, int ret_cap, int rank, int world,
+                         unsigned long long *out_rows, pmoe_stream_t stream);
 int pmoe_ep_combine_peer(const void *local_buf, size_t y_off, const int32_t *slot_of, void *out, int T, int world,
                          int K, int epoch, pmoe_stream_t stream);
 

@@ -6,7 +6,10 @@
   ``oracle/ref_shim.cu``. Only built when the reference checkout is present; the output directory is
   git-ignored and travels to a GPU machine as a prebuilt file.
 
-    python oracle/build_ref.py [/path/to/prime-flash-moe]
+    python oracle/build_ref.py /path/to/prime-flash-moe      (or PMOE_REFERENCE_ROOT=/path/to/prime-flash-moe)
+
+Without a path (argument or environment variable) only the C restatement is built and a prebuilt
+``oracle/_ref`` library, if present, is used as it is.
 """
 from __future__ import annotations
 
@@ -19,7 +22,14 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 REF_OUT = HERE / "_ref" / "libprime_moe_ref.so"
 C_OUT = HERE / "_build" / "liboracle_c.so"
-DEFAULT_REF = Path(os.environ.get("PMOE_REFERENCE_ROOT", "/root/reference"))
+def _default_ref():
+    """The reference checkout named by PMOE_REFERENCE_ROOT, else a checkout called ``reference`` beside this
+    repository if there is one, else None (a prebuilt library is then used as it is)."""
+    env = os.environ.get("PMOE_REFERENCE_ROOT")
+    if env:
+        return Path(env)
+    beside = HERE.parent.parent / "reference"
+    return beside if (beside / "prime_moe" / "csrc" / "kernels").exists() else None
 
 
 def _run(cmd):
@@ -40,8 +50,11 @@ def build_c_oracle() -> Path:
     return C_OUT
 
 
-def build_reference(ref_root: Path = DEFAULT_REF):
-    """Returns the library path, or None when the reference checkout is not available."""
+def build_reference(ref_root=None):
+    """Returns the library path, or None when neither the reference checkout nor a prebuilt library is available."""
+    ref_root = Path(ref_root) if ref_root else _default_ref()
+    if ref_root is None:
+        return REF_OUT if REF_OUT.exists() else None
     kdir = ref_root / "prime_moe" / "csrc" / "kernels"
     srcs = [kdir / "fused_moe_bf16_kernel.cu", kdir / "fused_moe_mxfp8_kernel.cu"]
     if not all(s.exists() for s in srcs):
@@ -57,4 +70,4 @@ def build_reference(ref_root: Path = DEFAULT_REF):
 
 if __name__ == "__main__":
     print(build_c_oracle())
-    print(build_reference(Path(sys.argv[1]) if len(sys.argv) > 1 else DEFAULT_REF))
+    print(build_reference(sys.argv[1] if len(sys.argv) > 1 else None))

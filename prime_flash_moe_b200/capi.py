@@ -27,6 +27,9 @@ SIGNATURES = {
     "pmoe_fused_moe_bf16": (_i, [_vp] * 8 + [_i] * 13 + [_vp]),
     "pmoe_fused_moe_bf16_workspace_bytes": (_sz, [_i] * 5),
     "pmoe_fused_moe_bf16_ws": (_i, [_vp] * 8 + [_i] * 13 + [_vp, _sz, _vp]),
+    "pmoe_fused_moe_bf16_ex": (_i, [_vp] * 8 + [_i] * 13 + [_vp, _sz, _vp, _vp, _vp]),
+    "pmoe_fused_moe_mxfp8_ex": (_i, [_vp] * 11 + [_i] * 12 + [_vp, _sz, _vp, _vp]),
+    "pmoe_ep_return_table": (_i, [_vp, _sz, _i, _i, _i, _i, _i, _vp, _vp]),
     "pmoe_fused_moe_mxfp8": (_i, [_vp] * 11 + [_i] * 12 + [_vp]),
     "pmoe_fused_moe_mxfp8_workspace_bytes": (_sz, [_i] * 5),
     "pmoe_fused_moe_mxfp8_ws": (_i, [_vp] * 11 + [_i] * 12 + [_vp, _sz, _vp]),
@@ -99,15 +102,28 @@ def moe_align(topk_ids: torch.Tensor, num_experts: int, block_m: int = 128, bpc:
     return sorted_ids, expert_ids, npp
 
 
+def _workspace(nbytes, device):
+    ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+    off = (-ws.data_ptr()) % 1024
+    return ws[off:off + nbytes]
+
+
 def fused_moe_bf16(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k,
-                   block_m=128, block_n=64, warp_n=4, stages=4, bpc=1, cpc=1, split=True, workspace=None):
+                   block_m=128, block_n=64, warp_n=4, stages=4, bpc=1, cpc=1, split=True, workspace=None,
+                   live_rows=None, out_rows=None):
     M, K = x.shape
     E, N, _ = w.shape
     with torch.cuda.device(x.device):
         common = (_p(x), _p(w), _p(w2), _p(out), _p(sorted_token_ids), _p(expert_ids), _p(num_tokens_post_padded),
                   _p(topk_weights), top_k, M, K, N, E, sorted_token_ids.numel(), block_m, block_n, warp_n, stages,
                   bpc, cpc, int(split))
-        if workspace is None:
+        if live_rows is not None or out_rows is not None:
+            if workspace is None:
+                workspace = _workspace(lib().pmoe_fused_moe_bf16_workspace_bytes(M, K, N, sorted_token_ids.numel(),
+                                                                                 int(split)), x.device)
+            _check(lib().pmoe_fused_moe_bf16_ex(*common, _p(workspace), workspace.numel() * workspace.element_size(),
+                                                _p(live_rows), _p(out_rows), _stream()))
+        elif workspace is None:
             _check(lib().pmoe_fused_moe_bf16(*common, _stream()))
         else:
             _check(lib().pmoe_fused_moe_bf16_ws(*common, _p(workspace), workspace.numel() * workspace.element_size(),
@@ -117,14 +133,20 @@ def fused_moe_bf16(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padde
 
 def fused_moe_mxfp8(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, expert_ids,
                     num_tokens_post_padded, topk_weights, out, top_k, block_m=128, block_n=64, warp_n=4,
-                    stages=4, bpc=1, split=True, workspace=None):
+                    stages=4, bpc=1, split=True, workspace=None, live_rows=None):
     M, K = x.shape
     E, N, _ = w.shape
     with torch.cuda.device(x.device):
         common = (_p(x), _p(x_scales), _p(w), _p(w_scales), _p(w2), _p(w2_scales), _p(out), _p(sorted_token_ids),
                   _p(expert_ids), _p(num_tokens_post_padded), _p(topk_weights), top_k, M, K, N, E,
                   sorted_token_ids.numel(), block_m, block_n, warp_n, stages, bpc, int(split))
-        if workspace is None:
+        if live_rows is not None:
+            if workspace is None:
+                workspace = _workspace(lib().pmoe_fused_moe_mxfp8_workspace_bytes(M, K, N, sorted_token_ids.numel(),
+                                                                                  int(split)), x.device)
+            _check(lib().pmoe_fused_moe_mxfp8_ex(*common, _p(workspace), workspace.numel() * workspace.element_size(),
+                                                 _p(live_rows), _stream()))
+        elif workspace is None:
             _check(lib().pmoe_fused_moe_mxfp8(*common, _stream()))
         else:
             _check(lib().pmoe_fused_moe_mxfp8_ws(*common, _p(workspace),

@@ -48,6 +48,11 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 }
 }  // namespace
 
+CallExtras &call_extras() {
+    thread_local CallExtras extras;
+    return extras;
+}
+
 int set_error(int code, const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);

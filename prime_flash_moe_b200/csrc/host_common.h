@@ -36,6 +36,18 @@ int make_tmap_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t elem_byte
 int scratch_alloc(void **ptr, size_t bytes, cudaStream_t stream);
 int scratch_free(void *ptr, cudaStream_t stream);
 
+// Optional extras of one call, set by the `_ex` entry points around the regular launch path (thread-local):
+//   live_rows  device int32[1]: only rows below *live_rows of `out` (and of x) are in use - the launchers then zero
+//              only those rows of `out`
+//   out_rows   device uint64[M]: row i of `out` lives at this address (possibly in another GPU's memory mapped
+//              into this process); the down kernels add their results there with plain vector reductions and the
+//              library does not zero anything (bf16 split pipeline only)
+struct CallExtras {
+    const int32_t *live_rows = nullptr;
+    const unsigned long long *out_rows = nullptr;
+};
+CallExtras &call_extras();
+
 // number of SMs of the current device (cached per device)
 int sm_count();
 

@@ -41,6 +41,7 @@
 
 #include "host_common.h"
 #include "ptx.cuh"
+#include "tile_sched.cuh"
 
 namespace pmoe {
 
@@ -55,28 +56,12 @@ constexpr uint32_t B_BYTES = 256 * BK * 2;       // 32 KB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t ACT_TILE_BYTES = 128 * 128 * 2;  // 128 rows x 128 bf16: two swizzled 16 KB halves
 constexpr int MAX_STAGES = 4;
-constexpr int GROUP_M = 8;                       // row blocks that run side by side on one weight slice
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int GATHER_THREADS = 128;             // optional LSU gather warps at the end of the block
 constexpr int MAX_THREADS = 64 + 8 * 32 + GATHER_THREADS;
 constexpr uint32_t BAR_BYTES = 256;
 constexpr uint32_t RED_ROW_BYTES = 256 + 16;     // down epilogue staging: 128 bf16 per row, padded against bank conflicts
 constexpr uint32_t RED_STAGE_BYTES = 128 * RED_ROW_BYTES;
-
-struct Coord {
-    int m_blk, n_tile;
-};
-__device__ __forceinline__ Coord tile_coord(int t, int m_blocks, int n_tiles) {
-    const int per_group = GROUP_M * n_tiles;
-    const int g = t / per_group;
-    const int first = g * GROUP_M;
-    const int gsz = min(GROUP_M, m_blocks - first);
-    const int local = t - g * per_group;
-    Coord c;
-    c.m_blk = first + local % gsz;
-    c.n_tile = local / gsz;
-    return c;
-}
 
 struct Args {
     const int32_t *sorted_ids;
@@ -102,6 +87,8 @@ struct Args {
     const int32_t *pair_list;
     const int32_t *tail_list;
     const int32_t *list_counts;
+    const int32_t *live_rows;              // optional: rows of `out` in use (only those are zeroed)
+    const unsigned long long *out_rows;    // optional: address of every row of `out` (down kernels, plain reductions)
     int short_boxes; // one-CTA split kernels: row blocks with <= SHORT_ROWS routed rows move only those rows of
                      // the A operand and of the activation tile (the rest of a 128-row block is padding)
 };
@@ -112,6 +99,16 @@ constexpr uint32_t SHORT_A_BYTES = SHORT_ROWS * 128;
 // routed rows come first in a block, so the block is short when row SHORT_ROWS is already padding
 __device__ __forceinline__ bool block_is_short(const Args &a, int blk, int what = 1) {
     return (a.short_boxes & what) && a.sorted_ids[blk * BM + SHORT_ROWS] < 0;
+}
+
+// rows of `out` the library has to zero
+__device__ __forceinline__ int live_out_rows(const Args &a) {
+    return a.live_rows ? max(0, min(a.M, *a.live_rows)) : a.M;
+}
+// destination of output row `tok`, columns from col0
+__device__ __forceinline__ __nv_bfloat16 *out_row_ptr(const Args &a, int tok, int col0) {
+    if (a.out_rows) return reinterpret_cast<__nv_bfloat16 *>(a.out_rows[tok]) + col0;
+    return a.out + static_cast<size_t>(tok) * a.K + col0;
 }
 
 __device__ __forceinline__ int num_row_blocks(const Args &a) {
@@ -527,7 +524,7 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const int cg = ew / 4;
         if (a.zero_out) {
             int4 *o4 = reinterpret_cast<int4 *>(a.out);
-            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const long long n4 = static_cast<long long>(live_out_rows(a)) * a.K / 8;
             const int4 z = make_int4(0, 0, 0, 0);
             for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
                  i += static_cast<long long>(gridDim.x) * epi_threads)
@@ -836,7 +833,7 @@ moe_up_dual_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         const int cg = ew / 4;
         if (a.zero_out) {
             int4 *o4 = reinterpret_cast<int4 *>(a.out);
-            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const long long n4 = static_cast<long long>(live_out_rows(a)) * a.K / 8;
             const int4 z = make_int4(0, 0, 0, 0);
             for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
                  i += static_cast<long long>(gridDim.x) * epi_threads)
@@ -1000,7 +997,7 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
             const bool valid = pair >= 0 && tok < a.M;
             const float wgt = valid ? a.topk_weights[pair] : 0.f;
             const int col0 = c.n_tile * 256;
-            __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + col0;
+            __nv_bfloat16 *dst = valid ? out_row_ptr(a, tok, col0) : a.out;
             const int cols = min(256, a.K - col0);
             if (a.bulk_reduce && ew >= 4) break;   // warps beyond the first four idle in the bulk epilogue
             if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
@@ -1391,7 +1388,7 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int cg = ew / 4;
         if (kUp && a.zero_out) {
             int4 *o4 = reinterpret_cast<int4 *>(a.out);
-            const long long n4 = static_cast<long long>(a.M) * a.K / 8;
+            const long long n4 = static_cast<long long>(live_out_rows(a)) * a.K / 8;
             const int4 z = make_int4(0, 0, 0, 0);
             for (long long i = static_cast<long long>(blockIdx.x) * epi_threads + et; i < n4;
                  i += static_cast<long long>(gridDim.x) * epi_threads)
@@ -1429,7 +1426,7 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 const bool valid = pair >= 0 && tok < a.M;
                 const float wgt = valid ? a.topk_weights[pair] : 0.f;
                 const int col0 = c.n_tile * 256;
-                __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + col0;
+                __nv_bfloat16 *dst = valid ? out_row_ptr(a, tok, col0) : a.out;
                 const int cols = min(256, a.K - col0);
                 if (a.bulk_reduce && ew >= 4) break;
                 if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
@@ -1553,7 +1550,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
     const int H = p.N / 2;
     const int max_blocks = p.sorted_num / BM;
     if (max_blocks == 0) {
-        if (p.split)
+        if (p.split && !call_extras().out_rows)
             PMOE_CUDA_OK(cudaMemsetAsync(p.out, 0, static_cast<size_t>(p.M) * p.K * 2, stream));
         return PMOE_OK;
     }
@@ -1572,8 +1569,13 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
     a.stages = std::min(p.stages, MAX_STAGES);
     a.epi_warps = p.warp_n;
     a.l2_ahead = l2_prefetch_distance();
+    const CallExtras extras = call_extras();
+    a.live_rows = extras.live_rows;
+    a.out_rows = extras.out_rows;
+    PMOE_REQUIRE(!extras.out_rows || p.split, PMOE_ERR_UNSUPPORTED, "fused_moe_bf16: out_rows requires split=True");
     const int bulk = down_bulk_reduce_mode();   // -1 auto: on when the down GEMM's K extent (H) is short
-    const bool bulk_reduce = bulk < 0 ? (H <= 1024) : bulk != 0;
+    // rows addressed through out_rows may live in a peer's memory: plain vector reductions only there
+    const bool bulk_reduce = extras.out_rows ? false : (bulk < 0 ? (H <= 1024) : bulk != 0);
     const int threads = 64 + 32 * a.epi_warps;
     const int sms = sm_count();
 
@@ -1733,7 +1735,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
         };
         if (phases & 2) {
             Args up = pa;
-            up.zero_out = 1;
+            up.zero_out = extras.out_rows ? 0 : 1;
             up.use_pdl = (pdl_enabled() && (phases & 1)) ? 1 : 0;
             if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128),
                                      ACT_TILE_BYTES, up.use_pdl ? 2 : 1))
@@ -1776,7 +1778,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
     const bool dual = a_mode != 0 && (dual_env < 0 ? static_cast<long long>(p.M) * p.top_k >= 1024ll * p.E : dual_env != 0);
     if ((phases & 2) && dual) {
         Args up = a;
-        up.zero_out = 1;
+        up.zero_out = extras.out_rows ? 0 : 1;
         up.pregathered = a_mode;
         up.x = static_cast<const __nv_bfloat16 *>(p.x);
         up.stages = std::min(a.stages, DUAL_MAX_STAGES);
@@ -1799,7 +1801,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
         PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_dual_bf16_kernel, map_x, map_w1, map_act, up));
     } else if (phases & 2) {
         Args up = a;
-        up.zero_out = 1;
+        up.zero_out = extras.out_rows ? 0 : 1;
         up.pregathered = a_mode;
         up.x = static_cast<const __nv_bfloat16 *>(p.x);
         const int threads = 64 + 32 * a.epi_warps + (a_mode == 2 ? GATHER_THREADS : 0);
@@ -1916,5 +1918,22 @@ extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2,
     const int rc = run(p, raw ? ws : nullptr, need, stream);
     if (raw)
         if (int rc2 = scratch_free(raw, stream)) return rc2;
+    return rc;
+}
+
+extern "C" int pmoe_fused_moe_bf16_ex(const void *x, const void *w, const void *w2, void *out,
+                                      const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                      const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
+                                      int M, int K, int N, int num_experts, int sorted_num, int block_m, int block_n,
+                                      int warp_n, int stages, int bpc, int cpc, int split, void *workspace,
+                                      size_t workspace_bytes, const int32_t *live_rows,
+                                      const unsigned long long *out_rows, pmoe_stream_t stream) {
+    pmoe::CallExtras &extras = pmoe::call_extras();
+    extras.live_rows = live_rows;
+    extras.out_rows = out_rows;
+    const int rc = pmoe_fused_moe_bf16_ws(x, w, w2, out, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                          topk_weights, top_k, M, K, N, num_experts, sorted_num, block_m, block_n, warp_n,
+                                          stages, bpc, cpc, split, workspace, workspace_bytes, stream);
+    extras = pmoe::CallExtras{};
     return rc;
 }

@@ -409,6 +409,42 @@ ep_push_back_kernel(const __nv_bfloat16 *__restrict__ y, int K, void *const *__r
     }
 }
 
+// out_rows[i] = address, in the memory of the rank row i came from, of that visit's row of the return area (0 for
+// rows that did not arrive): with this table the down kernels add their results straight into the source ranks'
+// buffers and no separate return pass is needed. Runs after ep_recv_prepare (the counts are complete then).
+__global__ void __launch_bounds__(256)
+ep_return_table_kernel(void *const *__restrict__ peers, size_t y_off, int K, int me, int world, int row_cap, int ret_cap,
+                       unsigned long long *__restrict__ out_rows) {
+    __shared__ int s_recv_base[kMaxRanks + 1];
+    __shared__ int s_ret_base[kMaxRanks];
+    const Header *h = static_cast<const Header *>(peers[me]);
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int s = 0; s < world; ++s) {
+            s_recv_base[s] = run;
+            run += ld_count(&h->M[s][me]);
+            int before = 0;
+            for (int g = 0; g < me; ++g) before += ld_count(&h->M[s][g]);
+            s_ret_base[s] = before;
+        }
+        s_recv_base[world] = run;
+    }
+    __syncthreads();
+    const int R = min(s_recv_base[world], row_cap);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < row_cap; i += gridDim.x * blockDim.x) {
+        unsigned long long addr = 0;
+        if (i < R) {
+            int s = 0;
+            while (s + 1 < world && s_recv_base[s + 1] <= i) ++s;
+            const long long v = static_cast<long long>(s_ret_base[s]) + (i - s_recv_base[s]);
+            if (v < ret_cap)
+                addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t *>(peers[s]) + y_off) +
+                       static_cast<unsigned long long>(v) * K * 2ull;
+        }
+        out_rows[i] = addr;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 ep_combine_peer_kernel(const void *local_buf, size_t y_off, const int32_t *__restrict__ slot_of,
                        __nv_bfloat16 *__restrict__ out, int T, int world, int K, int epoch) {
@@ -552,14 +588,16 @@ extern "C" int pmoe_ep_recv_prepare(const void *local_buf, size_t meta_off, int 
 extern "C" int pmoe_ep_push_back(const void *y, int K, void *const *peer_bufs, size_t y_off, int row_cap, int ret_cap,
                                  int rank, int world, int epoch, pmoe_stream_t stream) {
     using namespace pmoe;
-    PMOE_REQUIRE(y && peer_bufs, PMOE_ERR_BAD_ARG, "ep_push_back: null pointer");
+    PMOE_REQUIRE(peer_bufs, PMOE_ERR_BAD_ARG, "ep_push_back: null pointer");
     if (int rc = check_world(rank, world, "ep_push_back")) return rc;
     PMOE_REQUIRE(K > 0 && K % 8 == 0 && ((reinterpret_cast<uintptr_t>(y) | y_off) & 15) == 0, PMOE_ERR_BAD_ARG,
                  "ep_push_back: K must be a multiple of 8, y and the return area 16-byte aligned");
-    const int grid = std::max(1, std::min(8 * sm_count(), (row_cap + 7) / 8));
-    ep_push_back_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(y), K, peer_bufs, y_off, rank, world,
-                                                  row_cap, ret_cap);
-    PMOE_CUDA_OK(cudaGetLastError());
+    if (y) {   // y == NULL: the partial sums are already in the peers' return areas (pmoe_ep_return_table): signal only
+        const int grid = std::max(1, std::min(8 * sm_count(), (row_cap + 7) / 8));
+        ep_push_back_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(y), K, peer_bufs, y_off, rank,
+                                                      world, row_cap, ret_cap);
+        PMOE_CUDA_OK(cudaGetLastError());
+    }
     ep_signal_kernel<<<1, 32, 0, stream>>>(peer_bufs, rank, world, epoch, 2);
     PMOE_CUDA_OK(cudaGetLastError());
     return PMOE_OK;
@@ -575,6 +613,19 @@ extern "C" int pmoe_ep_combine_peer(const void *local_buf, size_t y_off, const i
                  "ep_combine_peer: out and the return area must be 16-byte aligned");
     ep_combine_peer_kernel<<<std::max(1, std::min(T, 8 * sm_count())), 256, 0, stream>>>(
         local_buf, y_off, slot_of, static_cast<__nv_bfloat16 *>(out), T, world, K, epoch);
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+extern "C" int pmoe_ep_return_table(void *const *peer_bufs, size_t y_off, int K, int row_cap, int ret_cap, int rank,
+                                    int world, unsigned long long *out_rows, pmoe_stream_t stream) {
+    using namespace pmoe;
+    PMOE_REQUIRE(peer_bufs && out_rows, PMOE_ERR_BAD_ARG, "ep_return_table: null pointer");
+    if (int rc = check_world(rank, world, "ep_return_table")) return rc;
+    PMOE_REQUIRE(K > 0 && K % 8 == 0 && (y_off & 15) == 0 && row_cap > 0, PMOE_ERR_BAD_ARG,
+                 "ep_return_table: K must be a multiple of 8 and the return area 16-byte aligned");
+    ep_return_table_kernel<<<std::max(1, std::min(2 * sm_count(), (row_cap + 255) / 256)), 256, 0, stream>>>(
+        peer_bufs, y_off, K, rank, world, row_cap, ret_cap, out_rows);
     PMOE_CUDA_OK(cudaGetLastError());
     return PMOE_OK;
 }

@@ -108,26 +108,44 @@ class LocalExperts:
         self.bpc = bpc if bpc else (2 if (w1_scales is None and split and w1.shape[1] >= 8192) else 1)
 
     def __call__(self, rows: torch.Tensor, local_ids: torch.Tensor, weights: torch.Tensor,
-                 row_scales: Optional[torch.Tensor] = None):
+                 row_scales: Optional[torch.Tensor] = None, live_rows: Optional[torch.Tensor] = None,
+                 out_rows: Optional[torch.Tensor] = None):
+        """``live_rows`` (device int32[1]): only that many leading rows are in use, the rest of the worst-case sized
+        buffers is neither routed nor zeroed. ``out_rows`` (device int64[R], bf16 only): the address of every
+        output row - the results are added there (possibly into a peer's memory) and ``None`` is returned."""
         if not rows.is_cuda:
             raise RuntimeError("LocalExperts needs CUDA tensors: this package has no CPU kernels")
         ops = torch.ops.prime_moe
         R, K = rows.shape
         top_k = local_ids.shape[1]
-        out = torch.empty(R, K, dtype=torch.bfloat16, device=rows.device)   # split=True zeroes it itself
+        if out_rows is not None:
+            if not hasattr(self, "_dummy_out") or self._dummy_out.device != rows.device:
+                self._dummy_out = torch.zeros(K, dtype=torch.bfloat16, device=rows.device)
+            out = self._dummy_out                 # never written: every row goes to its address in out_rows
+        else:
+            out = torch.empty(R, K, dtype=torch.bfloat16, device=rows.device)   # split=True zeroes it itself
         if R == 0:
             return out
-        if not self.split:
+        if not self.split and out_rows is None:
             out.zero_()
         s, e, n = ops.moe_align(local_ids.contiguous(), self.num_local, 128, self.bpc)
         w = weights.reshape(-1).contiguous()
-        if self.w1_scales is None:
+        if live_rows is not None or out_rows is not None:
+            from . import capi             # the `_ex` entry points of the C ABI carry the two extras
+            if self.w1_scales is None:
+                capi.fused_moe_bf16(rows, self.w1, self.w2, s, e, n, w, out, top_k, 128, 64, 4, self.stages, self.bpc, 1,
+                                    self.split, live_rows=live_rows, out_rows=out_rows)
+            else:
+                assert out_rows is None, "direct output rows are a bf16 option"
+                capi.fused_moe_mxfp8(rows, row_scales, self.w1, self.w1_scales, self.w2, self.w2_scales, s, e, n, w, out,
+                                     top_k, 128, 64, 4, self.stages, self.bpc, self.split, live_rows=live_rows)
+        elif self.w1_scales is None:
             ops.fused_moe_bf16(rows, self.w1, self.w2, s, e, n, w, out, top_k, 128, 64, 4, self.stages, self.bpc, 1,
                                self.split)
         else:
             ops.fused_moe_mxfp8(rows, row_scales, self.w1, self.w1_scales, self.w2, self.w2_scales, s, e, n, w, out,
                                 top_k, 128, 64, 4, self.stages, self.bpc, self.split)
-        return out
+        return None if out_rows is not None else out
 
 
 class _DeviceBytes:
@@ -230,6 +248,12 @@ class ExpertParallelMoE:
             combine = "peer" if (self.world > 1 and peer_exchange_possible(group)) else "nccl"
         self.combine_mode = combine if self.world > 1 else "nccl"
         self.exchange: Optional[PeerExchange] = None
+        self.direct_return = None   # peer mode: True / False forces the epilogue-direct return, None = by layer shape
+        env = __import__("os").environ.get("PMOE_EP_DIRECT")
+        if env is not None:
+            self.direct_return = env not in ("0", "")
+        self.profile = False        # record CUDA events around the phases of a peer-mode step (phase_ms() reads them)
+        self._events = []
 
     # rows this rank computed / sent in the last call; in peer mode the counts stay on the device until asked for
     @property
@@ -240,7 +264,27 @@ class ExpertParallelMoE:
     def last_sent_rows(self) -> int:
         return int(self._sent_rows.sum().item()) if torch.is_tensor(self._sent_rows) else self._sent_rows
 
+    def _mark(self, name):
+        if self.profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._events.append((name, ev))
+
+    def phase_ms(self):
+        """Mean milliseconds per phase over the profiled steps (synchronises); clears the record."""
+        torch.cuda.synchronize()
+        sums, n = {}, {}
+        prev = None
+        for name, ev in self._events:
+            if name != "start" and prev is not None:
+                sums[name] = sums.get(name, 0.0) + prev.elapsed_time(ev)
+                n[name] = n.get(name, 0) + 1
+            prev = ev
+        self._events = []
+        return {k: sums[k] / n[k] for k in sums}
+
     def _forward_peer(self, x, topk_ids, topk_weights, x_scales=None):
+        self._mark("start")
         from . import capi
         T, K = x.shape
         top_k = topk_ids.shape[1]
@@ -254,28 +298,51 @@ class ExpertParallelMoE:
             self._ids = torch.empty(ex.row_cap, top_k, dtype=torch.int32, device=x.device)
             self._wts = torch.empty(ex.row_cap, top_k, dtype=torch.float32, device=x.device)
             self._num_rows = torch.zeros(1, dtype=torch.int32, device=x.device)
+            self._out_rows = torch.zeros(ex.row_cap, dtype=torch.int64, device=x.device)
         lib, G, me = ex.lib, self.world, ex.rank
+        # wide bf16 layers return their partial sums from the down kernel's epilogue straight into the source ranks'
+        # buffers (a long k-loop per tile keeps the NVLink rate low); narrow ones copy finished rows afterwards
+        direct = self.direct_return
+        if direct is None:
+            direct = x_scales is None and isinstance(self.experts, LocalExperts) and self.experts.split and \
+                self.experts.w1.shape[1] >= 8192
         plan = make_dispatch_plan(topk_ids, topk_weights, self.num_experts, G)
         ex.epoch += 1
         e, tab, st = ex.epoch, ex.table.data_ptr(), torch.cuda.current_stream().cuda_stream
         x = x.contiguous()
         aux = None if x_scales is None else x_scales.contiguous()
+        mark = self._mark
         with torch.cuda.device(x.device):
+            if direct:
+                ex.buf[ex.y_off:ex.y_off + ex.ret_cap * K * 2].zero_()     # peers ADD into it during this step
+            mark("plan")
             capi._check(lib.pmoe_ep_publish_counts(plan.counts.data_ptr(), tab, me, G, e, st))
             capi._check(lib.pmoe_ep_push_rows(x.data_ptr(), row_bytes, 0 if aux is None else aux.data_ptr(), aux_bytes,
                                               plan.visit_token.data_ptr(), plan.visit_meta.data_ptr(), top_k, T, tab,
                                               ex.rows_off, ex.aux_off, ex.meta_off, ex.row_cap, me, G, e, st))
+            mark("dispatch")
             capi._check(lib.pmoe_ep_recv_prepare(ex.local_ptr, ex.meta_off, top_k, ex.row_cap, self._ids.data_ptr(),
                                                  self._wts.data_ptr(), self._num_rows.data_ptr(), me, G, e, st))
+            mark("wait+prepare")
             rows = ex.area(ex.rows_off, ex.row_cap, row_bytes).view(x.dtype)
+            extras = {"live_rows": self._num_rows} if isinstance(self.experts, LocalExperts) else {}
+            if direct:
+                capi._check(lib.pmoe_ep_return_table(tab, ex.y_off, K, ex.row_cap, ex.ret_cap, me, G,
+                                                     self._out_rows.data_ptr(), st))
+                extras["out_rows"] = self._out_rows
             if aux is None:
-                y = self.experts(rows, self._ids, self._wts)
+                y = self.experts(rows, self._ids, self._wts, **extras)
             else:
-                y = self.experts(rows, self._ids, self._wts, ex.area(ex.aux_off, ex.row_cap, aux_bytes).view(aux.dtype))
-            capi._check(lib.pmoe_ep_push_back(y.data_ptr(), K, tab, ex.y_off, ex.row_cap, ex.ret_cap, me, G, e, st))
+                y = self.experts(rows, self._ids, self._wts, ex.area(ex.aux_off, ex.row_cap, aux_bytes).view(aux.dtype),
+                                 **extras)
+            mark("experts")
+            capi._check(lib.pmoe_ep_push_back(0 if y is None else y.data_ptr(), K, tab, ex.y_off, ex.row_cap, ex.ret_cap,
+                                              me, G, e, st))
+            mark("return")
             out = torch.empty(T, K, dtype=torch.bfloat16, device=x.device)
             capi._check(lib.pmoe_ep_combine_peer(ex.local_ptr, ex.y_off, plan.slot_of.data_ptr(), out.data_ptr(), T, G, K,
                                                  e, st))
+            mark("wait+combine")
         self._recv_rows, self._sent_rows = self._num_rows, plan.counts
         self._keep = (plan, y, x, aux)     # alive until the next call: the kernels above may still be running
         return out

@@ -18,6 +18,7 @@ Functions executed (path inside the reference : name):
 from __future__ import annotations
 
 import ast
+import os
 import sys
 from pathlib import Path
 
@@ -131,4 +132,7 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PMOE_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/prime-flash-moe   (or set PMOE_REFERENCE_ROOT)")
+    main(root)

@@ -44,8 +44,10 @@ def _worker(rank, world, port, mx, combine, ret):
                                  requant_act=True)[lo:hi]
         else:
             experts = ep.LocalExperts(ep.shard_experts(w1, rank, world).to(dev), ep.shard_experts(w2, rank, world).to(dev))
-            layer = ep.ExpertParallelMoE(E, experts, combine=combine)
-            assert layer.combine_mode == combine
+            layer = ep.ExpertParallelMoE(E, experts, combine=combine.split("-")[0])
+            assert layer.combine_mode == combine.split("-")[0]
+            if combine.startswith("peer"):
+                layer.direct_return = combine == "peer-direct"
             layer(x[lo:hi].to(dev), ids[lo:hi].flip(0).contiguous().to(dev), wts[lo:hi].to(dev))
             out = layer(x[lo:hi].to(dev), ids[lo:hi].to(dev), wts[lo:hi].to(dev))
             ref = O.moe_ref_fp32(x, w1, w2, ids, wts)[lo:hi]
@@ -59,13 +61,16 @@ def _worker(rank, world, port, mx, combine, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("combine", ["nccl", "peer"])
+@pytest.mark.parametrize("combine", ["nccl", "peer", "peer-direct"])
 @pytest.mark.parametrize("mx", [False, True])
 def test_ep_two_gpus(mx, combine):
     """`nccl`: all-to-all dispatch / combine; `peer`: this library's kernels store rows, slot tables, counts and
-    partial sums into the other rank's buffer over NVLink (no NCCL call and no host sync inside a step)."""
+    partial sums into the other rank's buffer over NVLink (no NCCL call and no host sync inside a step);
+    `peer-direct` (bf16): the down kernel's epilogue adds its results straight into the source rank's buffer."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
+    if mx and combine == "peer-direct":
+        pytest.skip("the epilogue-direct return is a bf16 option")
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, _free_port(), mx, combine, ret), nprocs=2, join=True)
     assert len(ret) == 2
