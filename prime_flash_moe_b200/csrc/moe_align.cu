@@ -25,7 +25,8 @@ namespace {
 
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
-constexpr int kSmallN = 4096;      // up to here a single CTA does everything, no scratch
+constexpr int kSmallN = 4096;      // up to here a single CTA of 8 warps does everything, no scratch
+constexpr int kSmallN32 = 16384;   // ... and up to here a single CTA of 32 warps, when its counters fit (E <= 256)
 constexpr int kMaxExperts = 1024;
 
 __device__ __forceinline__ unsigned lanemask_lt() {
@@ -146,24 +147,25 @@ __device__ void block_offsets(const int *tot, int *offs, int *wsum, int E, int p
 // ---------------------------------------------------------------------------------------------
 // small n: one CTA, no scratch
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) moe_align_small_kernel(
+__global__ void __launch_bounds__(1024) moe_align_small_kernel(
     const int32_t *__restrict__ ids, int32_t *__restrict__ sorted, int32_t *__restrict__ expert_ids,
     int32_t *__restrict__ npp, int n, int E, int block_m, int pad_to, int max_padded, int max_blocks) {
     extern __shared__ int sm[];
-    int *cnt = sm;                       // [kWarpsPerCta][E]
-    int *tot = cnt + kWarpsPerCta * E;   // [E]
-    int *offs = tot + E;                 // [E + 1]
-    int *wsum = offs + E + 1;            // [kWarpsPerCta]
+    const int nthr = blockDim.x, nwarps = nthr >> 5;   // 8 warps, or 32 for the larger single-CTA problems
+    int *cnt = sm;                 // [nwarps][E]
+    int *tot = cnt + nwarps * E;   // [E]
+    int *offs = tot + E;           // [E + 1]
+    int *wsum = offs + E + 1;      // [nwarps]
     const int warp = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < kWarpsPerCta * E; i += kThreads) cnt[i] = 0;
+    for (int i = threadIdx.x; i < nwarps * E; i += nthr) cnt[i] = 0;
     __syncthreads();
-    const int seg = ((n + kWarpsPerCta - 1) / kWarpsPerCta + 31) & ~31;
+    const int seg = ((n + nwarps - 1) / nwarps + 31) & ~31;
     const int begin = min(warp * seg, n), end = min(begin + seg, n);
     warp_histogram(ids, begin, end, E, cnt + warp * E);
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += kThreads) {
+    for (int e = threadIdx.x; e < E; e += nthr) {
         int run = 0;
-        for (int w = 0; w < kWarpsPerCta; ++w) {
+        for (int w = 0; w < nwarps; ++w) {
             const int c = cnt[w * E + e];
             cnt[w * E + e] = run;
             run += c;
@@ -178,16 +180,16 @@ __global__ void __launch_bounds__(kThreads) moe_align_small_kernel(
         int4 *s4 = reinterpret_cast<int4 *>(sorted);
         const int n4 = max_padded >> 2;
         const int4 m1 = make_int4(-1, -1, -1, -1);
-        for (int i = threadIdx.x; i < n4; i += kThreads) s4[i] = m1;
+        for (int i = threadIdx.x; i < n4; i += nthr) s4[i] = m1;
         if (threadIdx.x < (max_padded & 3)) sorted[(n4 << 2) + threadIdx.x] = -1;
     }
-    for (int j = threadIdx.x; j < max_blocks; j += kThreads) {
+    for (int j = threadIdx.x; j < max_blocks; j += nthr) {
         const int row = j * block_m;
         expert_ids[j] = row >= total ? E - 1 : find_expert(offs, E, row);
     }
-    for (int e = threadIdx.x; e < E; e += kThreads) {
+    for (int e = threadIdx.x; e < E; e += nthr) {
         const int o = offs[e];
-        for (int w = 0; w < kWarpsPerCta; ++w) cnt[w * E + e] += o;
+        for (int w = 0; w < nwarps; ++w) cnt[w * E + e] += o;
     }
     __syncthreads();  // orders the -1 fill before the scatter stores of this CTA
     warp_scatter(ids, begin, end, E, cnt + warp * E, sorted, max_padded);
@@ -207,6 +209,9 @@ __global__ void __launch_bounds__(kThreads) moe_align_hist_kernel(
     const int32_t *__restrict__ ids, int n, int E, int seg, int *__restrict__ counts,
     int32_t *__restrict__ sorted, int max_padded) {
     extern __shared__ int sm[];
+    // the scatter kernel may start its own counting pass now; it waits for this whole grid before it reads the
+    // counts or writes sorted_token_ids
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < kWarpsPerCta * E; i += kThreads) sm[i] = 0;
     __syncthreads();
@@ -244,6 +249,7 @@ __global__ void __launch_bounds__(kThreads) moe_align_scatter_kernel(
     const int gw = blockIdx.x * kWarpsPerCta + warp;
     const int begin = min(gw * seg, n), end = min(begin + seg, n);
     warp_histogram(ids, begin, end, E, cnt + warp * E);
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the histogram kernel's counts and -1 fill are complete
     // column sums of counts[cta][e]: `parts` threads share one expert when there are fewer experts than threads
     const int ctas = gridDim.x, me = blockIdx.x;
     const int parts = max(1, kThreads / E);
@@ -290,7 +296,7 @@ constexpr int kIdsPerCtaMin = 2048;
 
 Plan make_plan(int n, int E) {
     Plan p{};
-    if (n <= kSmallN) return p;
+    if (n <= kSmallN || (n <= kSmallN32 && E <= 256)) return p;
     int ctas = (n + kIdsPerCtaMin - 1) / kIdsPerCtaMin;
     ctas = std::max(1, std::min(ctas, sm_count()));
     p.ctas = ctas;
@@ -322,8 +328,9 @@ int launch(const int32_t *topk_ids, int32_t *sorted, int32_t *expert_ids, int32_
            int block_m, int pad_to, int max_padded, int max_blocks, const Plan &p, int *ws,
            cudaStream_t stream) {
     if (p.ctas == 0) {
-        const size_t smem = (static_cast<size_t>(kWarpsPerCta) * E + 2 * E + 1 + kWarpsPerCta) * sizeof(int);
-        moe_align_small_kernel<<<1, kThreads, smem, stream>>>(topk_ids, sorted, expert_ids, npp, n, E, block_m,
+        const int warps = n > 1024 && E <= 256 ? 32 : kWarpsPerCta;
+        const size_t smem = (static_cast<size_t>(warps) * E + 2 * E + 1 + warps) * sizeof(int);   // <= 35 KB
+        moe_align_small_kernel<<<1, warps * 32, smem, stream>>>(topk_ids, sorted, expert_ids, npp, n, E, block_m,
                                                              pad_to, max_padded, max_blocks);
         PMOE_CUDA_OK(cudaGetLastError());
         return PMOE_OK;
@@ -334,9 +341,18 @@ int launch(const int32_t *topk_ids, int32_t *sorted, int32_t *expert_ids, int32_
     PMOE_CUDA_OK(cudaGetLastError());
     const size_t smem_s = (static_cast<size_t>(kWarpsPerCta) * E + 3 * static_cast<size_t>(E) + 1 + kWarpsPerCta) *
                           sizeof(int);
-    moe_align_scatter_kernel<<<p.ctas, kThreads, smem_s, stream>>>(topk_ids, n, E, p.seg, counts, block_m, pad_to,
-                                                                   sorted, expert_ids, npp, max_padded, max_blocks);
-    PMOE_CUDA_OK(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_s;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_align_scatter_kernel, topk_ids, n, E, p.seg, static_cast<const int *>(counts),
+                                    block_m, pad_to, sorted, expert_ids, npp, max_padded, max_blocks));
     return PMOE_OK;
 }
 

@@ -383,37 +383,11 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------------
-// down kernel (split). Two accumulators of unequal width so that the drain of one sub-tile runs under the MMAs
-// of the next: a work item is one row block x up to 384 output columns, computed as sub-tile 0 (256 columns,
-// TMEM columns [0,256)) followed by sub-tile 1 (128 columns, TMEM columns [256,384)); the four 16-column scale
-// regions sit at TMEM columns [448,512) (a ring of at most four slots never has more scale sets in flight:
-// the copy for fill f+4 is issued only after slot f's MMAs have completed and released the slot). A last item
-// narrower than 384 columns has a 256- or 128-column sub-tile 0 only. With six to sixteen k-steps per sub-tile
-// the commit -> drain -> release hand-over of a single accumulator was a third of this kernel's time.
-//   misc barriers: 0,1 tmem_full[acc] | 2,3 tmem_empty[acc]
+// down kernel (split): misc barriers 0 tmem_full | 1 tmem_empty
 // ---------------------------------------------------------------------------------------------
-constexpr uint32_t DOWN_SF_TMEM_BASE = 448;
-constexpr int DOWN_ITEM_COLS = 384;
-
-struct SubTile {
-    int col0, width, acc;
-};
-__device__ __forceinline__ int down_subtiles(int K, int unit, SubTile (&st)[2]) {
-    const int start = unit * DOWN_ITEM_COLS;
-    st[0].col0 = start;
-    st[0].width = min(256, K - start);
-    st[0].acc = 0;
-    if (K - start <= 256) return 1;
-    st[1].col0 = start + 256;
-    st[1].width = 128;
-    st[1].acc = 1;
-    return 2;
-}
-
 __global__ void __launch_bounds__(THREADS, 1)
 moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_w2,
-                      const __grid_constant__ CUtensorMap map_w2_half, const __grid_constant__ CUtensorMap map_act_short,
-                      const Args a) {
+                      const __grid_constant__ CUtensorMap map_act_short, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, a.stages, a.bulk_reduce ? RED_STAGE_BYTES : 0u);
     int *status = &g_status_mxfp8;
@@ -425,13 +399,10 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
             mbar_init(sm.empty(s), 1);
         }
         mbar_init(sm.misc(0), 1);
-        mbar_init(sm.misc(1), 1);
-        mbar_init(sm.misc(2), EPI_WARPS);
-        mbar_init(sm.misc(3), EPI_WARPS);
+        mbar_init(sm.misc(1), EPI_WARPS);
         fence_mbar_init();
         tma_prefetch_desc(&map_act);
         tma_prefetch_desc(&map_w2);
-        tma_prefetch_desc(&map_w2_half);
     }
     if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
     tc_fence_before();
@@ -443,8 +414,8 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
     if (a.use_pdl) pdl_wait_primary();
 
     const int m_blocks = live_row_blocks(a.npp, a.sorted_num);
-    const int n_units = (a.K + DOWN_ITEM_COLS - 1) / DOWN_ITEM_COLS;
-    const int num_items = m_blocks * n_units;
+    const int n_tiles = a.K / 256;
+    const int num_tiles = m_blocks * n_tiles;
     const int ksteps = a.H / BKB;
 
     if (warp == 0) {
@@ -453,35 +424,27 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
             uint32_t ph = 0;
             long long issued = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
-                const Coord c = tile_coord(t, m_blocks, n_units);
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Coord c = tile_coord(t, m_blocks, n_tiles);
                 const int e = a.expert_ids[c.m_blk];
+                const int w2_row = e * a.K + c.n_tile * 256;
+                const uint8_t *sf_w0 = a.w2_scales + static_cast<size_t>(w2_row >> 7) * ksteps * SF_TILE;
+                const uint8_t *sf_w1 = sf_w0 + static_cast<size_t>(ksteps) * SF_TILE;
                 const uint8_t *sf_a = a.act_sf + static_cast<size_t>(c.m_blk) * ksteps * SF_TILE;
                 const bool short_a = block_is_short(a, c.m_blk);
-                SubTile st[2];
-                const int nsub = down_subtiles(a.K, c.n_tile, st);
-                for (int q = 0; q < nsub && ok; ++q) {
-                    const int w2_row = e * a.K + st[q].col0;
-                    const bool wide = st[q].width == 256;
-                    const uint8_t *sf_w0 = a.w2_scales + static_cast<size_t>(w2_row >> 7) * ksteps * SF_TILE;
-                    const uint8_t *sf_w1 = sf_w0 + static_cast<size_t>(ksteps) * SF_TILE;
-                    const uint32_t bytes = (short_a ? SHORT_A_BYTES : A_BYTES) + (wide ? B_BYTES : B_BYTES / 2) +
-                                           (wide ? 3 : 2) * SF_TILE;
-                    for (int ks = 0; ks < ksteps; ++ks) {
-                        ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
-                        if (!ok) break;
-                        mbar_arrive_expect_tx(sm.full(s), bytes);
-                        tma_load_2d(sm.a(s), short_a ? &map_act_short : &map_act, sm.full(s), ks * BKB, c.m_blk * BM);
-                        tma_load_2d(sm.b(s), wide ? &map_w2 : &map_w2_half, sm.full(s), ks * BKB, w2_row);
-                        bulk_load_1d(sm.sfa(s), sf_a + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
-                        bulk_load_1d(sm.sfb(s), sf_w0 + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
-                        if (wide)
-                            bulk_load_1d(sm.sfb(s) + SF_TILE, sf_w1 + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
-                        ++issued;
-                        if (++s == a.stages) {
-                            s = 0;
-                            ph ^= 1;
-                        }
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sm.full(s), short_a ? STAGE_TX_BYTES - A_BYTES + SHORT_A_BYTES : STAGE_TX_BYTES);
+                    tma_load_2d(sm.a(s), short_a ? &map_act_short : &map_act, sm.full(s), ks * BKB, c.m_blk * BM);
+                    tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BKB, w2_row);
+                    bulk_load_1d(sm.sfa(s), sf_a + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s), sf_w0 + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    bulk_load_1d(sm.sfb(s) + SF_TILE, sf_w1 + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    ++issued;
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
                     }
                 }
             }
@@ -490,48 +453,29 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc_wide = idesc_mxf8_f32(128, 256);
-            constexpr uint32_t idesc_half = idesc_mxf8_f32(128, 128);
+            constexpr uint32_t idesc = idesc_mxf8_f32(128, 256);
             int s = 0;
             uint32_t ph = 0;
-            uint32_t uses[2] = {0, 0};
+            int it = 0;
             long long fill = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
-                const Coord c = tile_coord(t, m_blocks, n_units);
-                SubTile st[2];
-                const int nsub = down_subtiles(a.K, c.n_tile, st);
-                for (int q = 0; q < nsub && ok; ++q) {
-                    const int acc = st[q].acc;
-                    const bool wide = st[q].width == 256;
-                    ok = mbar_wait(sm.misc(2 + acc), (uses[acc] & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                ok = mbar_wait(sm.misc(1), (it & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int ks = 0; ks < ksteps; ++ks, ++fill) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem_base + static_cast<uint32_t>(acc) * 256u;
-                    for (int ks = 0; ks < ksteps; ++ks, ++fill) {
-                        ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t sfa_t = tmem_base + DOWN_SF_TMEM_BASE + 16u * static_cast<uint32_t>(fill & 3);
-                        const uint32_t sfb_t = sfa_t + 4;
-                        tmem_cp_sf_32x128b_warpx4(sfa_t, smem_desc_sf(sm.sfa(s)));
-                        tmem_cp_sf_32x128b_warpx4(sfb_t, smem_desc_sf(sm.sfb(s)));
-                        if (wide) tmem_cp_sf_32x128b_warpx4(sfb_t + 4, smem_desc_sf(sm.sfb(s) + SF_TILE));
-#pragma unroll
-                        for (uint32_t kb = 0; kb < 4; ++kb)
-                            umma_mxf8(d, smem_desc_sw128(sm.a(s) + kb * 32), smem_desc_sw128(sm.b(s) + kb * 32),
-                                      idesc_with_sf_ids(wide ? idesc_wide : idesc_half, kb, kb), sfa_t, sfb_t,
-                                      (ks | static_cast<int>(kb)) != 0 ? 1u : 0u);
-                        umma_commit(sm.empty(s));
-                        if (++s == a.stages) {
-                            s = 0;
-                            ph ^= 1;
-                        }
+                    issue_slot(tmem_base, sm.a(s), sm.b(s), sm.sfa(s), sm.sfb(s), sm.sfb(s) + SF_TILE, tmem_base, fill,
+                               ks == 0, idesc, 2);
+                    umma_commit(sm.empty(s));
+                    if (++s == a.stages) {
+                        s = 0;
+                        ph ^= 1;
                     }
-                    if (!ok) break;
-                    umma_commit(sm.misc(acc));
-                    ++uses[acc];
                 }
+                if (ok) umma_commit(sm.misc(0));
             }
         }
         __syncwarp();
@@ -539,58 +483,45 @@ moe_down_mxfp8_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_
         const int ew = warp - 2;
         const uint32_t lane_base = (warp & 3) * 32;
         const int row = lane_base + lane;
-        const int cg = ew >> 2;          // which half of the sub-tile's columns this warp handles
-        uint32_t uses[2] = {0, 0};
-        bool ok = true;
-        for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
-            const Coord c = tile_coord(t, m_blocks, n_units);
+        const int cg = ew >> 2;          // output columns [cg*128, cg*128+128) of the 256-wide tile
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
             const int pair = a.sorted_ids[c.m_blk * BM + row];
             const int tok = pair >= 0 ? pair / a.top_k : 0;
             const bool valid = pair >= 0 && tok < a.M;
             const float wgt = valid ? a.topk_weights[pair] : 0.f;
-            SubTile st[2];
-            const int nsub = down_subtiles(a.K, c.n_tile, st);
-            for (int q = 0; q < nsub && ok; ++q) {
-                const int acc = st[q].acc;
-                const int half = st[q].width >> 1;    // columns per warp group: 128 or 64
-                __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + st[q].col0 + cg * half;
-                ok = warp_wait(sm.misc(acc), uses[acc] & 1, status, ST_TIMEOUT_TMEM_FULL, lane);
-                if (!ok) break;
-                ++uses[acc];
-                tc_fence_after();
-                float v[128];
-                const uint32_t src = tmem_addr(tmem_base, lane_base, static_cast<uint32_t>(acc) * 256u + cg * half);
+            __nv_bfloat16 *dst = a.out + static_cast<size_t>(valid ? tok : 0) * a.K + c.n_tile * 256 + cg * 128;
+            if (!warp_wait(sm.misc(0), it & 1, status, ST_TIMEOUT_TMEM_FULL, lane)) break;
+            tc_fence_after();
+            float v[128];
 #pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    if (g * 32 < half) ld32(v + g * 32, src + g * 32);
-                tmem_ld_wait();
-                tc_fence_before();
-                warp_arrive(sm.misc(2 + acc), lane);
-                if (a.bulk_reduce) {
-                    // scaled bf16 row segment -> this thread's padded staging row -> one bulk reduction
-                    const uint32_t red_row = sm.act + (threadIdx.x - 64) * RED_ROW_BYTES;
-                    tma_store_wait_read<0>();
+            for (int q = 0; q < 4; ++q) ld32(v + q * 32, tmem_addr(tmem_base, lane_base, cg * 128 + q * 32));
+            tmem_ld_wait();
+            tc_fence_before();
+            warp_arrive(sm.misc(1), lane);
+            if (a.bulk_reduce) {
+                // scaled bf16 row segment -> this thread's padded staging row -> one 256-byte bulk reduction
+                const uint32_t red_row = sm.act + (threadIdx.x - 64) * RED_ROW_BYTES;
+                tma_store_wait_read<0>();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j * 8 < half)
-                            st_shared_v4(red_row + j * 16, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
-                                         pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
-                                         pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
-                                         pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
-                    fence_proxy_async_smem();
-                    if (valid) bulk_reduce_add_bf16(dst, red_row, static_cast<uint32_t>(half) * 2u);
-                    tma_store_commit();
-                    continue;
-                }
-                if (valid) {
+                for (int j = 0; j < 16; ++j)
+                    st_shared_v4(red_row + j * 16, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                                 pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                                 pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                                 pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
+                fence_proxy_async_smem();
+                if (valid) bulk_reduce_add_bf16(dst, red_row, 256);
+                tma_store_commit();
+                continue;
+            }
+            if (valid) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j * 8 < half)
-                            red_add_bf16x8(dst + j * 8, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
-                                           pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
-                                           pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
-                                           pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
-                }
+                for (int j = 0; j < 16; ++j)
+                    red_add_bf16x8(dst + j * 8, pack_bf16x2(wgt * v[j * 8 + 0], wgt * v[j * 8 + 1]),
+                                   pack_bf16x2(wgt * v[j * 8 + 2], wgt * v[j * 8 + 3]),
+                                   pack_bf16x2(wgt * v[j * 8 + 4], wgt * v[j * 8 + 5]),
+                                   pack_bf16x2(wgt * v[j * 8 + 6], wgt * v[j * 8 + 7]));
             }
         }
         if (a.bulk_reduce) tma_store_wait<0>();
@@ -1401,11 +1332,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         if (dn.bulk_reduce) dn.stages = std::min(dn.stages, 3);   // room for the reduction staging tile
         const size_t smem = smem_bytes(dn.stages, dn.bulk_reduce ? RED_STAGE_BYTES : 0u);
         if (int rc = set_smem(moe_down_mxfp8_kernel, smem)) return rc;
-        CUtensorMap map_w2_half;   // 128-row boxes for the narrow sub-tiles
-        if (int rc = make_tmap_2d(&map_w2_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.w2, static_cast<uint64_t>(p.E) * p.K,
-                                  H, 128, BKB, CU_TENSOR_MAP_SWIZZLE_128B, "w2 (128-row boxes)"))
-            return rc;
-        const int tiles = max_blocks * ((p.K + DOWN_ITEM_COLS - 1) / DOWN_ITEM_COLS);
+        const int tiles = max_blocks * (p.K / 256);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(std::min(tiles, sms));
         cfg.blockDim = dim3(THREADS);
@@ -1416,7 +1343,7 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = dn.use_pdl ? 1 : 0;
-        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_mxfp8_kernel, map_act, map_w2, map_w2_half, map_act_short, dn));
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_down_mxfp8_kernel, map_act, map_w2, map_act_short, dn));
     }
     return PMOE_OK;
 }
