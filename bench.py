@@ -610,6 +610,36 @@ def ep_sweep_entry(name, dtype, rank, world, device, args):
     return entry
 
 
+def sweep_pre_entries(device, peaks):
+    """The two steps ahead of the path, at the c3 shapes (T=16384, E=256, top_k=8, K=7168): router and MX activation
+    quantiser, L2 flushed before every call, achieved GB/s over their algorithmic bytes."""
+    import torch
+    ops = torch.ops.prime_moe
+    T, K, E, N, k, _ = CONFIGS["c3"]
+    g = torch.Generator(device=device).manual_seed(4400)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    out = []
+    logits = torch.randn(T, E, device=device, generator=g)
+    ms = time_calls(lambda: ops.route_topk(logits, k, True), 20, flush_buf)
+    nbytes = 4.0 * T * E + 8.0 * T * k
+    out.append(("route_topk", "route_topk_kernel", "fp32 logits", ms, nbytes))
+    x = torch.randn(T, K, device=device, generator=g).to(torch.bfloat16)
+    ms = time_calls(lambda: ops.quantize_mx(x, None), 20, flush_buf)
+    nbytes = 2.0 * T * K + T * K * (1.0 + 1.0 / 32)
+    out.append(("quantize_mx", "quantize_mx_kernel", "bf16 -> e4m3 + e8m0/32", ms, nbytes))
+    entries = []
+    for op, kernel, dtype, ms, nbytes in out:
+        ach = nbytes / (ms * 1e-3) / 1e9
+        entries.append({"config": "c3", "op": op, "dtype": dtype, "ms_per_step": ms, "value": ach, "unit": "GB/s",
+                        "roofline": {"kernel": kernel, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
+                                     "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                                     "peak_source": peaks["source"] + " (STREAM-style copy)", "traffic": None,
+                                     "algorithmic_bytes": nbytes}})
+    del flush_buf, logits, x
+    torch.cuda.empty_cache()
+    return entries
+
+
 def run_sweep(impl, device, peaks, stages, ref_pkg=None):
     entries = []
     for name, tokens, dtype in SWEEP:
@@ -626,6 +656,11 @@ def run_sweep(impl, device, peaks, stages, ref_pkg=None):
                                              else "the reference's moe_align_kernel"))
         except Exception as exc:
             entries.append({"config": name, "op": "moe_align", "error": f"{type(exc).__name__}: {exc}"[:200]})
+    if impl == "ours":          # the reference has no router or quantiser (it takes both from its caller)
+        try:
+            entries.extend(sweep_pre_entries(device, peaks))
+        except Exception as exc:
+            entries.append({"config": "c3", "op": "route_topk / quantize_mx", "error": f"{type(exc).__name__}: {exc}"[:200]})
     return entries
 
 

@@ -89,6 +89,7 @@ struct Args {
     const int32_t *list_counts;
     const int32_t *live_rows;              // optional: rows of `out` in use (only those are zeroed)
     const unsigned long long *out_rows;    // optional: address of every row of `out` (down kernels, plain reductions)
+    int down_ksplit; // one-CTA down kernel: split the k-range of its tiles when there are fewer tiles than CTAs
     int short_boxes; // one-CTA split kernels: row blocks with <= SHORT_ROWS routed rows move only those rows of
                      // the A operand and of the activation tile (the rest of a 128-row block is padding)
 };
@@ -918,8 +919,16 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
 
     const int m_blocks = num_tile_rows(a);
     const int n_tiles = (a.K + 255) / 256;
-    const int num_tiles = m_blocks * n_tiles;
-    const int ksteps = a.H / BK;
+    const int ksteps_all = a.H / BK;
+    // Few tiles for many SMs (the single-block tails of the bpc = 2 pipeline: a handful of row blocks x K/256
+    // column tiles): cut every tile's k-range into `ksplit` parts run as tiles of their own. The epilogue ADDS into
+    // `out` anyway, so the partial products need no extra reduction.
+    int ksplit = 1;
+    if (a.down_ksplit && m_blocks * n_tiles > 0) ksplit = max(1, min(min(4, ksteps_all), static_cast<int>(gridDim.x) / (m_blocks * n_tiles)));
+    const int kchunk = (ksteps_all + ksplit - 1) / ksplit;
+    ksplit = (ksteps_all + kchunk - 1) / kchunk;   // no empty part: an accumulator without MMAs must never be added
+    const int base_tiles = m_blocks * n_tiles;
+    const int num_tiles = base_tiles * ksplit;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -928,18 +937,19 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
             long long issued = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const Coord c = tile_coord(t, m_blocks, n_tiles);
-            const int mb = tile_row_block(a, c.m_blk);
+                const Coord c = tile_coord(t % base_tiles, m_blocks, n_tiles);
+                const int ks0 = (t / base_tiles) * kchunk, ks1 = min(ksteps_all, ks0 + kchunk);
+                const int mb = tile_row_block(a, c.m_blk);
                 const int e = a.expert_ids[mb];
                 const int w2_row = e * a.K + c.n_tile * 256;
                 const bool short_a = block_is_short(a, mb);
-                for (int ks = 0; ks < ksteps; ++ks) {
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
                     mbar_arrive_expect_tx(sm.full(s), short_a ? B_BYTES + SHORT_A_BYTES : STAGE_BYTES);
                     tma_load_2d(sm.a(s), short_a ? &map_act_short : &map_act, sm.full(s), ks * BK, mb * BM);
                     tma_load_2d(sm.b(s), &map_w2, sm.full(s), ks * BK, w2_row);
-                    if (a.l2_ahead && ks + a.l2_ahead < ksteps) tma_prefetch_l2_2d(&map_w2, (ks + a.l2_ahead) * BK, w2_row);
+                    if (a.l2_ahead && ks + a.l2_ahead < ks1) tma_prefetch_l2_2d(&map_w2, (ks + a.l2_ahead) * BK, w2_row);
                     ++issued;
                     if (++s == a.stages) {
                         s = 0;
@@ -963,14 +973,15 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * 256;
-                for (int ks = 0; ks < ksteps; ++ks) {
+                const int ks0 = (t / base_tiles) * kchunk, ks1 = min(ksteps_all, ks0 + kchunk);
+                for (int ks = ks0; ks < ks1; ++ks) {
                     ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
                         umma_f16(d, smem_desc_sw128(sm.a(s) + k * 32), smem_desc_sw128(sm.b(s) + k * 32), idesc,
-                                 (ks | k) != 0);
+                                 (ks != ks0) || (k != 0));
                     umma_commit(sm.empty(s));
                     if (++s == a.stages) {
                         s = 0;
@@ -989,7 +1000,7 @@ moe_down_bf16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_c
         const int cg = ew / 4;
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
-            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const Coord c = tile_coord(t % base_tiles, m_blocks, n_tiles);
             const int mb = tile_row_block(a, c.m_blk);
             const int buf = it & 1;
             const int pair = a.sorted_ids[mb * BM + row];
@@ -1761,6 +1772,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
             if (tails) {
                 Args td = ta;
                 td.use_pdl = 0;
+                td.down_ksplit = 1;
                 td.bulk_reduce = bulk_reduce ? 1 : 0;
                 if (bulk_reduce) td.stages = std::min(td.stages, 3);
                 if (int rc = launch_single(moe_down_bf16_kernel, td, (max_blocks / 2) * ((p.K + 255) / 256),

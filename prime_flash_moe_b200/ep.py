@@ -304,8 +304,9 @@ class ExpertParallelMoE:
         # buffers (a long k-loop per tile keeps the NVLink rate low); narrow ones copy finished rows afterwards
         direct = self.direct_return
         if direct is None:
-            direct = x_scales is None and isinstance(self.experts, LocalExperts) and self.experts.split and \
-                self.experts.w1.shape[1] >= 8192
+            direct = isinstance(self.experts, LocalExperts) and self.experts.w1.shape[1] >= 8192
+        # the epilogue-direct return exists for the bf16 split pipeline of this package's own kernels only
+        direct = bool(direct) and x_scales is None and isinstance(self.experts, LocalExperts) and self.experts.split
         plan = make_dispatch_plan(topk_ids, topk_weights, self.num_experts, G)
         ex.epoch += 1
         e, tab, st = ex.epoch, ex.table.data_ptr(), torch.cuda.current_stream().cuda_stream

@@ -68,6 +68,38 @@ def test_static_scratch_matches_allocating_entry_point_twice():
     assert capi.device_status() == 0
 
 
+def test_static_entry_point_takes_no_device_memory():
+    """What the entry point is for: a call must not take device memory from anywhere. Outputs are allocated first,
+    the entry point is warmed up once (its first call per device looks up the array's address), and then the
+    driver's free-memory figure and the sizes of torch's pools must be the same before and after more calls."""
+    from prime_flash_moe_b200 import capi
+    lib = capi.lib()
+    T, E, k = 8192, 128, 8
+    ids, _ = O.make_routing(T, E, k, seed=31)
+    ids = ids.to(DEV)
+    n = ids.numel()
+    max_padded = (n + E * 127 + 127) // 128 * 128
+    s = torch.empty(max_padded, dtype=torch.int32, device=DEV)
+    e = torch.empty(max_padded // 128, dtype=torch.int32, device=DEV)
+    npp = torch.empty(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    call = lambda: lib.pmoe_moe_align_static(ids.data_ptr(), s.data_ptr(), e.data_ptr(), npp.data_ptr(), n, E, 128, 128,
+                                             max_padded, max_padded // 128, stream)
+    assert call() == 0
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    reserved0, allocated0 = torch.cuda.memory_reserved(), torch.cuda.memory_allocated()
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"device free memory changed by {free0 - free1} bytes"
+    assert (torch.cuda.memory_reserved(), torch.cuda.memory_allocated()) == (reserved0, allocated0)
+    want_s, want_e, want_n = O.moe_align_spec(ids.cpu().numpy(), E, 128, 1)
+    assert np.array_equal(s.cpu().numpy(), want_s) and np.array_equal(e.cpu().numpy(), want_e)
+    assert int(npp.item()) == int(want_n[0])
+
+
 def test_static_scratch_rejects_oversized_problems():
     from prime_flash_moe_b200 import capi
     lib = capi.lib()
