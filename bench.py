@@ -562,7 +562,7 @@ def ep_sweep_entry(name, dtype, rank, world, device, args):
     import torch
     sys.path.insert(0, str(ROOT))
     from oracle import moe_oracle as O
-    from prime_flash_moe_b200 import ep
+    from prime_flash_moe_b200 import capi, ep
     T, K, E, N, k, routing = CONFIGS[name]
     per = E // world
     w1q, w1s, w2q, w2s = [], [], [], []
@@ -604,7 +604,7 @@ def ep_sweep_entry(name, dtype, rank, world, device, args):
              "value": world * flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "tokens_per_s": world * T / (ms * 1e-3),
              "experts_per_rank": per, "rows_computed_by_rank0": layer.last_recv_rows,
              "rows_sent_by_rank0": layer.last_sent_rows, "combine": layer.combine_mode, "phase_ms_rank0": phases,
-             "finite": bool(torch.isfinite(out.float()).all())}
+             "finite": bool(torch.isfinite(out.float()).all()), "device_status": capi.device_status()}
     if layer.exchange is not None:
         layer.exchange.close()
     return entry
@@ -822,6 +822,21 @@ def run_gpu_arm(args, impl):
     for _ in range(max(args.warmup, 3)):
         step(xin, ids, wts, out)
     barrier_sync(ref_world)
+    ep_fallback = None
+    if ep_mode and layer.combine_mode == "peer":
+        # the peer-memory exchange has bounded waits: if any rank recorded an expired one during warm-up (a peer that
+        # cannot be reached, a rank far behind), every rank switches to the NCCL exchange together instead of timing
+        # a broken step
+        st = max_over_ranks(float(capi.device_status()), world, device)
+        if st != 0:
+            capi.reset_device_status()
+            ep_fallback = f"device status {int(st)} after warm-up in peer mode: switched to the NCCL exchange"
+            if layer.exchange is not None:
+                layer.exchange.close()
+            layer = ep.ExpertParallelMoE(E, experts, combine="nccl")
+            for _ in range(3):
+                step(xin, ids, wts, out)
+            barrier_sync(ref_world)
     with ClockSampler(local) as clocks:
         if flush_l2:
             # the weights a step touches would stay in the 126 MB L2 from one step to the next: write a 256 MB
@@ -846,6 +861,65 @@ def run_gpu_arm(args, impl):
             ms_total = max_over_ranks(a.elapsed_time(b), ref_world, device)
     ms_step = ms_total / args.steps
     value = ref_world * flops / (ms_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel: timed alone, right after the device-resident loop (same thermal state),
+    # with the SM clock sampled while it runs ----
+    peaks = measured_peaks()
+    roofline = None
+    roof_clocks = ClockSampler(local)
+    roof_clocks.__enter__()
+    if impl == "ours" and args.split and mx and not ep_mode:
+        roofline = roofline_mxfp8(args, capi, ops, (xq, xs, w1q, w1s, w2q, w2s), ids, wts, out, cfg, peaks, value / world,
+                                  flush_buf if flush_l2 else None)
+        roofline = weight_streaming_roofline(roofline, cfg, ids, roofline["kernel_ms"]["moe_up_mxfp8"], ms_step, peaks, True,
+                                             431.8e6 if (args.config == "c2" and args.tokens == 128) else None)
+    if impl == "ours" and args.split and not mx and not ep_mode:
+        # dominant kernel = the gate/up GEMM (2/3 of the FLOPs); timed alone through the profiling hook
+        lib = capi.lib()
+        step(x, ids, wts, out)                      # fills the workspace-independent state
+        s, e, n = ops.moe_align(ids, E, 128, args.bpc)
+        nbytes = lib.pmoe_fused_moe_bf16_workspace_bytes(T, K, N, s.numel(), 1)
+        ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        off = (-ws.data_ptr()) % 1024
+        ws = ws[off:off + nbytes]
+        call = lambda: capi.fused_moe_bf16(x, w1, w2, s, e, n, wts, out, k, 128, 64 if args.warp_n == 4 else 32, args.warp_n,
+                                           args.stages, args.bpc, 1, True, workspace=ws)
+        call()
+        per_kernel = {}
+        masks = [("gather_rows", 1), ("moe_up_bf16", 2), ("moe_down_bf16", 4)]
+        if args.bpc == 2:      # the CTA-pair kernels without the single-block tail launches that follow them
+            masks = [("gather_rows", 1), ("moe_up_bf16", 2 | 8), ("moe_up_bf16_with_tails", 2), ("moe_down_bf16", 4 | 8),
+                     ("moe_down_bf16_with_tails", 4)]
+        for name, mask in masks:
+            lib.pmoe_debug_set_phase_mask(mask)
+            per_kernel[name] = time_calls(call, 20, flush_buf if flush_l2 else None)
+        lib.pmoe_debug_set_phase_mask(7)
+        call()
+        torch.cuda.synchronize()
+        rows_dominant = T * k
+        if args.bpc == 2 and os.environ.get("PMOE_PAIR_TAILS", "1") != "0":
+            # rows of the half-empty last pairs run on the one-CTA kernels, not on the kernel timed here
+            cnt = torch.bincount(ids_cpu.reshape(-1).long(), minlength=E)
+            rem = cnt % 256
+            rows_dominant -= int(rem[(rem > 0) & (rem <= 128)].sum())
+        up_flops = 2.0 * rows_dominant * K * N
+        achieved = up_flops / (per_kernel["moe_up_bf16"] * 1e-3) / 1e12
+        # DRAM bytes of one launch of that kernel, from the ncu captures summarised under profiles/
+        traffic = {("c1", 2): 2.713e9, ("c2", 1): 1.112e9}.get((args.config, args.bpc)) \
+            if (not args.tokens and args.stages == 4 and args.warp_n == 4) else None
+        roofline = {"kernel": "moe_pair_bf16_kernel<up>" if args.bpc == 2 else "moe_up_bf16_kernel", "bound": "tensor",
+                    "rows": rows_dominant, "achieved": achieved,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
+                    "traffic": traffic, "algorithmic_bytes": float(E * N * K * 2 + rows_dominant * K * 2 + rows_dominant * N + T * K * 2),
+                    "kernel_ms": per_kernel, "whole_op_frac": value / world / peaks["bf16_tflops"]}
+        roofline = weight_streaming_roofline(roofline, cfg, ids, per_kernel["moe_up_bf16"], ms_step, peaks, False,
+                                             835.3e6 if (args.config == "c2" and args.tokens == 128) else None)
+        assert capi.device_status() == 0, "a kernel recorded an error status"
+    roof_clocks.__exit__(None, None, None)
+    if roofline is not None:
+        roofline["sm_mhz_during_kernel_timing"] = roof_clocks.summary()["sm_mhz"]
 
     # ---- end to end: host buffers, copies inside the timed region ----
     # What a caller feeding the layer from host memory does: two sets of device buffers, the H2D copy of step
@@ -898,48 +972,6 @@ def run_gpu_arm(args, impl):
     e2e = {"value": ref_world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
-    peaks = measured_peaks()
-    roofline = None
-    if impl == "ours" and args.split and mx and not ep_mode:
-        roofline = roofline_mxfp8(args, capi, ops, (xq, xs, w1q, w1s, w2q, w2s), ids, wts, out, cfg, peaks, value / world,
-                                  flush_buf if flush_l2 else None)
-        roofline = weight_streaming_roofline(roofline, cfg, ids, roofline["kernel_ms"]["moe_up_mxfp8"], ms_step, peaks, True,
-                                             431.8e6 if (args.config == "c2" and args.tokens == 128) else None)
-    if impl == "ours" and args.split and not mx and not ep_mode:
-        # dominant kernel = the gate/up GEMM (2/3 of the FLOPs); timed alone through the profiling hook
-        lib = capi.lib()
-        step(x, ids, wts, out)                      # fills the workspace-independent state
-        s, e, n = ops.moe_align(ids, E, 128, args.bpc)
-        nbytes = lib.pmoe_fused_moe_bf16_workspace_bytes(T, K, N, s.numel(), 1)
-        ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
-        off = (-ws.data_ptr()) % 1024
-        ws = ws[off:off + nbytes]
-        call = lambda: capi.fused_moe_bf16(x, w1, w2, s, e, n, wts, out, k, 128, 64 if args.warp_n == 4 else 32, args.warp_n,
-                                           args.stages, args.bpc, 1, True, workspace=ws)
-        call()
-        per_kernel = {}
-        for name, mask in (("gather_rows", 1), ("moe_up_bf16", 2), ("moe_down_bf16", 4)):
-            lib.pmoe_debug_set_phase_mask(mask)
-            per_kernel[name] = time_calls(call, 20, flush_buf if flush_l2 else None)
-        lib.pmoe_debug_set_phase_mask(7)
-        call()
-        torch.cuda.synchronize()
-        up_flops = 2.0 * T * k * K * N
-        achieved = up_flops / (per_kernel["moe_up_bf16"] * 1e-3) / 1e12
-        # DRAM bytes of one launch of that kernel, from the ncu captures summarised under profiles/
-        traffic = {("c1", 2): 5.379e9, ("c2", 1): 1.112e9}.get((args.config, args.bpc)) \
-            if (not args.tokens and args.stages == 4 and args.warp_n == 4) else None
-        roofline = {"kernel": "moe_pair_bf16_kernel<up>" if args.bpc == 2 else "moe_up_bf16_kernel", "bound": "tensor",
-                    "achieved": achieved,
-                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                    "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
-                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
-                    "traffic": traffic, "algorithmic_bytes": float(E * N * K * 2 + T * k * K * 2 + T * k * N + T * K * 2),
-                    "kernel_ms": per_kernel, "whole_op_frac": value / world / peaks["bf16_tflops"]}
-        roofline = weight_streaming_roofline(roofline, cfg, ids, per_kernel["moe_up_bf16"], ms_step, peaks, False,
-                                             835.3e6 if (args.config == "c2" and args.tokens == 128) else None)
-        assert capi.device_status() == 0, "a kernel recorded an error status"
-
     cpu_baseline = None
     if rank == 0 and not args.no_cpu_baseline and not ep_mode and ref_world == 1:
         sample = 256 if T >= 256 else T
@@ -974,7 +1006,7 @@ def run_gpu_arm(args, impl):
                    "parity": ep_parity,
                    "parity_what": "max over ranks of max|ep_out - single_gpu_out| / max|single_gpu_out| on each "
                                   "rank's first 64 tokens (single-GPU operator on the full weights)",
-                   "combine": layer.combine_mode, "phase_ms_rank0": ep_phases,
+                   "combine": layer.combine_mode, "fallback": ep_fallback, "phase_ms_rank0": ep_phases,
                    "collective": ("none on the data path: rows, slot tables, counts and partial sums are stored "
                                   "into the peers' buffers over NVLink by this library's kernels"
                                   if layer.combine_mode == "peer" else

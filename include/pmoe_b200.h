@@ -185,6 +185,15 @@ int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, 
 enum { PMOE_DTYPE_F32 = 0, PMOE_DTYPE_BF16 = 1 };
 int pmoe_route_topk(const void *logits, int logits_dtype, int T, int num_experts, int top_k, int renormalize,
                     int32_t *topk_ids, float *topk_weights, pmoe_stream_t stream);
+/* Router and moe_align in one call: as pmoe_route_topk followed by pmoe_moe_align_ws on its topk_ids (same outputs,
+ * bit for bit), but for n = T * top_k above the single-CTA sizes ONE kernel routes the tokens, counts its own ids
+ * per expert and pre-fills sorted_token_ids - the ids are not read back for counting and one launch disappears.
+ * workspace: pmoe_moe_align_workspace_bytes(T * top_k, num_experts) bytes. When top_k does not divide the id range
+ * of a thread block (it does for every power of two up to 256) the two separate kernels run. */
+int pmoe_route_topk_align(const void *logits, int logits_dtype, int T, int num_experts, int top_k, int renormalize,
+                          int32_t *topk_ids, float *topk_weights, int32_t *sorted_token_ids, int32_t *expert_ids,
+                          int32_t *num_tokens_post_padded, int block_m, int pad_to, int max_padded, int max_blocks,
+                          void *workspace, size_t workspace_bytes, pmoe_stream_t stream);
 int pmoe_quantize_mx(const void *x /* bf16[src_rows, K] */, const int32_t *row_index, int src_rows, void *q,
                      void *scales, int rows, int K, pmoe_stream_t stream);
 
@@ -278,7 +287,7 @@ int pmoe_reset_device_status(void);
 
 /* Profiling hook, process-wide, not thread-safe: restrict the split pipelines to a subset of their
  * launches so that each kernel can be timed alone with CUDA events (1 = row gather, 2 = gate/up
- * kernel, 4 = down kernel; default 7 = all). A partial run leaves `out` undefined. Returns the
+ * kernel, 4 = down kernel; default 7 = all; + 8 = without the single-block tail launches of the bpc = 2 pipeline). A partial run leaves `out` undefined. Returns the
  * previous mask. No counterpart in the reference. */
 int pmoe_debug_set_phase_mask(int mask);
 

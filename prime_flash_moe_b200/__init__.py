@@ -93,6 +93,13 @@ def route_topk(logits, top_k, renormalize=True):
     return torch.ops.prime_moe.route_topk(logits, top_k, renormalize)
 
 
+def route_topk_align(logits, top_k, renormalize=True, block_m=128, bpc=1):
+    """``route_topk`` and ``moe_align`` in one call: ``(topk_ids, topk_weights, sorted_token_ids, expert_ids,
+    num_tokens_post_padded)``. Above the single-CTA sizes one kernel routes the tokens and counts its own ids per
+    expert, so the histogram pass of ``moe_align`` and one launch disappear."""
+    return torch.ops.prime_moe.route_topk_align(logits, top_k, renormalize, block_m, bpc)
+
+
 def quantize_mx(x, row_index=None):
     """bf16 ``[T, K]`` -> OCP-MX ``(e4m3 [R, K], e8m0 [R, K/32])`` as ``fused_moe_mxfp8`` takes ``x`` / ``x_scales``;
     with ``row_index`` int32 ``[R]`` output row r is ``x[row_index[r]]``. Bit-identical to the reference's test
@@ -114,4 +121,5 @@ def pack_scales_blocked(scales: torch.Tensor) -> torch.Tensor:
     return tiles.reshape(*lead, -1).view(torch.float8_e8m0fnu)
 
 
-__all__ = ["fused_moe_bf16", "fused_moe_mxfp8", "moe_align", "pack_scales_blocked", "route_topk", "quantize_mx", "BLOCK"]
+__all__ = ["fused_moe_bf16", "fused_moe_mxfp8", "moe_align", "pack_scales_blocked", "route_topk", "route_topk_align", "quantize_mx",
+           "BLOCK"]

@@ -51,6 +51,7 @@ SIGNATURES = {
     "pmoe_ep_push_back": (_i, [_vp, _i, _vp, _sz, _i, _i, _i, _i, _i, _vp]),
     "pmoe_ep_combine_peer": (_i, [_vp, _sz, _vp, _vp, _i, _i, _i, _i, _vp]),
     "pmoe_route_topk": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "pmoe_route_topk_align": (_i, [_vp, _i, _i, _i, _i, _i] + [_vp] * 5 + [_i] * 4 + [_vp, _sz, _vp]),
     "pmoe_quantize_mx": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "pmoe_debug_set_wait_ns": (_i, [C.c_ulonglong]),
     "pmoe_debug_wait_probe": (_i, [_vp]),
@@ -164,6 +165,25 @@ def route_topk(logits: torch.Tensor, top_k: int, renormalize: bool = True):
     with torch.cuda.device(logits.device):
         _check(lib().pmoe_route_topk(_p(logits), dtype, T, E, top_k, int(renormalize), _p(ids), _p(wts), _stream()))
     return ids, wts
+
+
+def route_topk_align(logits: torch.Tensor, top_k: int, renormalize: bool = True, block_m: int = 128, bpc: int = 1):
+    """Router + moe_align in one call: ``(topk_ids, topk_weights, sorted_token_ids, expert_ids, num_tokens_post_padded)``."""
+    assert logits.is_cuda and logits.dim() == 2 and logits.is_contiguous()
+    dtype = {torch.float32: 0, torch.bfloat16: 1}[logits.dtype]
+    T, E = logits.shape
+    n, pad_to = T * top_k, block_m * bpc
+    max_padded = (n + E * (pad_to - 1) + pad_to - 1) // pad_to * pad_to
+    mk = lambda *shape: torch.empty(*shape, dtype=torch.int32, device=logits.device)
+    ids, sorted_ids, expert_ids, npp = mk(T, top_k), mk(max_padded), mk(max_padded // block_m), mk(1)
+    wts = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    nbytes = lib().pmoe_moe_align_workspace_bytes(n, E)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _check(lib().pmoe_route_topk_align(_p(logits), dtype, T, E, top_k, int(renormalize), _p(ids), _p(wts), _p(sorted_ids),
+                                           _p(expert_ids), _p(npp), block_m, pad_to, max_padded, max_padded // block_m,
+                                           _p(ws), nbytes, _stream()))
+    return ids, wts, sorted_ids, expert_ids, npp
 
 
 def quantize_mx(x: torch.Tensor, row_index: torch.Tensor | None = None):

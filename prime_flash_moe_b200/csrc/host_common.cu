@@ -207,7 +207,7 @@ extern "C" int pmoe_debug_set_l2_ahead(int ksteps) {
 
 extern "C" int pmoe_debug_set_phase_mask(int mask) {
     const int old = pmoe::g_phase_mask;
-    pmoe::g_phase_mask = mask & 7;
+    pmoe::g_phase_mask = mask & 15;
     return old;
 }
 

@@ -84,7 +84,8 @@ bool pair_tails_enabled();
 // PMOE_DUAL=0/1 forces one / two row blocks per tile in the one-CTA bf16 gate/up kernel; unset = -1 = by size
 int dual_blocks_mode();   // bit 0: loads, bit 1: activation stores
 
-// which launches of a split pipeline run (pmoe_debug_set_phase_mask): 1 gather, 2 gate/up, 4 down
+// which launches of a split pipeline run (pmoe_debug_set_phase_mask): 1 gather, 2 gate/up, 4 down; 8 = without the
+// single-block tail launches of the bpc = 2 pipeline (to time the CTA-pair kernels alone)
 int phase_mask();
 
 }  // namespace pmoe

@@ -19,6 +19,7 @@
 #include <algorithm>
 
 #include "host_common.h"
+#include "route_warp.cuh"
 
 namespace pmoe {
 namespace {
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(kThreads) moe_align_hist_kernel(
 __global__ void __launch_bounds__(kThreads) moe_align_scatter_kernel(
     const int32_t *__restrict__ ids, int n, int E, int seg, const int *__restrict__ counts, int block_m,
     int pad_to, int32_t *__restrict__ sorted, int32_t *__restrict__ expert_ids, int32_t *__restrict__ npp,
-    int max_padded, int max_blocks) {
+    int max_padded, int max_blocks, int ids_from_primary) {
     extern __shared__ int sm[];
     int *cnt = sm;                       // [kWarpsPerCta][E] per-warp counts, later per-warp write cursors
     int *tot = cnt + kWarpsPerCta * E;   // [E] ids of expert e in all CTAs
@@ -248,6 +249,8 @@ __global__ void __launch_bounds__(kThreads) moe_align_scatter_kernel(
     __syncthreads();
     const int gw = blockIdx.x * kWarpsPerCta + warp;
     const int begin = min(gw * seg, n), end = min(begin + seg, n);
+    // after the fused router the ids themselves come from the preceding kernel: wait before reading them
+    if (ids_from_primary) asm volatile("griddepcontrol.wait;" ::: "memory");
     warp_histogram(ids, begin, end, E, cnt + warp * E);
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the histogram kernel's counts and -1 fill are complete
     // column sums of counts[cta][e]: `parts` threads share one expert when there are fewer experts than threads
@@ -352,12 +355,130 @@ int launch(const int32_t *topk_ids, int32_t *sorted, int32_t *expert_ids, int32_
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_align_scatter_kernel, topk_ids, n, E, p.seg, static_cast<const int *>(counts),
-                                    block_m, pad_to, sorted, expert_ids, npp, max_padded, max_blocks));
+                                    block_m, pad_to, sorted, expert_ids, npp, max_padded, max_blocks, 0));
     return PMOE_OK;
 }
 
 }  // namespace
 }  // namespace pmoe
+
+// ---------------------------------------------------------------------------------------------
+// router fused with the histogram pass: one kernel routes the tokens (softmax + top-k, one warp per token,
+// route_warp.cuh), writes topk_ids / topk_weights, counts its own ids per expert and fills sorted_token_ids with
+// -1 - i.e. it replaces route_topk_kernel AND moe_align_hist_kernel, and the ids are not read back for counting.
+// CTA c owns the ids [c*8*seg, (c+1)*8*seg) of the align plan, i.e. 8*seg / top_k whole tokens (the entry point
+// falls back to the two separate kernels when top_k does not divide 8*seg). 32 warps per CTA: the grid is the
+// align plan's (<= #SMs CTAs), so the tokens of a CTA are spread over more warps than the histogram pass has.
+// ---------------------------------------------------------------------------------------------
+namespace pmoe {
+namespace {
+
+template <typename T, int PER>
+__global__ void __launch_bounds__(1024) route_hist_kernel(
+    const T *__restrict__ logits, int tokens, int E, int top_k, int renormalize, int32_t *__restrict__ topk_ids,
+    float *__restrict__ topk_weights, int tokens_per_cta, int *__restrict__ counts, int32_t *__restrict__ sorted,
+    int max_padded) {
+    extern __shared__ int s_cnt[];   // [E]
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int t0 = blockIdx.x * tokens_per_cta, t1 = min(tokens, t0 + tokens_per_cta);
+    for (int t = t0 + warp; t < t1; t += nwarps) {
+        int idx;
+        float w;
+        route_token_warp<T, PER>(logits + static_cast<size_t>(t) * E, E, top_k, renormalize, lane, idx, w);
+        if (lane < top_k) {
+            topk_ids[static_cast<size_t>(t) * top_k + lane] = idx;
+            topk_weights[static_cast<size_t>(t) * top_k + lane] = w;
+            atomicAdd(&s_cnt[idx], 1);   // shared-memory integer counts: independent of the order of the adds
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[static_cast<size_t>(blockIdx.x) * E + e] = s_cnt[e];
+    int4 *s4 = reinterpret_cast<int4 *>(sorted);
+    const int n4 = max_padded >> 2;
+    const int4 m1 = make_int4(-1, -1, -1, -1);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) s4[i] = m1;
+    if (blockIdx.x == 0 && threadIdx.x < (max_padded & 3)) sorted[(n4 << 2) + threadIdx.x] = -1;
+}
+
+template <typename T>
+int launch_route_hist(const T *logits, int tokens, int E, int top_k, int renormalize, int32_t *ids, float *wts,
+                      const Plan &p, int *counts, int32_t *sorted, int max_padded, cudaStream_t stream) {
+    const int tokens_per_cta = kWarpsPerCta * p.seg / top_k;
+    const size_t smem = static_cast<size_t>(E) * sizeof(int);
+    const int per = (E + 31) / 32;
+#define PMOE_ROUTE_HIST_CASE(P)                                                                                      \
+    if (per <= P) {                                                                                                  \
+        route_hist_kernel<T, P><<<p.ctas, 1024, smem, stream>>>(logits, tokens, E, top_k, renormalize, ids, wts,     \
+                                                               tokens_per_cta, counts, sorted, max_padded);         \
+        PMOE_CUDA_OK(cudaGetLastError());                                                                            \
+        return PMOE_OK;                                                                                              \
+    }
+    PMOE_ROUTE_HIST_CASE(1)
+    PMOE_ROUTE_HIST_CASE(2)
+    PMOE_ROUTE_HIST_CASE(4)
+    PMOE_ROUTE_HIST_CASE(8)
+    PMOE_ROUTE_HIST_CASE(16)
+    PMOE_ROUTE_HIST_CASE(32)
+#undef PMOE_ROUTE_HIST_CASE
+    return set_error(PMOE_ERR_UNSUPPORTED, "route_topk_align supports at most 1024 experts, got %d", E);
+}
+
+}  // namespace
+}  // namespace pmoe
+
+extern "C" int pmoe_route_topk_align(const void *logits, int logits_dtype, int T, int num_experts, int top_k,
+                                     int renormalize, int32_t *topk_ids, float *topk_weights,
+                                     int32_t *sorted_token_ids, int32_t *expert_ids, int32_t *num_tokens_post_padded,
+                                     int block_m, int pad_to, int max_padded, int max_blocks, void *workspace,
+                                     size_t workspace_bytes, pmoe_stream_t stream) {
+    using namespace pmoe;
+    PMOE_REQUIRE(T >= 0 && top_k > 0 && static_cast<long long>(T) * top_k < (1ll << 31), PMOE_ERR_BAD_ARG,
+                 "route_topk_align: T >= 0, top_k > 0 and T * top_k < 2^31 required");
+    const int n = T * top_k;
+    if (int rc = check_args(topk_ids, sorted_token_ids, expert_ids, num_tokens_post_padded, n, num_experts, block_m,
+                            pad_to, max_padded, max_blocks))
+        return rc;
+    const Plan p = make_plan(n, num_experts);
+    PMOE_REQUIRE(p.ws_ints == 0 || (workspace && workspace_bytes >= p.ws_ints * sizeof(int)), PMOE_ERR_BAD_ARG,
+                 "route_topk_align: workspace of %zu bytes required, got %zu", p.ws_ints * sizeof(int), workspace_bytes);
+    const bool fused = p.ctas > 0 && (kWarpsPerCta * p.seg) % top_k == 0 && logits && topk_weights && top_k <= 32 &&
+                       top_k <= num_experts && num_experts <= kMaxExperts &&
+                       (logits_dtype == PMOE_DTYPE_F32 || logits_dtype == PMOE_DTYPE_BF16);
+    if (!fused) {   // small problems (one CTA aligns them) and top_k that does not divide a CTA's id range
+        if (int rc = pmoe_route_topk(logits, logits_dtype, T, num_experts, top_k, renormalize, topk_ids, topk_weights,
+                                     stream))
+            return rc;
+        return launch(topk_ids, sorted_token_ids, expert_ids, num_tokens_post_padded, n, num_experts, block_m, pad_to,
+                      max_padded, max_blocks, p, static_cast<int *>(workspace), stream);
+    }
+    int *counts = static_cast<int *>(workspace);
+    int rc = logits_dtype == PMOE_DTYPE_F32
+                 ? launch_route_hist(static_cast<const float *>(logits), T, num_experts, top_k, renormalize ? 1 : 0,
+                                     topk_ids, topk_weights, p, counts, sorted_token_ids, max_padded, stream)
+                 : launch_route_hist(static_cast<const __nv_bfloat16 *>(logits), T, num_experts, top_k,
+                                     renormalize ? 1 : 0, topk_ids, topk_weights, p, counts, sorted_token_ids,
+                                     max_padded, stream);
+    if (rc) return rc;
+    const size_t smem_s = (static_cast<size_t>(kWarpsPerCta) * num_experts + 3 * static_cast<size_t>(num_experts) + 1 +
+                           kWarpsPerCta) * sizeof(int);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_s;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_align_scatter_kernel, static_cast<const int32_t *>(topk_ids), n, num_experts,
+                                    p.seg, static_cast<const int *>(counts), block_m, pad_to, sorted_token_ids, expert_ids,
+                                    num_tokens_post_padded, max_padded, max_blocks, 1));
+    return PMOE_OK;
+}
 
 extern "C" size_t pmoe_moe_align_workspace_bytes(int n, int num_experts) {
     if (n < 0 || num_experts <= 0) return 0;

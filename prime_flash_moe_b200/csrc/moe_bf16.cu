@@ -1751,7 +1751,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
             if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128),
                                      ACT_TILE_BYTES, up.use_pdl ? 2 : 1))
                 return rc;
-            if (tails) {   // plain launch: starts when the pair kernel (which zeroes `out`) has finished
+            if (tails && !(phases & 8)) {   // plain launch: starts when the pair kernel (which zeroes `out`) has finished
                 Args tu = ta;
                 tu.use_pdl = 0;
                 if (int rc = launch_single(moe_up_bf16_kernel, tu, (max_blocks / 2) * (H / 128),
@@ -1769,7 +1769,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
                                      (max_blocks / 2) * ((p.K + 255) / 256), bulk_reduce ? RED_STAGE_BYTES : 0u,
                                      dn.use_pdl ? 2 : 1))
                 return rc;
-            if (tails) {
+            if (tails && !(phases & 8)) {
                 Args td = ta;
                 td.use_pdl = 0;
                 td.down_ksplit = 1;

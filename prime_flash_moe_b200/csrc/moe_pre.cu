@@ -18,6 +18,7 @@
 #include <algorithm>
 
 #include "host_common.h"
+#include "route_warp.cuh"
 
 namespace pmoe {
 namespace {
@@ -27,15 +28,6 @@ namespace {
 // ---------------------------------------------------------------------------------------------
 constexpr int kRouteWarps = 8;
 
-template <typename T>
-__device__ __forceinline__ float load_logit(const T *p);
-template <>
-__device__ __forceinline__ float load_logit<float>(const float *p) { return __ldg(p); }
-template <>
-__device__ __forceinline__ float load_logit<__nv_bfloat16>(const __nv_bfloat16 *p) {
-    return __bfloat162float(*p);
-}
-
 // PER = ceil(E / 32) rounded up to a power of two (1..32): registers per lane
 template <typename T, int PER>
 __global__ void __launch_bounds__(kRouteWarps * 32)
@@ -44,64 +36,12 @@ route_topk_kernel(const T *__restrict__ logits, int tokens, int E, int top_k, in
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * kRouteWarps + (threadIdx.x >> 5);
     if (t >= tokens) return;
-    const T *row = logits + static_cast<size_t>(t) * E;
-    float v[PER];
-    float m = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int e = lane + 32 * i;
-        v[i] = e < E ? load_logit<T>(row + e) : -INFINITY;
-        m = fmaxf(m, v[i]);
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-    float sum = 0.f;
-    if (!renormalize) {
-#pragma unroll
-        for (int i = 0; i < PER; ++i) sum += (lane + 32 * i < E) ? expf(v[i] - m) : 0.f;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-    }
-    // top_k rounds of arg-max; ties go to the lower expert index; taken entries drop to -inf
-    float my_val = 0.f;   // lane j keeps the j-th selected logit and index
-    int my_idx = 0;
-    for (int j = 0; j < top_k; ++j) {
-        float best = -INFINITY;
-        int best_e = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int e = lane + 32 * i;
-            if (e < E && (v[i] > best || (v[i] == best && e < best_e))) {
-                best = v[i];
-                best_e = e;
-            }
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, d);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, d);
-            if (ob > best || (ob == best && oe < best_e)) {
-                best = ob;
-                best_e = oe;
-            }
-        }
-        if (lane == j) {
-            my_val = best;
-            my_idx = best_e;
-        }
-#pragma unroll
-        for (int i = 0; i < PER; ++i)
-            if (lane + 32 * i == best_e) v[i] = -INFINITY;
-    }
-    float p = lane < top_k ? expf(my_val - m) : 0.f;
-    if (renormalize) {
-        sum = p;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-    }
+    int idx;
+    float w;
+    route_token_warp<T, PER>(logits + static_cast<size_t>(t) * E, E, top_k, renormalize, lane, idx, w);
     if (lane < top_k) {
-        topk_ids[static_cast<size_t>(t) * top_k + lane] = my_idx;
-        topk_weights[static_cast<size_t>(t) * top_k + lane] = p / sum;
+        topk_ids[static_cast<size_t>(t) * top_k + lane] = idx;
+        topk_weights[static_cast<size_t>(t) * top_k + lane] = w;
     }
 }
 
@@ -136,44 +76,66 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
     return lo | (hi << 16);
 }
 
+// one 8-element chunk: amax over the block's four lanes, exponent, e4m3 conversion
+__device__ __forceinline__ void quantize_chunk(const uint4 raw, uint2 *o, int *e_out) {
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __low2float(h[j]);
+        v[2 * j + 1] = __high2float(h[j]);
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
+    e = max(0, min(e, 254));
+    const uint32_t field = static_cast<uint32_t>(254 - e);
+    const float inv = __uint_as_float(field ? field << 23 : 0x00400000u);   // 2^(127-e); 2^-127 is subnormal
+    o->x = e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+    o->y = e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+    *e_out = e;
+}
+
+constexpr int kQuantUnroll = 4;   // independent 16-byte loads in flight per thread
+
 __global__ void __launch_bounds__(256)
 quantize_mx_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__restrict__ row_index, int src_rows,
                    uint8_t *__restrict__ q, uint8_t *__restrict__ scales, int rows, int K) {
     const int chunks = K / 8;                 // 16-byte chunks per row
     const long long total = static_cast<long long>(rows) * chunks;
-    // the trip count is uniform per warp (the shuffles below need all 32 lanes); lanes past the end idle
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    // the trip count is uniform per warp (the shuffles need all 32 lanes); lanes past the end idle. chunks is a
+    // multiple of 4, so the four lanes of a block always sit in one row and one iteration.
     for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + (threadIdx.x & ~31u); i0 < total;
-         i0 += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long i = min(i0 + (threadIdx.x & 31), total - 1);
-        const bool active = i0 + (threadIdx.x & 31) < total;
-        // chunks is a multiple of 4, so the four lanes of a block always sit in one row and one iteration
-        const int r = static_cast<int>(i / chunks), c = static_cast<int>(i - static_cast<long long>(r) * chunks);
-        int src = row_index ? row_index[r] : r;
-        const bool live = src >= 0 && src < src_rows;   // rows with an index outside x are written as zeros
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (live) raw = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(src) * K) + c);
-        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
-        float v[8];
+         i0 += kQuantUnroll * stride) {
+        uint4 raw[kQuantUnroll];
+        int r[kQuantUnroll], c[kQuantUnroll];
+        bool active[kQuantUnroll];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            v[2 * j] = __low2float(h[j]);
-            v[2 * j + 1] = __high2float(h[j]);
+        for (int u = 0; u < kQuantUnroll; ++u) {
+            const long long w0 = i0 + u * stride;               // this warp's first chunk of the u-th batch
+            const long long i = min(w0 + (threadIdx.x & 31), total - 1);
+            active[u] = w0 + (threadIdx.x & 31) < total;
+            r[u] = static_cast<int>(i / chunks);
+            c[u] = static_cast<int>(i - static_cast<long long>(r[u]) * chunks);
+            const int src = row_index ? row_index[r[u]] : r[u];
+            const bool live = src >= 0 && src < src_rows;       // rows with an index outside x are written as zeros
+            raw[u] = make_uint4(0, 0, 0, 0);
+            if (live && w0 < total) raw[u] = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(src) * K) + c[u]);
         }
-        float amax = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
-        e = max(0, min(e, 254));
-        const uint32_t field = static_cast<uint32_t>(254 - e);
-        const float inv = __uint_as_float(field ? field << 23 : 0x00400000u);   // 2^(127-e); 2^-127 is subnormal
-        uint2 o;
-        o.x = e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-        o.y = e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-        if (!active) continue;
-        reinterpret_cast<uint2 *>(q + static_cast<size_t>(r) * K)[c] = o;
-        if ((c & 3) == 0) scales[static_cast<size_t>(r) * (K / 32) + (c >> 2)] = static_cast<uint8_t>(e);
+        for (int u = 0; u < kQuantUnroll; ++u) {
+            if (i0 + u * stride >= total) break;                // uniform per warp
+            uint2 o;
+            int e;
+            quantize_chunk(raw[u], &o, &e);
+            if (!active[u]) continue;
+            reinterpret_cast<uint2 *>(q + static_cast<size_t>(r[u]) * K)[c[u]] = o;
+            if ((c[u] & 3) == 0) scales[static_cast<size_t>(r[u]) * (K / 32) + (c[u] >> 2)] = static_cast<uint8_t>(e);
+        }
     }
 }
 

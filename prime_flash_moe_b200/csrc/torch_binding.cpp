@@ -245,6 +245,34 @@ std::tuple<torch::Tensor, torch::Tensor> route_topk(const torch::Tensor &logits,
     return {ids, wts};
 }
 
+// router + moe_align in one call (pmoe_route_topk_align): (topk_ids, topk_weights, sorted_token_ids, expert_ids,
+// num_tokens_post_padded); the last three exactly as prime_moe::moe_align would return them for topk_ids
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> route_topk_align(
+    const torch::Tensor &logits, int64_t top_k, bool renormalize, int64_t block_m, int64_t bpc) {
+    at::cuda::OptionalCUDAGuard guard{device_of(logits)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous(), "logits must be a contiguous [T, E] tensor");
+    TORCH_CHECK(logits.dtype() == torch::kFloat32 || logits.dtype() == torch::kBFloat16,
+                "logits must be fp32 or bf16");
+    TORCH_CHECK(block_m > 0 && bpc > 0 && top_k > 0);
+    const int64_t T = logits.size(0), E = logits.size(1), n = T * top_k, pad_to = block_m * bpc;
+    const int64_t max_padded = (n + E * (pad_to - 1) + pad_to - 1) / pad_to * pad_to;
+    auto i32 = logits.options().dtype(torch::kInt32);
+    torch::Tensor ids = torch::empty({T, top_k}, i32), wts = torch::empty({T, top_k}, logits.options().dtype(torch::kFloat32));
+    torch::Tensor sorted = torch::empty({max_padded}, i32), experts = torch::empty({max_padded / block_m}, i32);
+    torch::Tensor npp = torch::empty({1}, i32);
+    const size_t ws_bytes = pmoe_moe_align_workspace_bytes(static_cast<int>(n), static_cast<int>(E));
+    torch::Tensor ws = torch::empty({static_cast<int64_t>(ws_bytes) + 16}, logits.options().dtype(torch::kUInt8));
+    check_status(pmoe_route_topk_align(
+        logits.const_data_ptr(), logits.dtype() == torch::kFloat32 ? PMOE_DTYPE_F32 : PMOE_DTYPE_BF16, static_cast<int>(T),
+        static_cast<int>(E), static_cast<int>(top_k), renormalize ? 1 : 0, static_cast<int32_t *>(ids.data_ptr()),
+        static_cast<float *>(wts.data_ptr()), static_cast<int32_t *>(sorted.data_ptr()),
+        static_cast<int32_t *>(experts.data_ptr()), static_cast<int32_t *>(npp.data_ptr()), static_cast<int>(block_m),
+        static_cast<int>(pad_to), static_cast<int>(max_padded), static_cast<int>(max_padded / block_m), ws.data_ptr(),
+        ws_bytes, stream));
+    return {ids, wts, sorted, experts, npp};
+}
+
 // activation quantiser (not in the reference: README.md:110-113 leaves it to the caller): bf16 [T, K] ->
 // (e4m3 [R, K], e8m0 [R, K/32]); with row_index int32 [R] output row r is x[row_index[r]], see pmoe_quantize_mx
 std::tuple<torch::Tensor, torch::Tensor> quantize_mx(const torch::Tensor &x,
@@ -275,6 +303,9 @@ std::tuple<torch::Tensor, torch::Tensor> quantize_mx(const torch::Tensor &x,
 TORCH_LIBRARY_FRAGMENT(prime_moe, m) {
     m.def("route_topk(Tensor logits, int top_k, bool renormalize=True) -> (Tensor, Tensor)");
     m.impl("route_topk", torch::kCUDA, &route_topk);
+    m.def("route_topk_align(Tensor logits, int top_k, bool renormalize=True, int block_m=128, int bpc=1) -> "
+          "(Tensor, Tensor, Tensor, Tensor, Tensor)");
+    m.impl("route_topk_align", torch::kCUDA, &route_topk_align);
     m.def("quantize_mx(Tensor x, Tensor? row_index=None) -> (Tensor, Tensor)");
     m.impl("quantize_mx", torch::kCUDA, &quantize_mx);
     m.def("ep_plan(Tensor topk_ids, Tensor topk_weights, int num_experts, int world) -> (Tensor, Tensor, Tensor, Tensor)");

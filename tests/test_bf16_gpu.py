@@ -294,3 +294,43 @@ def test_dual_block_tiles(T, K, E, N, k, bn, wn, stages, agather, monkeypatch):
     assert O.max_rel_to_peak(dual, ref) <= TOL
     assert O.max_rel_to_peak(one, ref) <= TOL
     assert O.max_rel_to_peak(dual, one.float()) <= TOL
+
+
+@pytest.mark.parametrize("bpc", [1, 2])
+def test_ex_entry_point_live_rows_and_output_addresses(bpc):
+    """`pmoe_fused_moe_bf16_ex` (the expert-parallel mode's entry point). live_rows: buffers sized for a worst case,
+    only the leading rows in use - the library zeroes just those rows of `out`. out_rows: every output row has its
+    own address (here rows of a second buffer in permuted order; across GPUs: rows of the source rank's buffer) and
+    the down kernels ADD their results there, zeroing nothing."""
+    from prime_flash_moe_b200 import capi
+    T, cap, K, E, N, k = 300, 512, 512, 4, 512, 2
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=77)
+    ref = O.moe_ref_fp32(x, w1, w2, ids, wts)
+    xd = torch.full((cap, K), float("nan"), dtype=torch.bfloat16, device=DEV)      # rows beyond T are never read
+    xd[:T] = x.to(DEV)
+    idd = torch.full((cap, k), -1, dtype=torch.int32, device=DEV)
+    idd[:T] = ids.to(DEV)
+    wd = torch.zeros(cap, k, dtype=torch.float32, device=DEV)
+    wd[:T] = wts.to(DEV)
+    live = torch.tensor([T], dtype=torch.int32, device=DEV)
+    s, e, n = capi.moe_align(idd, E, 128, bpc)
+    out = torch.full((cap, K), float("nan"), dtype=torch.bfloat16, device=DEV)
+    capi.fused_moe_bf16(xd, w1.to(DEV), w2.to(DEV), s, e, n, wd.view(-1), out, k, 128, 64, 4, 4, bpc, 1, True, live_rows=live)
+    torch.cuda.synchronize()
+    assert O.max_rel_to_peak(out[:T].cpu(), ref) <= TOL
+    assert torch.isnan(out[T:].float()).all(), "rows beyond live_rows must be left alone"
+    # every output row at its own address: row i of the result lands in row perm[i] of `y`
+    perm = torch.randperm(cap, generator=torch.Generator().manual_seed(3))
+    y = torch.zeros(cap, K, dtype=torch.bfloat16, device=DEV)
+    table = (y.data_ptr() + perm.to(torch.int64) * K * 2).to(DEV)
+    out.fill_(float("nan"))
+    capi.fused_moe_bf16(xd, w1.to(DEV), w2.to(DEV), s, e, n, wd.view(-1), out, k, 128, 64, 4, 4, bpc, 1, True, live_rows=live,
+                        out_rows=table)
+    torch.cuda.synchronize()
+    assert torch.isnan(out.float()).all(), "`out` itself is not written when out_rows is given"
+    assert O.max_rel_to_peak(y[perm[:T].to(DEV)].cpu(), ref) <= TOL
+    assert float(y[perm[T:].to(DEV)].float().abs().max()) == 0.0
+    assert capi.device_status() == 0
+    with pytest.raises(RuntimeError):      # a split=False call cannot address rows individually
+        capi.fused_moe_bf16(xd, w1.to(DEV), w2.to(DEV), s, e, n, wd.view(-1), out, k, 128, 64, 4, 4, 1, 1, False,
+                            out_rows=table)

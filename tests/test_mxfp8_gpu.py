@@ -217,3 +217,32 @@ def test_short_row_blocks(T, K, E, N, k, monkeypatch):
     # same arithmetic per routed row; the top_k bf16 reductions into an output element land in a different order
     # from run to run (with top_k = 8 two orders differ by up to ~1.3e-2 of the peak)
     assert O.max_rel_to_peak(short, full.float()) <= TOL
+
+
+def test_ex_entry_point_live_rows():
+    """`pmoe_fused_moe_mxfp8_ex`: worst-case sized buffers with only the leading `live_rows` rows in use; rows beyond
+    are neither read for a result nor zeroed."""
+    import prime_flash_moe_b200 as P
+    from prime_flash_moe_b200 import capi
+    T, cap, K, E, N, k = 200, 384, 512, 4, 512, 2
+    q, deq, ids, wts = quantised_case(T, K, E, N, k, seed=55)
+    ref = O.moe_ref_fp32(deq["x"], deq["w1"], deq["w2"], ids, wts, requant_act=True)
+    (xq, xs), (w1q, w1s), (w2q, w2s) = q["x"], q["w1"], q["w2"]
+    xd = torch.zeros(cap, K, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    xd[:T] = xq.to(DEV)
+    sd = torch.zeros(cap, K // 32, dtype=torch.uint8, device=DEV).view(torch.float8_e8m0fnu)
+    sd[:T] = xs.to(DEV)
+    idd = torch.full((cap, k), -1, dtype=torch.int32, device=DEV)
+    idd[:T] = ids.to(DEV)
+    wd = torch.zeros(cap, k, dtype=torch.float32, device=DEV)
+    wd[:T] = wts.to(DEV)
+    live = torch.tensor([T], dtype=torch.int32, device=DEV)
+    s, e, n = capi.moe_align(idd, E, 128, 1)
+    out = torch.full((cap, K), float("nan"), dtype=torch.bfloat16, device=DEV)
+    capi.fused_moe_mxfp8(xd, sd, w1q.to(DEV), P.pack_scales_blocked(w1s).to(DEV), w2q.to(DEV),
+                         P.pack_scales_blocked(w2s).to(DEV), s, e, n, wd.view(-1), out, k, 128, 64, 4, 4, 1, True,
+                         live_rows=live)
+    torch.cuda.synchronize()
+    assert O.max_rel_to_peak(out[:T].cpu(), ref) <= TOL
+    assert torch.isnan(out[T:].float()).all()
+    assert capi.device_status() == 0

@@ -149,6 +149,44 @@ def test_route_then_align_then_moe():
     assert O.max_rel_to_peak(out.cpu(), ref) <= 2e-2
 
 
+@pytest.mark.parametrize("via", ["capi", "torch"])
+@pytest.mark.parametrize("T,E,k,bpc,dtype", [
+    (64, 8, 2, 1, torch.float32),            # one CTA aligns it: router kernel + small align kernel
+    (4096, 8, 2, 2, torch.float32),          # n = 8192, E <= 256: still one CTA
+    (8192, 128, 8, 1, torch.float32),        # fused router + histogram kernel, then the scatter pass
+    (16384, 256, 8, 1, torch.bfloat16),
+    (20000, 64, 4, 2, torch.float32),
+    (9000, 100, 5, 1, torch.float32),        # top_k = 5 does not divide a CTA's id range: the separate kernels
+    (3000, 1024, 8, 1, torch.float32),
+])
+def test_route_topk_align_equals_the_two_separate_calls(T, E, k, bpc, dtype, via):
+    """Router fused with the moe_align histogram pass: all five outputs identical, bit for bit, to route_topk
+    followed by moe_align on its ids - and the routing tables to the CPU restatement of the reference's."""
+    import numpy as np
+    import prime_flash_moe_b200 as P
+    from prime_flash_moe_b200 import capi
+    g = torch.Generator().manual_seed(T + E)
+    if dtype == torch.bfloat16:
+        base = (0x3C00 + torch.arange(E, dtype=torch.int32)).to(torch.int16).view(torch.bfloat16)
+        logits = torch.stack([base[torch.randperm(E, generator=g)] for _ in range(T)])
+    else:
+        logits = torch.randn(T, E, generator=g)
+    ld = logits.to(DEV)
+    if via == "capi":
+        ids, wts, s, e, n = capi.route_topk_align(ld, k, True, 128, bpc)
+    else:
+        ids, wts, s, e, n = P.route_topk_align(ld, k, True, 128, bpc)
+    ids2, wts2 = capi.route_topk(ld, k, True)
+    s2, e2, n2 = capi.moe_align(ids2, E, 128, bpc)
+    torch.cuda.synchronize()
+    assert torch.equal(ids, ids2) and torch.equal(wts, wts2)
+    assert torch.equal(s, s2) and torch.equal(e, e2) and torch.equal(n, n2)
+    want = O.moe_align_spec(ids.cpu().numpy(), E, 128, bpc)
+    for got, ref in zip((s, e, n), want):
+        assert np.array_equal(got.cpu().numpy(), ref)
+    assert capi.device_status() == 0
+
+
 def test_argument_checks():
     from prime_flash_moe_b200 import capi
     lib = capi.lib()
