@@ -52,6 +52,8 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SF_TMEM_BASE = 256;           // columns [256, 384): eight 16-column scale regions
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr int GATHER_THREADS = 128;             // optional LSU gather warps of the gate/up kernel
+constexpr int UP_MAX_THREADS = THREADS + GATHER_THREADS;
 constexpr uint32_t BAR_BYTES = 256;
 constexpr uint32_t RED_ROW_BYTES = 256 + 16;              // down epilogue staging: 128 bf16 per thread, padded
 constexpr uint32_t RED_STAGE_BYTES = EPI_WARPS * 32 * RED_ROW_BYTES;
@@ -75,6 +77,9 @@ struct Args {
     int use_pdl;
     int bulk_reduce;   // down kernel: reduce into `out` with cp.reduce.async.bulk from a staging tile
     const int32_t *live_rows;   // optional: rows of `out` in use (only those are zeroed)
+    const uint8_t *x;           // gate/up kernel with the in-kernel row gather: e4m3 activations [M, K] ...
+    const uint8_t *x_scales;    // ... and their row-major e8m0 scales [M, K/32]
+    int lsu_gather;             // gate/up kernel: A rows and A scale tiles gathered from x by four extra warps
     int short_boxes;   // split kernels: row blocks with <= SHORT_ROWS routed rows move only those rows of the A
                        // operand and of the activation tile (the rest of a 128-row block is padding)
 };
@@ -203,7 +208,7 @@ gather_rows_mxfp8_kernel(const uint8_t *__restrict__ x, const uint8_t *__restric
 // ---------------------------------------------------------------------------------------------
 // up kernel (split): misc barriers 0 tmem_full | 1 tmem_empty | 2 staged | 3 stage_free
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(UP_MAX_THREADS, 1)
 moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                     const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_x_short,
                     const __grid_constant__ CUtensorMap map_act_short, const Args a) {
@@ -215,7 +220,7 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
-            mbar_init(sm.full(s), 1);
+            mbar_init(sm.full(s), a.lsu_gather ? 1 + GATHER_THREADS : 1);
             mbar_init(sm.empty(s), 1);
         }
         mbar_init(sm.misc(0), 1);
@@ -260,15 +265,19 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const uint8_t *sf_gate = a.w_scales + static_cast<size_t>(row_gate >> 7) * ksteps * SF_TILE;
                 const uint8_t *sf_up = a.w_scales + static_cast<size_t>(row_up >> 7) * ksteps * SF_TILE;
                 const uint8_t *sf_x = a.xsf_tiles + static_cast<size_t>(c.m_blk) * ksteps * SF_TILE;
-                const bool short_a = block_is_short(a, c.m_blk);
+                const bool short_a = !a.lsu_gather && block_is_short(a, c.m_blk);
                 for (int ks = 0; ks < ksteps; ++ks) {
                     ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(sm.full(s), short_a ? STAGE_TX_BYTES - A_BYTES + SHORT_A_BYTES : STAGE_TX_BYTES);
-                    tma_load_2d(sm.a(s), short_a ? &map_x_short : &map_x, sm.full(s), ks * BKB, c.m_blk * BM);
+                    if (a.lsu_gather) {   // the A tile and its scale tile come from the gather warps
+                        mbar_arrive_expect_tx(sm.full(s), B_BYTES + 2 * SF_TILE);
+                    } else {
+                        mbar_arrive_expect_tx(sm.full(s), short_a ? STAGE_TX_BYTES - A_BYTES + SHORT_A_BYTES : STAGE_TX_BYTES);
+                        tma_load_2d(sm.a(s), short_a ? &map_x_short : &map_x, sm.full(s), ks * BKB, c.m_blk * BM);
+                        bulk_load_1d(sm.sfa(s), sf_x + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
+                    }
                     tma_load_2d(sm.b(s), &map_w1, sm.full(s), ks * BKB, row_gate);
                     tma_load_2d(sm.b(s) + B_BYTES / 2, &map_w1, sm.full(s), ks * BKB, row_up);
-                    bulk_load_1d(sm.sfa(s), sf_x + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
                     bulk_load_1d(sm.sfb(s), sf_gate + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
                     bulk_load_1d(sm.sfb(s) + SF_TILE, sf_up + static_cast<size_t>(ks) * SF_TILE, SF_TILE, sm.full(s));
                     ++issued;
@@ -309,6 +318,65 @@ moe_up_mxfp8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
         }
         __syncwarp();
+    } else if (warp >= 2 + EPI_WARPS) {
+        // ---------------- LSU gather warps: A rows and the A scale tile straight from x / x_scales ----------------
+        // As in the bf16 gate/up kernel: 8 consecutive lanes copy the eight 16-byte chunks of one 128-byte row segment
+        // (thread g serves rows (g>>3) + 16*i) into the 128-byte-swizzled tile; in addition thread g copies the four
+        // scale bytes of row g for this k-step into the 512-byte scale tile (byte (r%32)*16 + (r/32)*4 + kb). cp.async
+        // writes through the generic proxy, tcgen05.mma / tcgen05.cp read through the async proxy: each thread waits
+        // for its own copies of a slot (lagging behind the slots it is issuing), fences, then arrives on `full`.
+        const int g = threadIdx.x - 64 - epi_threads;
+        const int q = g >> 3, chunk = g & 7;
+        const int lag = min(2, a.stages - 1);
+        const int kblocks = a.K / 32;
+        int s = 0, s_done = 0;
+        uint32_t ph = 0;
+        long long issued = 0, arrived = 0;
+        auto publish = [&](int pending_allowed) {
+            if (pending_allowed >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else if (pending_allowed == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;" ::: "memory");
+            fence_proxy_async_smem();
+            while (arrived < issued - pending_allowed) {
+                mbar_arrive(sm.full(s_done));
+                if (++s_done == a.stages) s_done = 0;
+                ++arrived;
+            }
+        };
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const Coord c = tile_coord(t, m_blocks, n_tiles);
+            const uint8_t *src[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int pair = a.sorted_ids[c.m_blk * BM + q + 16 * i];
+                int tok = pair >= 0 ? pair / a.top_k : 0;     // padding rows read token 0; their result is dropped
+                if (tok >= a.M) tok = 0;
+                src[i] = a.x + static_cast<size_t>(tok) * a.K + chunk * 16;
+            }
+            const int pair_g = a.sorted_ids[c.m_blk * BM + g];
+            int tok_g = pair_g >= 0 ? pair_g / a.top_k : 0;
+            if (tok_g >= a.M) tok_g = 0;
+            const uint8_t *ssrc = a.x_scales + static_cast<size_t>(tok_g) * kblocks;
+            const uint32_t sdst = (g & 31) * 16 + (g >> 5) * 4;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                if (!ok) break;
+                const uint32_t dst = sm.a(s) + q * 128 + ((chunk ^ (q & 7)) << 4);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) cp_async_16(dst + i * 16 * 128, src[i] + ks * BKB);
+                cp_async_4(sm.sfa(s) + sdst, ssrc + ks * 4);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                ++issued;
+                if (++s == a.stages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+                if (issued - arrived > lag) publish(lag);
+            }
+        }
+        publish(0);
+        cp_async_wait_all();
     } else {
         const int ew = warp - 2;
         const int et = threadIdx.x - 64;
@@ -1191,7 +1259,14 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
         return rc;
     a.short_boxes = short_boxes_mode();
 
-    if (phases & 1) {
+    // In-kernel row gather for the one-CTA gate/up kernel (PMOE_AGATHER=lsu): the pre-pass (routed rows written and
+    // read again, scale rows re-tiled) disappears, but unlike bf16 it does not pay here - the gate/up kernel gets
+    // 10-18 % slower with the four gather warps beside its eight epilogue warps (c2 T=8192 247 -> 292 us, c3 4.82 ->
+    // 5.30 ms, c4 6.72 -> 7.94 ms), more than the pre-pass costs (37 us, 0.34 ms, 0.82 ms) except on c3 (-1 %). So the
+    // pre-pass stays the default and the gather an option.
+    const int a_mode = a_operand_mode();
+    const bool lsu = p.split && p.bpc == 1 && a_mode == 2 && (reinterpret_cast<uintptr_t>(p.x_scales) & 3) == 0;
+    if ((phases & 1) && !lsu) {
         gather_rows_mxfp8_kernel<<<std::min(4 * sms, (p.sorted_num + 7) / 8), 256, 0, stream>>>(
             static_cast<const uint8_t *>(p.x), static_cast<const uint8_t *>(p.x_scales), x_sorted, xsf, a);
         PMOE_CUDA_OK(cudaGetLastError());
@@ -1308,13 +1383,16 @@ int run(const Problem &p, void *workspace, cudaStream_t stream) {
     if (phases & 2) {
         Args up = a;
         up.zero_out = 1;
+        up.lsu_gather = lsu ? 1 : 0;
+        up.x = static_cast<const uint8_t *>(p.x);
+        up.x_scales = static_cast<const uint8_t *>(p.x_scales);
         const size_t smem = smem_bytes(up.stages, ACT_EXTRA);
         if (int rc = set_smem(moe_up_mxfp8_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
-        up.use_pdl = (pdl_enabled() && (phases & 1)) ? 1 : 0;
+        up.use_pdl = (pdl_enabled() && (phases & 1) && !lsu) ? 1 : 0;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(std::min(tiles, sms));
-        cfg.blockDim = dim3(THREADS);
+        cfg.blockDim = dim3(lsu ? UP_MAX_THREADS : THREADS);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];

@@ -99,7 +99,7 @@ __device__ __forceinline__ void quantize_chunk(const uint4 raw, uint2 *o, int *e
     *e_out = e;
 }
 
-constexpr int kQuantUnroll = 4;   // independent 16-byte loads in flight per thread
+constexpr int kQuantUnroll = 2;   // independent 16-byte loads in flight per thread
 
 __global__ void __launch_bounds__(256)
 quantize_mx_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__restrict__ row_index, int src_rows,

@@ -246,3 +246,23 @@ def test_ex_entry_point_live_rows():
     assert O.max_rel_to_peak(out[:T].cpu(), ref) <= TOL
     assert torch.isnan(out[T:].float()).all()
     assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("stages", [1, 2, 4])
+@pytest.mark.parametrize("T,K,E,N,k", [(8, 256, 1, 256, 1), (300, 512, 4, 512, 2), (256, 4096, 8, 512, 4),
+                                        (1000, 1024, 16, 768, 8), (700, 256, 3, 1024, 1), (2048, 2048, 32, 2048, 4)])
+def test_in_kernel_row_gather(T, K, E, N, k, stages, monkeypatch):
+    """Gate/up kernel with the routed rows of x and their scale rows gathered inside the kernel (four LSU warps,
+    PMOE_AGATHER=lsu; an option, the pre-pass measured faster) against the row-gather pre-pass (PMOE_AGATHER=pre): the
+    same arithmetic per routed row, so both meet the oracle bound and differ from one another only by the order of
+    the bf16 reductions into `out`."""
+    q, deq, ids, wts = quantised_case(T, K, E, N, k, seed=T + stages)
+    ref = O.moe_ref_fp32(deq["x"], deq["w1"], deq["w2"], ids, wts, requant_act=True)
+    monkeypatch.setenv("PMOE_AGATHER", "lsu")
+    lsu, _ = run_mine(q, ids, wts, True, stages=stages)
+    monkeypatch.setenv("PMOE_AGATHER", "pre")
+    pre, _ = run_mine(q, ids, wts, True, stages=stages)
+    assert torch.isfinite(lsu.float()).all()
+    assert O.max_rel_to_peak(lsu, ref) <= TOL
+    assert O.max_rel_to_peak(pre, ref) <= TOL
+    assert O.max_rel_to_peak(lsu, pre.float()) <= TOL
