@@ -155,6 +155,25 @@ def dist_setup(args):
     return world, rank, local
 
 
+def bind_to_gpu_numa_node(index: int):
+    """Multi-rank runs: keep this process (and the pinned host buffers it allocates afterwards) on the CPUs NVML
+    reports as local to its GPU, so that eight ranks copying through host memory do not all cross the socket link.
+    Reads the affinity mask only; any failure (no NVML, CPUs outside the container's cpuset) leaves things as they are."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def barrier_sync(world):
     import torch
     if world > 1:
@@ -688,6 +707,8 @@ def run_gpu_arm(args, impl):
         return                     # the reference arm is single-GPU: rank 0 alone runs and prints
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    if world > 1:
+        bind_to_gpu_numa_node(local)
     cfg = list(CONFIGS[args.config])
     if args.tokens:
         cfg[0] = args.tokens

@@ -180,8 +180,8 @@ int pmoe_fused_moe_mxfp8_ws(const void *x, const void *x_scales, const void *w, 
  *   32 elements: e = clamp(exponent(amax) - 8, 0, 254), q = satfinite_e4m3(v * 2^(127 - e))), the layout
  *   pmoe_fused_moe_mxfp8 takes as x / x_scales. row_index == NULL: output row r is x[r] (rows <= src_rows).
  *   row_index int32[rows]: output row r is x[row_index[r]] - the expert-parallel dispatch gather and the
- *   quantiser in one pass; an index outside [0, src_rows) yields a row of zeros. K % 32 == 0; x 16-byte and
- *   q 8-byte aligned. */
+ *   quantiser in one pass; an index outside [0, src_rows) yields a row of zeros. K % 32 == 0; x and q 16-byte
+ *   aligned. */
 enum { PMOE_DTYPE_F32 = 0, PMOE_DTYPE_BF16 = 1 };
 int pmoe_route_topk(const void *logits, int logits_dtype, int T, int num_experts, int top_k, int renormalize,
                     int32_t *topk_ids, float *topk_weights, pmoe_stream_t stream);

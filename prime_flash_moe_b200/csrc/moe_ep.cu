@@ -318,6 +318,7 @@ __global__ void __launch_bounds__(256)
 ep_push_rows_kernel(const PushArgs a) {
     __shared__ int s_send_base[kMaxRanks + 1];   // first visit of mine to rank g
     __shared__ int s_dst_base[kMaxRanks];        // first row of mine in rank g's areas
+    __shared__ int s_most;                       // largest number of visits to one rank
     const Header *h = static_cast<const Header *>(a.peers[a.me]);
     wait_flags(h->cnt_flag, a.world, a.epoch, ST_TIMEOUT_EP_COUNTS);
     if (threadIdx.x == 0) {
@@ -330,14 +331,22 @@ ep_push_rows_kernel(const PushArgs a) {
             s_dst_base[g] = before;
         }
         s_send_base[a.world] = run;
+        int most = 0;
+        for (int g = 0; g < a.world; ++g) most = max(most, s_send_base[g + 1] - s_send_base[g]);
+        s_most = min(most, a.T);
     }
     __syncthreads();
-    const int V = min(s_send_base[a.world], a.T * a.world);
+    // Consecutive warps serve DIFFERENT destination ranks (the j-th visit to rank me+1, me+2, ... in turn), so every
+    // rank drives all its links at once and no destination is written by all ranks at the same moment; walking the
+    // visits in their stored order (all of rank 0's first) made every rank hit the same peer's ingress link together.
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
-    for (int v = blockIdx.x * warps + (threadIdx.x >> 5); v < V; v += gridDim.x * warps) {
-        int g = 0;
-        while (g + 1 < a.world && s_send_base[g + 1] <= v) ++g;
-        const long long row = static_cast<long long>(s_dst_base[g]) + (v - s_send_base[g]);
+    const long long slots = static_cast<long long>(s_most) * a.world;
+    for (long long u = blockIdx.x * warps + (threadIdx.x >> 5); u < slots; u += static_cast<long long>(gridDim.x) * warps) {
+        const int j = static_cast<int>(u / a.world);
+        const int g = (static_cast<int>(u % a.world) + a.me + 1) % a.world;
+        if (j >= s_send_base[g + 1] - s_send_base[g]) continue;
+        const int v = s_send_base[g] + j;
+        const long long row = static_cast<long long>(s_dst_base[g]) + j;
         if (row >= a.row_cap) continue;            // cannot happen with a row_cap of world * T; never write past an area
         const int tok = a.visit_token[v];
         if (tok < 0 || tok >= a.T) continue;
@@ -383,6 +392,7 @@ ep_push_back_kernel(const __nv_bfloat16 *__restrict__ y, int K, void *const *__r
                     int world, int row_cap, int ret_cap) {
     __shared__ int s_recv_base[kMaxRanks + 1];   // first local row that came from rank s
     __shared__ int s_ret_base[kMaxRanks];        // first visit of rank s that went to me (index in s's return area)
+    __shared__ int s_most_rows;                  // largest number of rows from one rank
     const Header *h = static_cast<const Header *>(peers[me]);
     if (threadIdx.x == 0) {
         int run = 0;
@@ -394,14 +404,21 @@ ep_push_back_kernel(const __nv_bfloat16 *__restrict__ y, int K, void *const *__r
             s_ret_base[s] = before;
         }
         s_recv_base[world] = run;
+        int most = 0;
+        for (int s = 0; s < world; ++s) most = max(most, s_recv_base[s + 1] - s_recv_base[s]);
+        s_most_rows = most;
     }
     __syncthreads();
-    const int R = min(s_recv_base[world], row_cap);
+    // consecutive warps return rows to different source ranks (me+1, me+2, ... in turn), as in ep_push_rows_kernel
     const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
-    for (int i = blockIdx.x * warps + (threadIdx.x >> 5); i < R; i += gridDim.x * warps) {
-        int s = 0;
-        while (s + 1 < world && s_recv_base[s + 1] <= i) ++s;
-        const long long v = static_cast<long long>(s_ret_base[s]) + (i - s_recv_base[s]);
+    const long long slots = static_cast<long long>(s_most_rows) * world;
+    for (long long u = blockIdx.x * warps + (threadIdx.x >> 5); u < slots; u += static_cast<long long>(gridDim.x) * warps) {
+        const int j = static_cast<int>(u / world);
+        const int s = (static_cast<int>(u % world) + me + 1) % world;
+        if (j >= s_recv_base[s + 1] - s_recv_base[s]) continue;
+        const int i = s_recv_base[s] + j;
+        if (i >= row_cap) continue;
+        const long long v = static_cast<long long>(s_ret_base[s]) + j;
         if (v >= ret_cap) continue;
         const int4 *src = reinterpret_cast<const int4 *>(y + static_cast<size_t>(i) * K);
         int4 *dst = reinterpret_cast<int4 *>(static_cast<uint8_t *>(peers[s]) + y_off) + static_cast<size_t>(v) * (K / 8);

@@ -68,7 +68,7 @@ int launch_route(const T *logits, int tokens, int E, int top_k, int renormalize,
 }
 
 // ---------------------------------------------------------------------------------------------
-// MX quantiser: 4 lanes per 32-element block, 8 elements (16 bytes in, 8 bytes out) per thread
+// MX quantiser
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
     const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
@@ -76,66 +76,50 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
     return lo | (hi << 16);
 }
 
-// one 8-element chunk: amax over the block's four lanes, exponent, e4m3 conversion
-__device__ __forceinline__ void quantize_chunk(const uint4 raw, uint2 *o, int *e_out) {
-    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        v[2 * j] = __low2float(h[j]);
-        v[2 * j + 1] = __high2float(h[j]);
-    }
-    float amax = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
-    e = max(0, min(e, 254));
-    const uint32_t field = static_cast<uint32_t>(254 - e);
-    const float inv = __uint_as_float(field ? field << 23 : 0x00400000u);   // 2^(127-e); 2^-127 is subnormal
-    o->x = e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-    o->y = e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-    *e_out = e;
-}
-
-constexpr int kQuantUnroll = 2;   // independent 16-byte loads in flight per thread
-
+// One thread per 32-element block: four 16-byte loads (64 contiguous bytes), the block maximum, the e8m0 exponent,
+// 32 e4m3 values as two 16-byte stores and one scale byte (consecutive threads, consecutive scale bytes).
 __global__ void __launch_bounds__(256)
 quantize_mx_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__restrict__ row_index, int src_rows,
                    uint8_t *__restrict__ q, uint8_t *__restrict__ scales, int rows, int K) {
-    const int chunks = K / 8;                 // 16-byte chunks per row
-    const long long total = static_cast<long long>(rows) * chunks;
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    // the trip count is uniform per warp (the shuffles need all 32 lanes); lanes past the end idle. chunks is a
-    // multiple of 4, so the four lanes of a block always sit in one row and one iteration.
-    for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + (threadIdx.x & ~31u); i0 < total;
-         i0 += kQuantUnroll * stride) {
-        uint4 raw[kQuantUnroll];
-        int r[kQuantUnroll], c[kQuantUnroll];
-        bool active[kQuantUnroll];
+    const int kblocks = K / 32;
+    const long long total = static_cast<long long>(rows) * kblocks;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / kblocks), kb = static_cast<int>(i - static_cast<long long>(r) * kblocks);
+        const int src = row_index ? row_index[r] : r;
+        const bool live = src >= 0 && src < src_rows;       // rows with an index outside x are written as zeros
+        uint4 raw[4];
 #pragma unroll
-        for (int u = 0; u < kQuantUnroll; ++u) {
-            const long long w0 = i0 + u * stride;               // this warp's first chunk of the u-th batch
-            const long long i = min(w0 + (threadIdx.x & 31), total - 1);
-            active[u] = w0 + (threadIdx.x & 31) < total;
-            r[u] = static_cast<int>(i / chunks);
-            c[u] = static_cast<int>(i - static_cast<long long>(r[u]) * chunks);
-            const int src = row_index ? row_index[r[u]] : r[u];
-            const bool live = src >= 0 && src < src_rows;       // rows with an index outside x are written as zeros
+        for (int u = 0; u < 4; ++u) {
             raw[u] = make_uint4(0, 0, 0, 0);
-            if (live && w0 < total) raw[u] = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(src) * K) + c[u]);
+            if (live) raw[u] = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(src) * K + kb * 32) + u);
         }
+        float v[32];
 #pragma unroll
-        for (int u = 0; u < kQuantUnroll; ++u) {
-            if (i0 + u * stride >= total) break;                // uniform per warp
-            uint2 o;
-            int e;
-            quantize_chunk(raw[u], &o, &e);
-            if (!active[u]) continue;
-            reinterpret_cast<uint2 *>(q + static_cast<size_t>(r[u]) * K)[c[u]] = o;
-            if ((c[u] & 3) == 0) scales[static_cast<size_t>(r[u]) * (K / 32) + (c[u] >> 2)] = static_cast<uint8_t>(e);
+        for (int u = 0; u < 4; ++u) {
+            const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[u * 8 + 2 * j] = __low2float(h[j]);
+                v[u * 8 + 2 * j + 1] = __high2float(h[j]);
+            }
         }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 8;
+        e = max(0, min(e, 254));
+        const uint32_t field = static_cast<uint32_t>(254 - e);
+        const float inv = __uint_as_float(field ? field << 23 : 0x00400000u);   // 2^(127-e); 2^-127 is subnormal
+        uint4 o[2];
+        uint32_t *ow = reinterpret_cast<uint32_t *>(o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            ow[j] = e4m3x4(v[4 * j] * inv, v[4 * j + 1] * inv, v[4 * j + 2] * inv, v[4 * j + 3] * inv);
+        uint4 *dst = reinterpret_cast<uint4 *>(q + static_cast<size_t>(r) * K + kb * 32);
+        dst[0] = o[0];
+        dst[1] = o[1];
+        scales[i] = static_cast<uint8_t>(e);
     }
 }
 
@@ -166,10 +150,10 @@ extern "C" int pmoe_quantize_mx(const void *x, const int32_t *row_index, int src
     PMOE_REQUIRE(x && q && scales, PMOE_ERR_BAD_ARG, "quantize_mx: null pointer");
     PMOE_REQUIRE(rows >= 0 && src_rows >= 0 && K > 0 && K % 32 == 0, PMOE_ERR_BAD_ARG,
                  "quantize_mx: rows >= 0 and K a positive multiple of 32 required");
-    PMOE_REQUIRE(((reinterpret_cast<uintptr_t>(x) & 15) | (reinterpret_cast<uintptr_t>(q) & 7)) == 0, PMOE_ERR_BAD_ARG,
-                 "quantize_mx: x must be 16-byte and q 8-byte aligned");
+    PMOE_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q)) & 15) == 0, PMOE_ERR_BAD_ARG,
+                 "quantize_mx: x and q must be 16-byte aligned");
     if (rows == 0) return PMOE_OK;
-    const long long total = static_cast<long long>(rows) * (K / 8);
+    const long long total = static_cast<long long>(rows) * (K / 32);
     const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 16ll * sm_count()));
     quantize_mx_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), row_index, src_rows,
                                                  static_cast<uint8_t *>(q), static_cast<uint8_t *>(scales), rows, K);
