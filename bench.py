@@ -71,8 +71,9 @@ def parse_args():
                          "default when the expert count divides), 'replica' runs N independent copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="headline workload only")
-    ap.add_argument("--op", default="moe", choices=["moe", "moe_align"],
-                    help="'moe_align' times the routing kernels alone on the routing table of --config (GB/s line)")
+    ap.add_argument("--op", default="moe", choices=["moe", "moe_align", "pre"],
+                    help="'moe_align' times the routing kernels alone on the routing table of --config (GB/s line); "
+                         "'pre' times the router and the MX activation quantiser alone at the c3 shapes")
     ap.add_argument("--ep-combine", default="auto", choices=["auto", "nccl", "peer"],
                     help="expert-parallel combine: NCCL all-to-all, or this library's kernel storing into the source "
                          "rank's buffer over NVLink (auto = peer when every rank can map its peers)")
@@ -1129,6 +1130,21 @@ def run_align_only(args):
     print(json.dumps(e))
 
 
+def run_pre_only(args):
+    """`--op pre`: router and MX activation quantiser alone (the command their ncu summary under profiles/ was made
+    with). One JSON line per kernel."""
+    import torch
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    sys.path.insert(0, str(ROOT))
+    import prime_flash_moe_b200  # noqa: F401
+    for e in sweep_pre_entries(device, measured_peaks()):
+        e.update({"metric": e["op"] + "_gbs", "n_gpus": 1, "higher_is_better": True, "data": "synthetic", "impl": "ours"})
+        print(json.dumps(e))
+
+
 def main():
     args = parse_args()
     if args.bpc == 0:
@@ -1140,6 +1156,8 @@ def main():
         args.parallel = "ep" if world > 1 and CONFIGS[args.config][2] % world == 0 else "replica"
     if args.op == "moe_align":
         run_align_only(args)
+    elif args.op == "pre":
+        run_pre_only(args)
     elif args.impl == "cpu":
         run_cpu_arm(args)
     else:
