@@ -780,7 +780,10 @@ def run_gpu_arm(args, impl):
         ops = torch.ops.prime_moe
         (bn, wn), stages, split, bpc = ((64, 4) if args.warp_n == 4 else (32, 8)), args.stages, bool(args.split), args.bpc
         # align kernels + gather, gate/up|fused, down|finalize (+ pair classification and the two tail launches, bpc=2)
-        launches_per_step = (2 if T * k > 4096 else 1) + 3 + (3 if (bpc == 2 and split and not mx) else 0)
+        # moe_align (one CTA up to 4096 ids, or 16384 with <= 256 experts; else histogram + scatter) + row gather,
+        # gate/up|fused, down|finalize (+ pair classification and the two tail launches, bpc=2)
+        align_launches = 1 if (T * k <= 4096 or (T * k <= 16384 and E <= 256)) else 2
+        launches_per_step = align_launches + 3 + (3 if (bpc == 2 and split and not mx) else 0)
 
         def step(x_, ids_, wts_, out_):
             s, e, n = ops.moe_align(ids_, E, 128, bpc)
@@ -1017,7 +1020,9 @@ def run_gpu_arm(args, impl):
             layer.profile = False
         # plan (3) + moe_align (1 or 2) + row gather, gate/up, down (3) + combine (1) (+ publish, push, 2 signals,
         # prepare, return: 6 in peer mode)
-        launches_per_step = 3 + (2 if ep_rows[-1] * k > 4096 else 1) + 3 + 1 + (6 if layer.combine_mode == "peer" else 0)
+        n_local = (world * T if layer.combine_mode == "peer" else ep_rows[-1]) * k      # ids moe_align sees on this rank
+        align_launches = 1 if (n_local <= 4096 or (n_local <= 16384 and E // world <= 256)) else 2
+        launches_per_step = 3 + align_launches + 3 + 1 + (6 if layer.combine_mode == "peer" else 0)
         a_, b_ = out[:np_].float(), par_ref.float()
         ep_parity = max_over_ranks(float((a_ - b_).abs().max() / b_.abs().max().clamp_min(1e-30)), world, device)
     ep_info = None
