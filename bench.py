@@ -292,6 +292,37 @@ def roofline_mxfp8(args, capi, ops, tensors, ids, wts, out, cfg, peaks, whole_tf
             "kernel_ms": per_kernel, "whole_op_frac": whole_tflops / peak}
 
 
+def select_knobs(candidates, trial_calls=3, final_calls=8):
+    """The reference arm's knob choice: every candidate `(call, knobs)` is timed over `trial_calls` calls after two
+    warm-up calls, then the three fastest are timed again over `final_calls` calls and the fastest of those wins
+    (a single short trial picked a slow setting now and then). Returns `(ms, call, knobs)` or None."""
+    import torch
+
+    def timed(call, n):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            call()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    first = []
+    for call, knobs in candidates:
+        try:
+            for _ in range(2):
+                call()
+            torch.cuda.synchronize()
+            first.append((timed(call, trial_calls), call, knobs))
+        except Exception:
+            continue
+    if not first:
+        return None
+    first.sort(key=lambda t: t[0])
+    second = [(timed(call, final_calls), call, knobs) for _, call, knobs in first[:3]]
+    return min(second, key=lambda t: t[0])
+
+
 def time_calls(call, reps, flush_buf=None):
     """Mean milliseconds of `call` on the current stream: one pair of events around `reps` back-to-back calls,
     or - with a flush buffer - a pair per call with the L2 flushed (buffer rewritten) before each."""
@@ -514,7 +545,7 @@ def sweep_entry_reference(name, tokens, dtype, device, ref_pkg):
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device) if \
         touched * (N * K + K * (N // 2)) * (1 if mx else 2) < (256 << 20) else None
     flops = 3.0 * T * k * K * N
-    best = None
+    cands = []
     for split in (True, False):
         for bn, wn in ((64, 4), (32, 8)):
             for stages in (1, 2, 3, 4):
@@ -527,20 +558,8 @@ def sweep_entry_reference(name, tokens, dtype, device, ref_pkg):
                                                 128, bn, wn, stages, 1, split)
                     else:
                         ref_pkg.fused_moe_bf16(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k, 128, bn, wn, stages, 1, 1, split)
-                try:
-                    cand()
-                    torch.cuda.synchronize()
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                    for _ in range(2):
-                        cand()
-                    b.record()
-                    torch.cuda.synchronize()
-                    ms = a.elapsed_time(b) / 2
-                except Exception:
-                    continue
-                if best is None or ms < best[0]:
-                    best = (ms, cand, {"block_n": bn, "warp_n": wn, "stages": stages, "split": split})
+                cands.append((cand, {"block_n": bn, "warp_n": wn, "stages": stages, "split": split}))
+    best = select_knobs(cands, trial_calls=2, final_calls=5)
     if best is None:
         return {"config": name, "tokens": T, "dtype": dtype, "unavailable": "every knob setting of the reference failed"}
     ms = time_steps(best[1], 20 if flops < 5e12 else 8, flush_buf)
@@ -805,7 +824,7 @@ def run_gpu_arm(args, impl):
         assert str(ref_dir) in str(Path(ref_pkg.__file__).resolve()), "wrong prime_moe imported"
         ops = torch.ops.prime_moe
         launches_per_step = None
-        best = None
+        cands = []
         for split in (True, False):
             for bn, wn in ((64, 4), (32, 8)):
                 for stages in (1, 2, 3, 4):
@@ -818,25 +837,16 @@ def run_gpu_arm(args, impl):
                                                     wn, stages, 1, split)
                         else:
                             ref_pkg.fused_moe_bf16(x_, w1, w2, s, e, n, wts_, out_, k, 128, bn, wn, stages, 1, 1, split)
-                    try:
-                        for _ in range(2):
-                            cand(xin, ids, wts, out)
-                        torch.cuda.synchronize()
-                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        a.record()
-                        for _ in range(3):
-                            cand(xin, ids, wts, out)
-                        b.record()
-                        torch.cuda.synchronize()
-                        ms = a.elapsed_time(b) / 3
-                    except Exception:
-                        continue
-                    if best is None or ms < best[0]:
-                        best = (ms, cand, {"block_n": bn, "warp_n": wn, "stages": stages, "split": split, "bpc": 1})
+                    cands.append((lambda cand=cand: cand(xin, ids, wts, out),
+                                  {"block_n": bn, "warp_n": wn, "stages": stages, "split": split, "bpc": 1, "_step": cand}))
+        best = select_knobs(cands)
         if best is None:
             print(json.dumps({"impl": "reference", "unavailable": "every knob setting of the reference failed"}))
             return
-        _, step, knobs = best
+        knobs = dict(best[2])
+        step = knobs.pop("_step")
+        torch.cuda.synchronize()
+        time.sleep(0.5)       # the knob sweep ran ~150 back-to-back steps: let the power state settle before timing
 
     ref_world = 1 if impl == "reference" else world
     # bytes of the weights one step reads: experts actually routed to x (w1 + w2)
