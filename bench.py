@@ -996,18 +996,22 @@ def run_gpu_arm(args, impl):
     # kernels, and over 20 steps of 2.4 ms that pipeline fill / drain alone is ~5 % of the measurement
     e2e_steps = min(max(args.steps, 50), 200)
     e2e_run(3)
-    barrier_sync(ref_world)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    e2e_run(e2e_steps)
-    b.record()
-    barrier_sync(ref_world)
-    e2e_ms = max_over_ranks(a.elapsed_time(b), ref_world, device) / e2e_steps
+    e2e_runs = []
+    for _ in range(2):      # two timed regions, the faster one is reported (both arms alike): on a fresh box the first
+        barrier_sync(ref_world)   # region through host memory now and then runs at half speed for either arm
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        e2e_run(e2e_steps)
+        b.record()
+        barrier_sync(ref_world)
+        e2e_runs.append(max_over_ranks(a.elapsed_time(b), ref_world, device) / e2e_steps)
+    e2e_ms = min(e2e_runs)
     hout = houts[0]
     h2d = sum(t.numel() * t.element_size() for t in hx) + hids.numel() * 4 + hwts.numel() * 4
     d2h = hout.numel() * 2
     e2e = {"value": ref_world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+           "ms_per_step_of_both_regions": e2e_runs}
 
     cpu_baseline = None
     if rank == 0 and not args.no_cpu_baseline and not ep_mode and ref_world == 1:
