@@ -198,6 +198,24 @@ int pmoe_quantize_mx(const void *x /* bf16[src_rows, K] */, const int32_t *row_i
                      void *scales, int rows, int K, pmoe_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Backward pass of pmoe_fused_moe_bf16 (no counterpart in the reference, which is forward-only, README.md:17).
+ * Same routing tensors as the forward call (moe_align output with block_m = 128, pad_to = 128) and the same x,
+ * w1 [E, N, K], w2 [E, K, N/2]; d_out bf16[T, K] is the gradient of `out`. Writes (does not accumulate into)
+ *   d_x  bf16[T, K]        d_w1 bf16[E, N, K]        d_w2 bf16[E, K, N/2]   (experts without rows get zeros)
+ *   d_topk_weights fp32[T, top_k], or NULL to skip it (entries of routes to ids outside [0, E) stay 0)
+ * The gate/up pre-activations are recomputed from x (nothing is kept from the forward call), products accumulate
+ * in fp32 and every intermediate is rounded to bf16 once. K % 64 == 0, N % 128 == 0, sorted_num % 128 == 0,
+ * tensors 16-byte aligned, workspace 1024-byte aligned with pmoe_fused_moe_bf16_backward_workspace_bytes() bytes.
+ * Asynchronous on `stream`; bounded waits and status reporting as for the forward kernels. */
+size_t pmoe_fused_moe_bf16_backward_workspace_bytes(int T, int K, int N, int num_experts, int top_k, int sorted_num);
+int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, const void *d_out,
+                                 const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                 const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k, int T,
+                                 int K, int N, int num_experts, int sorted_num, void *d_x, void *d_w1, void *d_w2,
+                                 float *d_topk_weights, void *workspace, size_t workspace_bytes,
+                                 pmoe_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Expert-parallel glue (no counterpart in the reference, which is single-GPU). Experts are sharded
  * contiguously over `world` ranks (num_experts / world each). The unit of exchange is a VISIT: a (token,
  * destination rank) pair such that at least one of the token's top_k experts lives on that rank.

@@ -305,3 +305,14 @@ def make_case(T, K, E, N, top_k, seed, dist="uniform", x_std=1.0, w_std=None):
     w2 = (torch.randn(E, K, H, generator=g) * s2).to(torch.bfloat16)
     ids, wts = make_routing(T, E, top_k, seed + 1, dist)
     return x, w1, w2, ids, wts
+
+
+def moe_backward_ref_fp32(x, w1, w2, topk_ids, topk_weights, d_out):
+    """Gradients of the fp32 evaluation above (``moe_ref_fp32``, i.e. the contraction of the reference's test
+    oracle test/test.py:13-48) with respect to ``x``, ``w1``, ``w2`` and ``topk_weights`` for an output gradient
+    ``d_out``, by autograd. The reference has no backward pass (README.md:17); this is the checker of the
+    library's own one. Returns fp32 ``(d_x, d_w1, d_w2, d_topk_weights)``."""
+    leaves = [t.detach().float().clone().requires_grad_(True) for t in (x, w1, w2, topk_weights)]
+    out = moe_ref_fp32(leaves[0], leaves[1], leaves[2], topk_ids, leaves[3])
+    out.backward(d_out.float())
+    return tuple(t.grad if t.grad is not None else torch.zeros_like(t) for t in leaves)

@@ -25,7 +25,8 @@ OBJ_DIR = PKG / "_lib" / "obj"
 NATIVE_LIB = LIB_DIR / "libpmoe_b200.so"
 TORCH_EXT = PKG / "_C.so"
 
-CUDA_SOURCES = ["host_common.cu", "moe_align.cu", "moe_bf16.cu", "moe_mxfp8.cu", "moe_ep.cu", "moe_pre.cu"]
+CUDA_SOURCES = ["host_common.cu", "moe_align.cu", "moe_bf16.cu", "moe_mxfp8.cu", "moe_ep.cu", "moe_pre.cu",
+                "moe_bwd_bf16.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC",

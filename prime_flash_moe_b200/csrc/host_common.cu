@@ -180,6 +180,8 @@ bool pregather_enabled() {   // read on every call, like the other per-call swit
 int status_fetch_bf16(int *value, bool reset);
 int status_fetch_mxfp8(int *value, bool reset);
 int status_fetch_ep(int *value, bool reset);
+int status_fetch_bwd(int *value, bool reset);
+int wait_ns_store_bwd(unsigned long long ns);
 int wait_ns_store_ep(unsigned long long ns);
 int wait_ns_store_bf16(unsigned long long ns);
 int wait_ns_store_mxfp8(unsigned long long ns);
@@ -215,12 +217,13 @@ extern "C" int pmoe_device_status(int *status) {
     using namespace pmoe;
     PMOE_REQUIRE(status != nullptr, PMOE_ERR_BAD_ARG, "pmoe_device_status: null pointer");
     PMOE_CUDA_OK(cudaDeviceSynchronize());
-    int a = 0, b = 0, c = 0, d = 0;
+    int a = 0, b = 0, c = 0, d = 0, e = 0;
     if (int rc = status_fetch_bf16(&a, false)) return rc;
+    if (int rc = status_fetch_bwd(&e, false)) return rc;
     if (int rc = status_fetch_mxfp8(&b, false)) return rc;
     if (int rc = status_fetch_misc(&c, false)) return rc;
     if (int rc = status_fetch_ep(&d, false)) return rc;
-    *status = a ? a : (b ? b : (c ? c : d));
+    *status = a ? a : (b ? b : (c ? c : (d ? d : e)));
     if (*status) return set_error(PMOE_ERR_DEVICE, "a kernel gave up a bounded wait (device status %d)", *status);
     return PMOE_OK;
 }
@@ -231,6 +234,7 @@ extern "C" int pmoe_reset_device_status(void) {
     if (int rc = status_fetch_bf16(nullptr, true)) return rc;
     if (int rc = status_fetch_mxfp8(nullptr, true)) return rc;
     if (int rc = status_fetch_ep(nullptr, true)) return rc;
+    if (int rc = status_fetch_bwd(nullptr, true)) return rc;
     return status_fetch_misc(nullptr, true);
 }
 
@@ -241,6 +245,7 @@ extern "C" int pmoe_debug_set_wait_ns(unsigned long long ns) {
     if (int rc = wait_ns_store_bf16(ns)) return rc;
     if (int rc = wait_ns_store_mxfp8(ns)) return rc;
     if (int rc = wait_ns_store_ep(ns)) return rc;
+    if (int rc = wait_ns_store_bwd(ns)) return rc;
     PMOE_CUDA_OK(cudaMemcpyToSymbol(g_wait_ns, &ns, sizeof(ns)));
     return PMOE_OK;
 }

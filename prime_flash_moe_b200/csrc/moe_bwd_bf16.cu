@@ -1,0 +1,614 @@
+// Backward pass of the bf16 MoE FFN (the reference is forward-only, README.md:17; this is an addition).
+//
+// Forward, in sorted-row space (rows of sorted_token_ids, one expert per 128-row block):
+//     gu   = xs @ W1[e]^T               xs = x[token(row)]            [R, N], N = 2H (gate | up)
+//     act  = silu(gate) * up                                          [R, H]
+//     out[token] += wt[row] * (act @ W2[e]^T)                         W2[e] is [K, H]
+// Backward for d_out [T, K]:
+//     d_act = wt * (dos @ W2[e])        dos = d_out[token(row)]       contraction over K, W2 read N-major
+//     d_gate, d_up from d_act, gate, up (SwiGLU derivative)           d_gu [R, N]
+//     d_wt[row] = sum_h (dos @ W2[e])[row, h] * act[row, h]
+//     d_xs  = d_gu @ W1[e]              contraction over N, W1 read N-major; d_x[t] = sum of its rows
+//     d_W2[e] = dos_e^T @ (wt * act)_e  contraction over the expert's rows, both operands M/N-major
+//     d_W1[e] = d_gu_e^T @ xs_e
+//
+// All five contractions run on one persistent tcgen05 kernel (128 x 256 tile, K-step 64, four-slot TMA ring,
+// two TMEM accumulators) whose operands are either K-major (the contraction index is contiguous in memory) or
+// M/N-major (the row / column index is contiguous): the second form needs no transposed copy of anything - a
+// 64 x 64 TMA box of the row-major tensor lands in shared memory as eight 8-row swizzle atoms, which is the
+// canonical M/N-major 128-byte-swizzle operand layout (atom stride along K = 1024 B, along M/N = the box size).
+//
+// Algorithmic bytes (one pass each): weights 2 x (read W1, W2; write dW1, dW2) and the row-space intermediates
+// xs, dos, gu, d_gu, act [R, K | N | H]; FLOPs = 3 x forward (gu recompute + 2 dgrad + 2 wgrad = 5 GEMMs of the
+// forward's two sizes: 2*R*K*N x 3 + 2*R*K*H x 2).
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "host_common.h"
+#include "ptx.cuh"
+#include "tile_sched.cuh"
+
+namespace pmoe {
+
+__device__ int g_status_bwd = 0;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr uint32_t BOX_BYTES = 64 * 64 * 2;           // one 64 x 64 bf16 box: 8 KB, eight swizzle atoms
+constexpr uint32_t A_BYTES = BM * BK * 2;             // 16 KB
+constexpr uint32_t B_BYTES = BN * BK * 2;             // 32 KB
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;   // 48 KB
+constexpr int STAGES = 4;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + 256;
+
+enum : int {
+    MODE_NT_STORE = 0,     // C[R, n] = A[R, k] . B[e][n, k]^T          A, B K-major       plain bf16 store
+    MODE_NN_SWIGLU = 1,    // C[R, h] = A[R, k] . B[e][k, h]            B N-major          SwiGLU backward epilogue
+    MODE_NN_STORE = 2,     // C[R, n] = A[R, k] . B[e][k, n]            B N-major          plain bf16 store
+    MODE_WGRAD = 3,        // C[e][m, n] = sum over the expert's rows A[r, m] . B[r, n]    both M/N-major
+};
+
+struct GArgs {
+    int mode;
+    const int32_t *sorted_ids, *expert_ids, *npp;
+    int sorted_num;
+    const int32_t *eblk;          // MODE_WGRAD: first / one-past-last row block of every expert, [2 * E]
+    const float *topk_weights;
+    int top_k, tokens, E;
+    int ksteps;                   // modes 0-2: contraction length / 64
+    int n_tiles;                  // 256-column tiles of C
+    int m_tiles;                  // MODE_WGRAD: 128-row tiles of one expert's C
+    int b_rows_per_expert;        // rows of one expert in B's 2-D view (modes 0-2)
+    __nv_bfloat16 *c;
+    long long ldc;
+    int c_cols;                   // live columns of C
+    int c_rows;                   // MODE_WGRAD: rows of one expert's C
+    // MODE_NN_SWIGLU
+    const __nv_bfloat16 *gu;      // [R, N] gate | up pre-activations
+    __nv_bfloat16 *dgu;           // [R, N]
+    __nv_bfloat16 *actw;          // [R, H] wt * silu(gate) * up
+    float *dwt;                   // [tokens * top_k] or null
+    int H, N;
+};
+
+// ---------------------------------------------------------------------------------------------
+// row-space helpers (HBM-bound)
+// ---------------------------------------------------------------------------------------------
+// dst[r] = src[token(r)] for the live rows, zeros for padding rows; 16 bytes per thread and step
+__global__ void __launch_bounds__(256)
+gather_token_rows_kernel(const __nv_bfloat16 *__restrict__ src, const int32_t *__restrict__ sorted_ids,
+                         const int32_t *__restrict__ npp, int sorted_num, int top_k, int tokens, int K,
+                         __nv_bfloat16 *__restrict__ dst) {
+    const int rows = live_row_blocks(npp, sorted_num) * BM;
+    const int vec_per_row = K / 8;
+    const long long total = static_cast<long long>(rows) * vec_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / vec_per_row), v = static_cast<int>(i - static_cast<long long>(r) * vec_per_row);
+        const int pair = sorted_ids[r];
+        const int tok = pair >= 0 ? pair / top_k : tokens;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (tok < tokens) val = __ldg(reinterpret_cast<const uint4 *>(src + static_cast<size_t>(tok) * K) + v);
+        reinterpret_cast<uint4 *>(dst + static_cast<size_t>(r) * K)[v] = val;
+    }
+}
+
+// inv[pair] = sorted row of the pair (inv is preset to -1); eblk[e] / eblk[E + e] = block range of expert e
+// (preset to 0)
+__global__ void __launch_bounds__(256)
+row_maps_kernel(const int32_t *__restrict__ sorted_ids, const int32_t *__restrict__ expert_ids,
+                const int32_t *__restrict__ npp, int sorted_num, int top_k, int tokens, int E,
+                int32_t *__restrict__ inv, int32_t *__restrict__ eblk) {
+    const int blocks = live_row_blocks(npp, sorted_num);
+    const int rows = blocks * BM;
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+        const int pair = sorted_ids[r];
+        if (pair >= 0 && pair < tokens * top_k) inv[pair] = r;
+        if ((r & (BM - 1)) == 0) {
+            const int b = r / BM, e = expert_ids[b];
+            if (e >= 0 && e < E) {
+                if (b == 0 || expert_ids[b - 1] != e) eblk[e] = b;
+                if (b == blocks - 1 || expert_ids[b + 1] != e) eblk[E + e] = b + 1;
+            }
+        }
+    }
+}
+
+// dx[t] = sum over the token's top_k routes of d_xs[row of the route] (fp32 sum, one rounding)
+__global__ void __launch_bounds__(256)
+combine_dx_kernel(const __nv_bfloat16 *__restrict__ dxs, const int32_t *__restrict__ inv, int top_k, int tokens,
+                  int K, __nv_bfloat16 *__restrict__ dx) {
+    const int vec_per_row = K / 8;
+    const long long total = static_cast<long long>(tokens) * vec_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / vec_per_row), v = static_cast<int>(i - static_cast<long long>(t) * vec_per_row);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < top_k; ++j) {
+            const int r = inv[t * top_k + j];
+            if (r < 0) continue;
+            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(dxs + static_cast<size_t>(r) * K) + v);
+            const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                acc[2 * q] += __low2float(h[q]);
+                acc[2 * q + 1] += __high2float(h[q]);
+            }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        reinterpret_cast<uint4 *>(dx + static_cast<size_t>(t) * K)[v] = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// the grouped GEMM
+//   warp 0: TMA producer | warp 1: TMEM owner + MMA issuer | warps 2-9: epilogue (lane quarter = warp % 4,
+//   column half = (warp - 2) / 4)
+//   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2]
+// ---------------------------------------------------------------------------------------------
+struct Ring {
+    uint32_t ring, bars;
+    __device__ __forceinline__ uint32_t a(int s) const { return ring + s * STAGE_BYTES; }
+    __device__ __forceinline__ uint32_t b(int s) const { return ring + s * STAGE_BYTES + A_BYTES; }
+    __device__ __forceinline__ uint32_t full(int s) const { return bars + 8 * s; }
+    __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8 * (STAGES + s); }
+    __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * STAGES + i); }
+    __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * STAGES + 4); }
+};
+
+// Shared-memory descriptor of an M/N-major operand made of 64 x 64 boxes written by TMA with SWIZZLE_128B: one
+// 128-byte line holds 64 consecutive M (or N) indices of one k, eight lines (8 k) form a 1024-byte swizzle atom;
+// atoms follow each other along k every 1024 B (stride byte offset) and along M/N every box (leading byte offset).
+// Stepping by one MMA (16 k) adds 2048 B to `addr`.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr) {
+    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(BOX_BYTES >> 4) << 16) |
+           (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+struct Tile {
+    int mb, nt, e, mt, k0, k1;
+};
+
+__device__ __forceinline__ Tile decode_tile(const GArgs &a, int t, int m_blocks) {
+    Tile tl;
+    if (a.mode == MODE_WGRAD) {
+        const int per = a.m_tiles * a.n_tiles;
+        tl.e = t / per;
+        const int rem = t - tl.e * per;
+        tl.mt = rem % a.m_tiles;
+        tl.nt = rem / a.m_tiles;
+        tl.mb = 0;
+        tl.k0 = 2 * a.eblk[tl.e];              // k-step = 64-row chunk of the sorted row space
+        tl.k1 = 2 * a.eblk[a.E + tl.e];
+    } else {
+        const Coord c = tile_coord(t, m_blocks, a.n_tiles);
+        tl.mb = c.m_blk;
+        tl.nt = c.n_tile;
+        tl.mt = 0;
+        tl.e = max(0, min(a.E - 1, a.expert_ids[c.m_blk]));
+        tl.k0 = 0;
+        tl.k1 = a.ksteps;
+    }
+    return tl;
+}
+
+__device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16 *dst, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint4 o;
+        o.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+        o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+        o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+        o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+        reinterpret_cast<uint4 *>(dst)[j] = o;
+    }
+}
+
+__device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16 *src, float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 raw = reinterpret_cast<const uint4 *>(src)[j];
+        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            v[8 * j + 2 * q] = __low2float(h[q]);
+            v[8 * j + 2 * q + 1] = __high2float(h[q]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    Ring sm;
+    sm.ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    sm.bars = sm.ring + STAGES * STAGE_BYTES;
+    int *status = &g_status_bwd;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), 1);
+        mbar_init(sm.misc(2), EPI_WARPS * 32);
+        mbar_init(sm.misc(3), EPI_WARPS * 32);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) tmem_alloc(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    const int m_blocks = live_row_blocks(a.npp, a.sorted_num);
+    const int num_tiles = a.mode == MODE_WGRAD ? a.E * a.m_tiles * a.n_tiles : m_blocks * a.n_tiles;
+    const bool a_mn = a.mode == MODE_WGRAD;
+    const bool b_mn = a.mode != MODE_NT_STORE;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Tile tl = decode_tile(a, t, m_blocks);
+                for (int ks = tl.k0; ks < tl.k1; ++ks) {
+                    ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sm.full(s), STAGE_BYTES);
+                    if (a_mn) {
+#pragma unroll
+                        for (int i = 0; i < 2; ++i)
+                            tma_load_2d(sm.a(s) + i * BOX_BYTES, &map_a, sm.full(s), tl.mt * BM + i * 64, ks * 64);
+                    } else {
+                        tma_load_2d(sm.a(s), &map_a, sm.full(s), ks * BK, tl.mb * BM);
+                    }
+                    if (!b_mn) {
+                        tma_load_2d(sm.b(s), &map_b, sm.full(s), ks * BK, tl.e * a.b_rows_per_expert + tl.nt * BN);
+                    } else {
+                        const int krow = a.mode == MODE_WGRAD ? ks * 64 : tl.e * a.b_rows_per_expert + ks * 64;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tma_load_2d(sm.b(s) + j * BOX_BYTES, &map_b, sm.full(s), tl.nt * BN + j * 64, krow);
+                    }
+                    ++issued;
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                // give the copies already issued a bounded time to land before the CTA exits
+                const long long first = issued > STAGES ? issued - STAGES : 0;
+                for (long long f = first; f < issued; ++f) {
+                    const uint32_t bar = sm.full(static_cast<int>(f % STAGES));
+                    const uint32_t parity = static_cast<uint32_t>((f / STAGES) & 1);
+                    const uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(bar, parity))
+                        if (globaltimer_ns() - t0 > 20000000ull) break;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = idesc_bf16_f32(BM, BN) | (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const Tile tl = decode_tile(a, t, m_blocks);
+                if (tl.k1 <= tl.k0) continue;
+                const int buf = it & 1;
+                ok = mbar_wait(sm.misc(2 + buf), ((it >> 1) & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BN;
+                for (int ks = tl.k0; ks < tl.k1; ++ks) {
+                    ok = mbar_wait(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = a_mn ? smem_desc_mn_sw128(sm.a(s) + k * 2048) : smem_desc_sw128(sm.a(s) + k * 32);
+                        const uint64_t bd = b_mn ? smem_desc_mn_sw128(sm.b(s) + k * 2048) : smem_desc_sw128(sm.b(s) + k * 32);
+                        umma_f16(d, ad, bd, idesc, (ks != tl.k0) || (k != 0));
+                    }
+                    umma_commit(sm.empty(s));
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit(sm.misc(buf));
+                ++it;
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int cg = ew / 4;
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const Tile tl = decode_tile(a, t, m_blocks);
+            const int col0 = tl.nt * BN;
+            if (tl.k1 <= tl.k0) {
+                // an expert without rows: its weight gradient is zero
+                const int m = tl.mt * BM + row;
+                if (m < a.c_rows) {
+                    __nv_bfloat16 *dst = a.c + (static_cast<size_t>(tl.e) * a.c_rows + m) * a.ldc + col0;
+                    for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
+                        if (col0 + ch * 32 < a.c_cols)
+                            for (int j = 0; j < 4; ++j)
+                                reinterpret_cast<uint4 *>(dst + ch * 32)[j] = make_uint4(0, 0, 0, 0);
+                }
+                continue;
+            }
+            const int buf = it & 1;
+            if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * BN;
+            if (a.mode == MODE_NN_SWIGLU) {
+                const size_t row_g = static_cast<size_t>(tl.mb) * BM + row;
+                const int pair = a.sorted_ids[row_g];
+                const bool valid = pair >= 0 && pair < a.tokens * a.top_k;
+                const float wt = valid ? a.topk_weights[pair] : 0.f;
+                float part = 0.f;
+                for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
+                    const int h0 = col0 + ch * 32;
+                    if (h0 >= a.H) break;
+                    float c[32], g[32], u[32];
+                    tmem_ld_32x32(c, tmem_addr(acc, lane_base, ch * 32));
+                    load_chunk_bf16(a.gu + row_g * a.N + h0, g);
+                    load_chunk_bf16(a.gu + row_g * a.N + a.H + h0, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float s = 1.f / (1.f + __expf(-g[j]));
+                        const float silu = g[j] * s;
+                        const float act = silu * u[j];
+                        const float d = wt * c[j];
+                        part += c[j] * act;
+                        c[j] = wt * act;                                   // -> actw
+                        g[j] = d * u[j] * s * (1.f + g[j] * (1.f - s));    // -> d_gate
+                        u[j] = d * silu;                                   // -> d_up
+                    }
+                    store_chunk_bf16(a.actw + row_g * a.H + h0, c);
+                    store_chunk_bf16(a.dgu + row_g * a.N + h0, g);
+                    store_chunk_bf16(a.dgu + row_g * a.N + a.H + h0, u);
+                }
+                if (a.dwt && valid) atomicAdd(a.dwt + pair, part);
+            } else {
+                __nv_bfloat16 *dst;
+                bool row_ok = true;
+                if (a.mode == MODE_WGRAD) {
+                    const int m = tl.mt * BM + row;
+                    row_ok = m < a.c_rows;
+                    dst = a.c + (static_cast<size_t>(tl.e) * a.c_rows + (row_ok ? m : 0)) * a.ldc + col0;
+                } else {
+                    dst = a.c + (static_cast<size_t>(tl.mb) * BM + row) * a.ldc + col0;
+                }
+                for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
+                    if (col0 + ch * 32 >= a.c_cols) break;
+                    float v[32];
+                    tmem_ld_32x32(v, tmem_addr(acc, lane_base, ch * 32));
+                    tmem_ld_wait();
+                    if (row_ok) store_chunk_bf16(dst + ch * 32, v);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(sm.misc(2 + buf));
+            ++it;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+size_t align_up(size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); }
+
+struct BwdLayout {
+    size_t xs, dos, gu, dgu, actw, inv, eblk, total;
+};
+
+// xs | dos (reused for d_xs once dW2 is done) | gu | d_gu | wt*act | pair -> row | expert block ranges
+BwdLayout plan_backward(int T, int K, int N, int E, int top_k, int sorted_num) {
+    const size_t R = static_cast<size_t>(sorted_num);
+    BwdLayout l{};
+    size_t off = 0;
+    l.xs = off, off = align_up(off + R * K * 2);
+    l.dos = off, off = align_up(off + R * K * 2);
+    l.gu = off, off = align_up(off + R * N * 2);
+    l.dgu = off, off = align_up(off + R * N * 2);
+    l.actw = off, off = align_up(off + R * (N / 2) * 2);
+    l.inv = off, off = align_up(off + static_cast<size_t>(T) * top_k * sizeof(int32_t));
+    l.eblk = off, off = align_up(off + 2 * static_cast<size_t>(E) * sizeof(int32_t));
+    l.total = off;
+    return l;
+}
+
+int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    PMOE_CUDA_OK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        PMOE_CUDA_OK(cudaFuncSetAttribute(moe_bwd_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(SMEM_BYTES)));
+        configured[dev] = true;
+    }
+    moe_bwd_gemm_kernel<<<sm_count(), THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+int bf16_map(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char *what) {
+    return make_tmap_2d(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, rows, cols, box_rows, 64,
+                        CU_TENSOR_MAP_SWIZZLE_128B, what);
+}
+
+}  // namespace
+
+int wait_ns_store_bwd(unsigned long long ns) {
+    PMOE_CUDA_OK(cudaMemcpyToSymbol(g_wait_ns, &ns, sizeof(ns)));
+    return PMOE_OK;
+}
+
+int status_fetch_bwd(int *value, bool reset) {
+    if (value) PMOE_CUDA_OK(cudaMemcpyFromSymbol(value, g_status_bwd, sizeof(int)));
+    if (reset) {
+        const int zero = 0;
+        PMOE_CUDA_OK(cudaMemcpyToSymbol(g_status_bwd, &zero, sizeof(int)));
+    }
+    return PMOE_OK;
+}
+
+}  // namespace pmoe
+
+extern "C" size_t pmoe_fused_moe_bf16_backward_workspace_bytes(int T, int K, int N, int num_experts, int top_k,
+                                                               int sorted_num) {
+    if (T <= 0 || K <= 0 || N <= 0 || num_experts <= 0 || top_k <= 0 || sorted_num <= 0) return 0;
+    return pmoe::plan_backward(T, K, N, num_experts, top_k, sorted_num).total;
+}
+
+extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, const void *d_out,
+                                            const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                            const int32_t *num_tokens_post_padded, const float *topk_weights,
+                                            int top_k, int T, int K, int N, int num_experts, int sorted_num,
+                                            void *d_x, void *d_w1, void *d_w2, float *d_topk_weights,
+                                            void *workspace, size_t workspace_bytes, pmoe_stream_t stream_) {
+    using namespace pmoe;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PMOE_REQUIRE(x && w1 && w2 && d_out && sorted_token_ids && expert_ids && num_tokens_post_padded && topk_weights &&
+                     d_x && d_w1 && d_w2,
+                 PMOE_ERR_BAD_ARG, "fused_moe_bf16_backward: null pointer");
+    PMOE_REQUIRE(T >= 0 && K > 0 && N > 0 && num_experts > 0 && top_k > 0 && sorted_num >= 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_backward: negative or zero size");
+    PMOE_REQUIRE(K % 64 == 0 && N % 128 == 0, PMOE_ERR_UNSUPPORTED,
+                 "fused_moe_bf16_backward: K must be a multiple of 64 and N of 128, got K=%d N=%d", K, N);
+    PMOE_REQUIRE(sorted_num % 128 == 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_backward: sorted_num must be a multiple of block_m = 128, got %d", sorted_num);
+    const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w1) |
+                          reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(d_out) |
+                          reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_w1) |
+                          reinterpret_cast<uintptr_t>(d_w2);
+    PMOE_REQUIRE((all & 15) == 0, PMOE_ERR_BAD_ARG, "fused_moe_bf16_backward: tensors must be 16-byte aligned");
+    const int H = N / 2, E = num_experts;
+    const size_t w1_bytes = static_cast<size_t>(E) * N * K * 2, w2_bytes = static_cast<size_t>(E) * K * H * 2;
+    if (T == 0 || sorted_num == 0) {   // no routed row: every gradient is zero
+        PMOE_CUDA_OK(cudaMemsetAsync(d_w1, 0, w1_bytes, stream));
+        PMOE_CUDA_OK(cudaMemsetAsync(d_w2, 0, w2_bytes, stream));
+        return PMOE_OK;
+    }
+    const BwdLayout lay = plan_backward(T, K, N, E, top_k, sorted_num);
+    PMOE_REQUIRE(workspace && workspace_bytes >= lay.total, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_backward: workspace of %zu bytes required, got %zu", lay.total, workspace_bytes);
+    PMOE_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_backward: workspace must be 1024-byte aligned");
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    auto *xs = reinterpret_cast<__nv_bfloat16 *>(ws + lay.xs);
+    auto *dos = reinterpret_cast<__nv_bfloat16 *>(ws + lay.dos);
+    auto *gu = reinterpret_cast<__nv_bfloat16 *>(ws + lay.gu);
+    auto *dgu = reinterpret_cast<__nv_bfloat16 *>(ws + lay.dgu);
+    auto *actw = reinterpret_cast<__nv_bfloat16 *>(ws + lay.actw);
+    auto *inv = reinterpret_cast<int32_t *>(ws + lay.inv);
+    auto *eblk = reinterpret_cast<int32_t *>(ws + lay.eblk);
+    const uint64_t R = static_cast<uint64_t>(sorted_num);
+
+    PMOE_CUDA_OK(cudaMemsetAsync(inv, 0xFF, static_cast<size_t>(T) * top_k * sizeof(int32_t), stream));
+    PMOE_CUDA_OK(cudaMemsetAsync(eblk, 0, 2 * static_cast<size_t>(E) * sizeof(int32_t), stream));
+    if (d_topk_weights)
+        PMOE_CUDA_OK(cudaMemsetAsync(d_topk_weights, 0, static_cast<size_t>(T) * top_k * sizeof(float), stream));
+    const int small_grid = std::max(1, std::min(sorted_num / 256 + 1, 8 * sm_count()));
+    row_maps_kernel<<<small_grid, 256, 0, stream>>>(sorted_token_ids, expert_ids, num_tokens_post_padded, sorted_num,
+                                                    top_k, T, E, inv, eblk);
+    PMOE_CUDA_OK(cudaGetLastError());
+    const int copy_grid = 8 * sm_count();
+    gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), sorted_token_ids,
+                                                            num_tokens_post_padded, sorted_num, top_k, T, K, xs);
+    PMOE_CUDA_OK(cudaGetLastError());
+    gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d_out),
+                                                            sorted_token_ids, num_tokens_post_padded, sorted_num,
+                                                            top_k, T, K, dos);
+    PMOE_CUDA_OK(cudaGetLastError());
+
+    CUtensorMap xs_k, xs_mn, dos_k, dos_mn, dgu_k, dgu_mn, actw_mn, w1_k, w1_mn, w2_mn;
+    if (int rc = bf16_map(&xs_k, xs, R, K, 128, "xs rows")) return rc;
+    if (int rc = bf16_map(&xs_mn, xs, R, K, 64, "xs boxes")) return rc;
+    if (int rc = bf16_map(&dos_k, dos, R, K, 128, "d_out rows")) return rc;
+    if (int rc = bf16_map(&dos_mn, dos, R, K, 64, "d_out boxes")) return rc;
+    if (int rc = bf16_map(&dgu_k, dgu, R, N, 128, "d_gu rows")) return rc;
+    if (int rc = bf16_map(&dgu_mn, dgu, R, N, 64, "d_gu boxes")) return rc;
+    if (int rc = bf16_map(&actw_mn, actw, R, H, 64, "act boxes")) return rc;
+    if (int rc = bf16_map(&w1_k, w1, static_cast<uint64_t>(E) * N, K, 256, "w1 rows")) return rc;
+    if (int rc = bf16_map(&w1_mn, w1, static_cast<uint64_t>(E) * N, K, 64, "w1 boxes")) return rc;
+    if (int rc = bf16_map(&w2_mn, w2, static_cast<uint64_t>(E) * K, H, 64, "w2 boxes")) return rc;
+
+    GArgs base{};
+    base.sorted_ids = sorted_token_ids, base.expert_ids = expert_ids, base.npp = num_tokens_post_padded;
+    base.sorted_num = sorted_num, base.eblk = eblk, base.topk_weights = topk_weights;
+    base.top_k = top_k, base.tokens = T, base.E = E, base.H = H, base.N = N;
+
+    {   // gate | up pre-activations: gu = xs . W1[e]^T
+        GArgs g = base;
+        g.mode = MODE_NT_STORE, g.ksteps = K / 64, g.n_tiles = (N + 255) / 256, g.b_rows_per_expert = N;
+        g.c = gu, g.ldc = N, g.c_cols = N;
+        if (int rc = launch_gemm(xs_k, w1_k, g, stream)) return rc;
+    }
+    {   // d_act = wt * (dos . W2[e]) -> d_gu, wt * act, d_wt
+        GArgs g = base;
+        g.mode = MODE_NN_SWIGLU, g.ksteps = K / 64, g.n_tiles = (H + 255) / 256, g.b_rows_per_expert = K;
+        g.gu = gu, g.dgu = dgu, g.actw = actw, g.dwt = d_topk_weights;
+        if (int rc = launch_gemm(dos_k, w2_mn, g, stream)) return rc;
+    }
+    {   // d_W2[e] [K, H] = dos_e^T . (wt * act)_e
+        GArgs g = base;
+        g.mode = MODE_WGRAD, g.m_tiles = (K + 127) / 128, g.n_tiles = (H + 255) / 256;
+        g.c = static_cast<__nv_bfloat16 *>(d_w2), g.ldc = H, g.c_cols = H, g.c_rows = K;
+        if (int rc = launch_gemm(dos_mn, actw_mn, g, stream)) return rc;
+    }
+    {   // d_xs = d_gu . W1[e], written over dos (dead from here on)
+        GArgs g = base;
+        g.mode = MODE_NN_STORE, g.ksteps = N / 64, g.n_tiles = (K + 255) / 256, g.b_rows_per_expert = N;
+        g.c = dos, g.ldc = K, g.c_cols = K;
+        if (int rc = launch_gemm(dgu_k, w1_mn, g, stream)) return rc;
+    }
+    {   // d_W1[e] [N, K] = d_gu_e^T . xs_e
+        GArgs g = base;
+        g.mode = MODE_WGRAD, g.m_tiles = (N + 127) / 128, g.n_tiles = (K + 255) / 256;
+        g.c = static_cast<__nv_bfloat16 *>(d_w1), g.ldc = K, g.c_cols = K, g.c_rows = N;
+        if (int rc = launch_gemm(dgu_mn, xs_mn, g, stream)) return rc;
+    }
+    combine_dx_kernel<<<copy_grid, 256, 0, stream>>>(dos, inv, top_k, T, K, static_cast<__nv_bfloat16 *>(d_x));
+    PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}

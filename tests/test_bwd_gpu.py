@@ -1,0 +1,90 @@
+"""Backward pass of fused_moe_bf16 on the GPU against autograd through the all-fp32 CPU oracle.
+
+Tolerance: max|grad - ref| <= 2e-2 * max|ref| per gradient tensor (the forward's tolerance; every intermediate of
+the backward pass - gate/up pre-activations, activation, d_gate/d_up, d_xs - is rounded to bf16 once)."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 2e-2
+
+
+def run_backward(x, w1, w2, ids, wts, d_out, need_weight_grad=True):
+    from prime_flash_moe_b200 import capi
+    E = w1.shape[0]
+    k = ids.shape[1]
+    s, e, n = capi.moe_align(ids.to(DEV), E, 128, 1)
+    grads = capi.fused_moe_bf16_backward(x.to(DEV), w1.to(DEV), w2.to(DEV), d_out.to(DEV), s, e, n, wts.to(DEV), k,
+                                         need_weight_grad=need_weight_grad)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    return tuple(None if g is None else g.cpu() for g in grads)
+
+
+def check(grads, refs):
+    for name, g, r in zip(("d_x", "d_w1", "d_w2", "d_topk_weights"), grads, refs):
+        if g is None:
+            continue
+        assert torch.isfinite(g.float()).all(), name
+        err = O.max_rel_to_peak(g, r)
+        assert err <= TOL, f"{name}: {err}"
+
+
+@pytest.mark.parametrize("T,K,E,N,k", [
+    (1, 128, 2, 256, 1), (8, 128, 1, 256, 1), (64, 512, 4, 512, 2),
+    (130, 320, 5, 768, 3),       # K neither a multiple of 128 nor of 256: ragged row and column tiles
+    (100, 256, 4, 384, 2),       # H = 192: ragged column tile of the SwiGLU step
+    (256, 4096, 8, 512, 4),      # benchmark configuration 0
+    (300, 1024, 8, 1024, 4), (1000, 384, 16, 256, 8),
+])
+def test_vs_autograd_of_fp32_oracle(T, K, E, N, k):
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=T + K)
+    d_out = torch.randn(T, K, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16)
+    refs = O.moe_backward_ref_fp32(x, w1, w2, ids, wts, d_out)
+    check(run_backward(x, w1, w2, ids, wts, d_out), refs)
+
+
+def test_experts_without_rows_get_zero_weight_gradients():
+    T, K, E, N, k = 8, 256, 16, 256, 2
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=3)
+    ids = (ids % 3).to(torch.int32)           # only experts 0..2 are routed to
+    ids[:, 1] = (ids[:, 0] + 1) % 3
+    d_out = torch.randn(T, K, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    refs = O.moe_backward_ref_fp32(x, w1, w2, ids, wts, d_out)
+    grads = run_backward(x, w1, w2, ids, wts, d_out)
+    check(grads, refs)
+    assert float(grads[1][3:].float().abs().max()) == 0.0
+    assert float(grads[2][3:].float().abs().max()) == 0.0
+
+
+def test_ids_out_of_range_are_ignored_and_weight_gradient_is_optional():
+    T, K, E, N, k = 50, 256, 4, 256, 2
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=5)
+    d_out = torch.randn(T, K, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    bad = ids.clone()
+    bad[::7, 1] = E + 3                       # these routes are dropped by moe_align
+    keep = bad < E
+    refs = O.moe_backward_ref_fp32(x, w1, w2, torch.where(keep, bad, torch.zeros_like(bad)),
+                                   torch.where(keep, wts, torch.zeros_like(wts)), d_out)
+    grads = run_backward(x, w1, w2, bad, wts, d_out)
+    check(grads[:3], refs[:3])
+    assert float(grads[3][~keep].abs().max()) == 0.0
+    assert O.max_rel_to_peak(grads[3][keep], refs[3][keep]) <= TOL
+    assert run_backward(x, w1, w2, bad, wts, d_out, need_weight_grad=False)[3] is None
+
+
+def test_argument_checks():
+    from prime_flash_moe_b200 import capi
+    x, w1, w2, ids, wts = O.make_case(16, 96, 2, 256, 1, seed=1)     # K = 96 is not a multiple of 64
+    s, e, n = capi.moe_align(ids.to(DEV), 2, 128, 1)
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        capi.fused_moe_bf16_backward(x.to(DEV), w1.to(DEV), w2.to(DEV), x.to(DEV), s, e, n, wts.to(DEV), 1)
+    x, w1, w2, ids, wts = O.make_case(16, 128, 2, 256, 1, seed=1)
+    s, e, n = capi.moe_align(ids.to(DEV), 2, 128, 1)
+    small = torch.empty(2048, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError, match="workspace"):
+        capi.fused_moe_bf16_backward(x.to(DEV), w1.to(DEV), w2.to(DEV), x.to(DEV), s, e, n, wts.to(DEV), 1,
+                                     workspace=small[(-small.data_ptr()) % 1024:][:1024])
