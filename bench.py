@@ -71,9 +71,10 @@ def parse_args():
                          "default when the expert count divides), 'replica' runs N independent copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="headline workload only")
-    ap.add_argument("--op", default="moe", choices=["moe", "moe_align", "pre"],
+    ap.add_argument("--op", default="moe", choices=["moe", "moe_align", "pre", "backward"],
                     help="'moe_align' times the routing kernels alone on the routing table of --config (GB/s line); "
-                         "'pre' times the router and the MX activation quantiser alone at the c3 shapes")
+                         "'pre' times the router and the MX activation quantiser alone at the c3 shapes; 'backward' times the "
+                         "bf16 backward pass and each of its steps on --config")
     ap.add_argument("--ep-combine", default="auto", choices=["auto", "nccl", "peer"],
                     help="expert-parallel combine: NCCL all-to-all, or this library's kernel storing into the source "
                          "rank's buffer over NVLink (auto = peer when every rank can map its peers)")
@@ -679,6 +680,48 @@ def sweep_pre_entries(device, peaks):
     return entries
 
 
+SWEEP_BACKWARD = [("c0", 0), ("c2", 8192), ("c1", 0)]
+BACKWARD_STEPS = (("prep", 1), ("gate_up_recompute", 2), ("d_act_swiglu", 4), ("d_w2", 8), ("d_xs", 16), ("d_w1", 32),
+                  ("combine_d_x", 64))
+
+
+def sweep_backward_entry(name, tokens, device, peaks):
+    """Backward pass of the bf16 layer (`fused_moe_bf16_backward`; the reference has none): d_x, d_w1, d_w2 and
+    d_topk_weights from d_out, L2 flushed before every call. FLOPs = 3 x forward (gate/up recompute, two dgrad and two
+    wgrad GEMMs); the roofline is the tensor one over the whole call."""
+    import torch
+    from prime_flash_moe_b200 import capi
+    ops = torch.ops.prime_moe
+    c = build_sweep_case(name, tokens, "bf16", device)
+    T, K, E, N, k, routing = c["cfg"]
+    lib = capi.lib()
+    s, e, n = ops.moe_align(c["ids"], E, 128, 1)
+    d_out = torch.randn(T, K, device=device, generator=torch.Generator(device=device).manual_seed(99)).to(torch.bfloat16)
+    ws = capi._workspace(lib.pmoe_fused_moe_bf16_backward_workspace_bytes(T, K, N, E, k, s.numel()), device)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    call = lambda: capi.fused_moe_bf16_backward(c["x"], c["w1"], c["w2"], d_out, s, e, n, c["wts"], k, workspace=ws)
+    flops = 9.0 * T * k * K * N
+    reps = 10 if flops < 2e13 else 5
+    ms = time_calls(call, reps, flush_buf)
+    steps = {}
+    for label, bit in BACKWARD_STEPS:
+        lib.pmoe_debug_set_backward_mask(bit)
+        steps[label] = time_calls(call, reps, flush_buf)
+    lib.pmoe_debug_set_backward_mask(127)
+    call()
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0, "a kernel recorded an error status"
+    ach = flops / (ms * 1e-3) / 1e12
+    del c, ws, d_out, flush_buf
+    torch.cuda.empty_cache()
+    return {"config": name, "tokens": T, "op": "backward", "dtype": "bf16", "ms_per_step": ms, "value": ach,
+            "unit": "TFLOP/s",
+            "roofline": {"kernel": "moe_bwd_gemm_kernel (5 launches)", "bound": "tensor", "achieved": ach,
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
+                         "peak_source": peaks["source"] + " (burst cuBLAS bf16)", "traffic": None,
+                         "kernel_ms": steps}}
+
+
 def run_sweep(impl, device, peaks, stages, ref_pkg=None):
     entries = []
     for name, tokens, dtype in SWEEP:
@@ -700,6 +743,12 @@ def run_sweep(impl, device, peaks, stages, ref_pkg=None):
             entries.extend(sweep_pre_entries(device, peaks))
         except Exception as exc:
             entries.append({"config": "c3", "op": "route_topk / quantize_mx", "error": f"{type(exc).__name__}: {exc}"[:200]})
+        for name, tokens in SWEEP_BACKWARD:     # nor a backward pass
+            try:
+                entries.append(sweep_backward_entry(name, tokens, device, peaks))
+            except Exception as exc:
+                entries.append({"config": name, "tokens": tokens, "op": "backward",
+                                "error": f"{type(exc).__name__}: {exc}"[:200]})
     return entries
 
 
@@ -1166,6 +1215,20 @@ def run_pre_only(args):
         print(json.dumps(e))
 
 
+def run_backward_only(args):
+    """`--op backward`: the bf16 backward pass alone on --config (--tokens overrides T). One JSON line."""
+    import torch
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    sys.path.insert(0, str(ROOT))
+    import prime_flash_moe_b200  # noqa: F401
+    e = sweep_backward_entry(args.config, args.tokens or 0, device, measured_peaks())
+    e.update({"metric": "moe_ffn_backward_tflops", "n_gpus": 1, "higher_is_better": True, "data": "synthetic", "impl": "ours"})
+    print(json.dumps(e))
+
+
 def main():
     args = parse_args()
     if args.bpc == 0:
@@ -1179,6 +1242,8 @@ def main():
         run_align_only(args)
     elif args.op == "pre":
         run_pre_only(args)
+    elif args.op == "backward":
+        run_backward_only(args)
     elif args.impl == "cpu":
         run_cpu_arm(args)
     else:

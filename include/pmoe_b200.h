@@ -214,6 +214,10 @@ int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, 
                                  int K, int N, int num_experts, int sorted_num, void *d_x, void *d_w1, void *d_w2,
                                  float *d_topk_weights, void *workspace, size_t workspace_bytes,
                                  pmoe_stream_t stream);
+/* Measurement hook: which steps of the backward pass run. Bits: 1 row maps + row gathers, 2 gate/up recompute,
+ * 4 d_act + SwiGLU derivative, 8 d_w2, 16 d_xs, 32 d_w1, 64 d_x combine; 127 = all (default). Returns the old mask.
+ * With bits missing the outputs are incomplete. */
+int pmoe_debug_set_backward_mask(int mask);
 
 /* ---------------------------------------------------------------------------------------------
  * Expert-parallel glue (no counterpart in the reference, which is single-GPU). Experts are sharded

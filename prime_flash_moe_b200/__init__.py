@@ -121,5 +121,39 @@ def pack_scales_blocked(scales: torch.Tensor) -> torch.Tensor:
     return tiles.reshape(*lead, -1).view(torch.float8_e8m0fnu)
 
 
+def fused_moe_bf16_backward(x, w, w2, d_out, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, top_k):
+    """Gradients of ``fused_moe_bf16`` (bpc = 1 routing tensors): ``(d_x, d_w, d_w2, d_topk_weights)``. The reference
+    is forward-only (README.md:17); the checker is autograd through the fp32 test oracle (test/test.py:13-48)."""
+    return torch.ops.prime_moe.fused_moe_bf16_backward(x, w, w2, d_out.contiguous(), sorted_token_ids, expert_ids,
+                                                       num_tokens_post_padded, topk_weights, top_k)
+
+
+class _MoEFFN(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, w2, topk_ids, topk_weights):
+        num_experts, top_k = w.shape[0], topk_ids.shape[1]
+        sorted_ids, expert_ids, npp = torch.ops.prime_moe.moe_align(topk_ids, num_experts, 128, 1)
+        wts = topk_weights.detach().float().contiguous()
+        out = torch.empty_like(x)
+        torch.ops.prime_moe.fused_moe_bf16(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k, 128, 64, 4, 4, 1, 1, True)
+        ctx.save_for_backward(x, w, w2, sorted_ids, expert_ids, npp, wts)
+        ctx.top_k = top_k
+        ctx.weights_dtype = topk_weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        x, w, w2, sorted_ids, expert_ids, npp, wts = ctx.saved_tensors
+        d_x, d_w, d_w2, d_wt = fused_moe_bf16_backward(x, w, w2, d_out, sorted_ids, expert_ids, npp, wts, ctx.top_k)
+        return d_x, d_w, d_w2, None, d_wt.to(ctx.weights_dtype)
+
+
+def moe_ffn(x, w, w2, topk_ids, topk_weights):
+    """Differentiable bf16 MoE FFN layer: ``moe_align`` + ``fused_moe_bf16`` forward, ``fused_moe_bf16_backward`` for the
+    gradients of ``x``, ``w``, ``w2`` and ``topk_weights`` (only the routed rows' inputs are kept for the backward
+    pass; the gate/up pre-activations are recomputed)."""
+    return _MoEFFN.apply(x, w, w2, topk_ids, topk_weights)
+
+
 __all__ = ["fused_moe_bf16", "fused_moe_mxfp8", "moe_align", "pack_scales_blocked", "route_topk", "route_topk_align", "quantize_mx",
-           "BLOCK"]
+           "fused_moe_bf16_backward", "moe_ffn", "BLOCK"]

@@ -55,6 +55,7 @@ SIGNATURES = {
     "pmoe_quantize_mx": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "pmoe_fused_moe_bf16_backward_workspace_bytes": (_sz, [_i] * 6),
     "pmoe_fused_moe_bf16_backward": (_i, [_vp] * 8 + [_i] * 6 + [_vp] * 5 + [_sz, _vp]),
+    "pmoe_debug_set_backward_mask": (_i, [_i]),
     "pmoe_debug_set_wait_ns": (_i, [C.c_ulonglong]),
     "pmoe_debug_wait_probe": (_i, [_vp]),
     "pmoe_debug_bf16_workspace_extent": (_sz, [_i] * 8),

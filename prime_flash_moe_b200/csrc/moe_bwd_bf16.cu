@@ -478,6 +478,10 @@ int bf16_map(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uin
 
 }  // namespace
 
+// which steps of the backward pass run (pmoe_debug_set_backward_mask): 1 row maps + gathers, 2 gate/up recompute,
+// 4 d_act + SwiGLU derivative, 8 d_w2, 16 d_xs, 32 d_w1, 64 d_x combine
+int g_bwd_mask = 127;
+
 int wait_ns_store_bwd(unsigned long long ns) {
     PMOE_CUDA_OK(cudaMemcpyToSymbol(g_wait_ns, &ns, sizeof(ns)));
     return PMOE_OK;
@@ -493,6 +497,12 @@ int status_fetch_bwd(int *value, bool reset) {
 }
 
 }  // namespace pmoe
+
+extern "C" int pmoe_debug_set_backward_mask(int mask) {
+    const int old = pmoe::g_bwd_mask;
+    pmoe::g_bwd_mask = mask & 127;
+    return old;
+}
 
 extern "C" size_t pmoe_fused_moe_bf16_backward_workspace_bytes(int T, int K, int N, int num_experts, int top_k,
                                                                int sorted_num) {
@@ -544,22 +554,26 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     auto *eblk = reinterpret_cast<int32_t *>(ws + lay.eblk);
     const uint64_t R = static_cast<uint64_t>(sorted_num);
 
-    PMOE_CUDA_OK(cudaMemsetAsync(inv, 0xFF, static_cast<size_t>(T) * top_k * sizeof(int32_t), stream));
-    PMOE_CUDA_OK(cudaMemsetAsync(eblk, 0, 2 * static_cast<size_t>(E) * sizeof(int32_t), stream));
-    if (d_topk_weights)
-        PMOE_CUDA_OK(cudaMemsetAsync(d_topk_weights, 0, static_cast<size_t>(T) * top_k * sizeof(float), stream));
-    const int small_grid = std::max(1, std::min(sorted_num / 256 + 1, 8 * sm_count()));
-    row_maps_kernel<<<small_grid, 256, 0, stream>>>(sorted_token_ids, expert_ids, num_tokens_post_padded, sorted_num,
-                                                    top_k, T, E, inv, eblk);
-    PMOE_CUDA_OK(cudaGetLastError());
+    const int mask = g_bwd_mask;
     const int copy_grid = 8 * sm_count();
-    gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), sorted_token_ids,
-                                                            num_tokens_post_padded, sorted_num, top_k, T, K, xs);
-    PMOE_CUDA_OK(cudaGetLastError());
-    gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d_out),
-                                                            sorted_token_ids, num_tokens_post_padded, sorted_num,
-                                                            top_k, T, K, dos);
-    PMOE_CUDA_OK(cudaGetLastError());
+    if (mask & 1) {
+        PMOE_CUDA_OK(cudaMemsetAsync(inv, 0xFF, static_cast<size_t>(T) * top_k * sizeof(int32_t), stream));
+        PMOE_CUDA_OK(cudaMemsetAsync(eblk, 0, 2 * static_cast<size_t>(E) * sizeof(int32_t), stream));
+        const int small_grid = std::max(1, std::min(sorted_num / 256 + 1, 8 * sm_count()));
+        row_maps_kernel<<<small_grid, 256, 0, stream>>>(sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                                        sorted_num, top_k, T, E, inv, eblk);
+        PMOE_CUDA_OK(cudaGetLastError());
+        gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x),
+                                                                sorted_token_ids, num_tokens_post_padded, sorted_num,
+                                                                top_k, T, K, xs);
+        PMOE_CUDA_OK(cudaGetLastError());
+        gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d_out),
+                                                                sorted_token_ids, num_tokens_post_padded, sorted_num,
+                                                                top_k, T, K, dos);
+        PMOE_CUDA_OK(cudaGetLastError());
+    }
+    if ((mask & 4) && d_topk_weights)
+        PMOE_CUDA_OK(cudaMemsetAsync(d_topk_weights, 0, static_cast<size_t>(T) * top_k * sizeof(float), stream));
 
     CUtensorMap xs_k, xs_mn, dos_k, dos_mn, dgu_k, dgu_mn, actw_mn, w1_k, w1_mn, w2_mn;
     if (int rc = bf16_map(&xs_k, xs, R, K, 128, "xs rows")) return rc;
@@ -578,37 +592,39 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     base.sorted_num = sorted_num, base.eblk = eblk, base.topk_weights = topk_weights;
     base.top_k = top_k, base.tokens = T, base.E = E, base.H = H, base.N = N;
 
-    {   // gate | up pre-activations: gu = xs . W1[e]^T
+    if (mask & 2) {   // gate | up pre-activations: gu = xs . W1[e]^T
         GArgs g = base;
         g.mode = MODE_NT_STORE, g.ksteps = K / 64, g.n_tiles = (N + 255) / 256, g.b_rows_per_expert = N;
         g.c = gu, g.ldc = N, g.c_cols = N;
         if (int rc = launch_gemm(xs_k, w1_k, g, stream)) return rc;
     }
-    {   // d_act = wt * (dos . W2[e]) -> d_gu, wt * act, d_wt
+    if (mask & 4) {   // d_act = wt * (dos . W2[e]) -> d_gu, wt * act, d_wt
         GArgs g = base;
         g.mode = MODE_NN_SWIGLU, g.ksteps = K / 64, g.n_tiles = (H + 255) / 256, g.b_rows_per_expert = K;
         g.gu = gu, g.dgu = dgu, g.actw = actw, g.dwt = d_topk_weights;
         if (int rc = launch_gemm(dos_k, w2_mn, g, stream)) return rc;
     }
-    {   // d_W2[e] [K, H] = dos_e^T . (wt * act)_e
+    if (mask & 8) {   // d_W2[e] [K, H] = dos_e^T . (wt * act)_e
         GArgs g = base;
         g.mode = MODE_WGRAD, g.m_tiles = (K + 127) / 128, g.n_tiles = (H + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w2), g.ldc = H, g.c_cols = H, g.c_rows = K;
         if (int rc = launch_gemm(dos_mn, actw_mn, g, stream)) return rc;
     }
-    {   // d_xs = d_gu . W1[e], written over dos (dead from here on)
+    if (mask & 16) {   // d_xs = d_gu . W1[e], written over dos (dead from here on)
         GArgs g = base;
         g.mode = MODE_NN_STORE, g.ksteps = N / 64, g.n_tiles = (K + 255) / 256, g.b_rows_per_expert = N;
         g.c = dos, g.ldc = K, g.c_cols = K;
         if (int rc = launch_gemm(dgu_k, w1_mn, g, stream)) return rc;
     }
-    {   // d_W1[e] [N, K] = d_gu_e^T . xs_e
+    if (mask & 32) {   // d_W1[e] [N, K] = d_gu_e^T . xs_e
         GArgs g = base;
         g.mode = MODE_WGRAD, g.m_tiles = (N + 127) / 128, g.n_tiles = (K + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w1), g.ldc = K, g.c_cols = K, g.c_rows = N;
         if (int rc = launch_gemm(dgu_mn, xs_mn, g, stream)) return rc;
     }
-    combine_dx_kernel<<<copy_grid, 256, 0, stream>>>(dos, inv, top_k, T, K, static_cast<__nv_bfloat16 *>(d_x));
-    PMOE_CUDA_OK(cudaGetLastError());
+    if (mask & 64) {
+        combine_dx_kernel<<<copy_grid, 256, 0, stream>>>(dos, inv, top_k, T, K, static_cast<__nv_bfloat16 *>(d_x));
+        PMOE_CUDA_OK(cudaGetLastError());
+    }
     return PMOE_OK;
 }

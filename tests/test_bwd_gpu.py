@@ -88,3 +88,17 @@ def test_argument_checks():
     with pytest.raises(RuntimeError, match="workspace"):
         capi.fused_moe_bf16_backward(x.to(DEV), w1.to(DEV), w2.to(DEV), x.to(DEV), s, e, n, wts.to(DEV), 1,
                                      workspace=small[(-small.data_ptr()) % 1024:][:1024])
+
+
+def test_autograd_layer_matches_oracle_gradients():
+    import prime_flash_moe_b200 as P
+    T, K, E, N, k = 200, 512, 6, 512, 3
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=11)
+    d_out = torch.randn(T, K, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    refs = O.moe_backward_ref_fp32(x, w1, w2, ids, wts, d_out)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (x, w1, w2, wts)]
+    out = P.moe_ffn(leaves[0], leaves[1], leaves[2], ids.to(DEV), leaves[3])
+    assert O.max_rel_to_peak(out.detach().cpu(), O.moe_ref_fp32(x, w1, w2, ids, wts)) <= TOL
+    out.backward(d_out.to(DEV))
+    torch.cuda.synchronize()
+    check(tuple(t.grad.cpu() for t in leaves), refs)
