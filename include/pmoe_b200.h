@@ -205,7 +205,7 @@ int pmoe_quantize_mx(const void *x /* bf16[src_rows, K] */, const int32_t *row_i
  *   d_topk_weights fp32[T, top_k], or NULL to skip it (entries of routes to ids outside [0, E) stay 0)
  * The gate/up pre-activations are recomputed from x (nothing is kept from the forward call), products accumulate
  * in fp32 and every intermediate is rounded to bf16 once. K % 64 == 0, N % 128 == 0, sorted_num % 128 == 0,
- * tensors 16-byte aligned, workspace 1024-byte aligned with pmoe_fused_moe_bf16_backward_workspace_bytes() bytes.
+ * tensors 16-byte aligned (d_w1, d_w2: 32), workspace 1024-byte aligned with pmoe_fused_moe_bf16_backward_workspace_bytes() bytes.
  * Asynchronous on `stream`; bounded waits and status reporting as for the forward kernels. */
 size_t pmoe_fused_moe_bf16_backward_workspace_bytes(int T, int K, int N, int num_experts, int top_k, int sorted_num);
 int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, const void *d_out,

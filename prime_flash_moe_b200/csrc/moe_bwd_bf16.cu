@@ -201,27 +201,31 @@ __device__ __forceinline__ Tile decode_tile(const GArgs &a, int t, int m_blocks)
     return tl;
 }
 
+// 32 fp32 -> 32 bf16 = 64 contiguous bytes as two 256-bit stores (every store fills a whole 32-byte sector, so a
+// warp whose lanes hold different rows still writes full sectors); `dst` must be 32-byte aligned
 __device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16 *dst, const float (&v)[32]) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        uint4 o;
-        o.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
-        o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
-        o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
-        o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
-        reinterpret_cast<uint4 *>(dst)[j] = o;
+    for (int j = 0; j < 2; ++j) {
+        uint32_t w[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) w[q] = pack_bf16x2(v[16 * j + 2 * q], v[16 * j + 2 * q + 1]);
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * j), "r"(w[0]), "r"(w[1]),
+                     "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                     : "memory");
     }
 }
 
 __device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16 *src, float (&v)[32]) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint4 raw = reinterpret_cast<const uint4 *>(src)[j];
-        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+    for (int j = 0; j < 2; ++j) {
+        uint32_t w[8];
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                     : "l"(src + 16 * j));
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            v[8 * j + 2 * q] = __low2float(h[q]);
-            v[8 * j + 2 * q + 1] = __high2float(h[q]);
+        for (int q = 0; q < 8; ++q) {
+            v[16 * j + 2 * q] = __uint_as_float(w[q] << 16);
+            v[16 * j + 2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
         }
     }
 }
@@ -361,7 +365,7 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
                         if (col0 + ch * 32 < a.c_cols)
                             for (int j = 0; j < 4; ++j)
-                                reinterpret_cast<uint4 *>(dst + ch * 32)[j] = make_uint4(0, 0, 0, 0);
+                                reinterpret_cast<uint4 *>(dst + ch * 32)[j] = make_uint4(0, 0, 0, 0);   // rare path
                 }
                 continue;
             }
@@ -532,6 +536,8 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
                           reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_w1) |
                           reinterpret_cast<uintptr_t>(d_w2);
     PMOE_REQUIRE((all & 15) == 0, PMOE_ERR_BAD_ARG, "fused_moe_bf16_backward: tensors must be 16-byte aligned");
+    PMOE_REQUIRE(((reinterpret_cast<uintptr_t>(d_w1) | reinterpret_cast<uintptr_t>(d_w2)) & 31) == 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_backward: d_w1 and d_w2 must be 32-byte aligned (256-bit stores)");
     const int H = N / 2, E = num_experts;
     const size_t w1_bytes = static_cast<size_t>(E) * N * K * 2, w2_bytes = static_cast<size_t>(E) * K * H * 2;
     if (T == 0 || sorted_num == 0) {   // no routed row: every gradient is zero
