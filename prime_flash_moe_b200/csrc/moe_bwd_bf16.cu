@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -432,6 +433,184 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------
+// weight-gradient GEMM on CTA pairs (cluster of 2, tcgen05 cta_group::2, M = 256): the pair computes 256 rows of
+// one expert's gradient x 256 columns. Each CTA loads its own 128 M indices of A and its own 128 N indices of B
+// (two 64 x 64 boxes each: 32 KB per ring slot and CTA instead of 48 KB, six slots), the even CTA issues the MMAs
+// for both, each CTA drains the accumulator rows of its half. No multicast loads; ring slots and accumulators are
+// released to both CTAs by multicast tcgen05.commit.
+//   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2] (even CTA; both CTAs' epilogue warps arrive there)
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t PAIR_STAGE_BYTES = 4 * BOX_BYTES;   // 32 KB
+constexpr int PAIR_STAGES = 6;
+constexpr size_t PAIR_SMEM_BYTES = 1024 + static_cast<size_t>(PAIR_STAGES) * PAIR_STAGE_BYTES + 256;
+
+struct RingPair {
+    uint32_t ring, bars;
+    __device__ __forceinline__ uint32_t a(int s) const { return ring + s * PAIR_STAGE_BYTES; }
+    __device__ __forceinline__ uint32_t b(int s) const { return ring + s * PAIR_STAGE_BYTES + 2 * BOX_BYTES; }
+    __device__ __forceinline__ uint32_t full(int s) const { return bars + 8 * s; }
+    __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8 * (PAIR_STAGES + s); }
+    __device__ __forceinline__ uint32_t misc(int i) const { return bars + 8 * (2 * PAIR_STAGES + i); }
+    __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * PAIR_STAGES + 4); }
+};
+
+struct PairTile {
+    int e, mt2, nt, k0, k1;
+};
+__device__ __forceinline__ PairTile decode_pair_tile(const GArgs &a, int t, int m_tiles2) {
+    PairTile tl;
+    const int per = m_tiles2 * a.n_tiles;
+    tl.e = t / per;
+    const int rem = t - tl.e * per;
+    tl.mt2 = rem % m_tiles2;
+    tl.nt = rem / m_tiles2;
+    tl.k0 = 2 * a.eblk[tl.e];
+    tl.k1 = 2 * a.eblk[a.E + tl.e];
+    return tl;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const GArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    RingPair sm;
+    sm.ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    sm.bars = sm.ring + PAIR_STAGES * PAIR_STAGE_BYTES;
+    int *status = &g_status_bwd;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(sm.full(s), 1);
+            mbar_init(sm.empty(s), 1);
+        }
+        mbar_init(sm.misc(0), 1);
+        mbar_init(sm.misc(1), 1);
+        mbar_init(sm.misc(2), 2 * EPI_WARPS * 32);
+        mbar_init(sm.misc(3), 2 * EPI_WARPS * 32);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) tmem_alloc_pair(sm.tmem_slot(), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // both CTAs' barriers are initialised and both halves of TMEM allocated
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
+
+    const int m_tiles2 = (a.c_rows + 255) / 256;
+    const int num_tiles = a.E * m_tiles2 * a.n_tiles;
+    const int first = blockIdx.x >> 1, step = gridDim.x >> 1;   // this pair's tile sequence
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = first; t < num_tiles && ok; t += step) {
+                const PairTile tl = decode_pair_tile(a, t, m_tiles2);
+                const int m0 = tl.mt2 * 256 + static_cast<int>(rank) * 128;
+                const int n0 = tl.nt * BN + static_cast<int>(rank) * 128;
+                for (int ks = tl.k0; ks < tl.k1; ++ks) {
+                    ok = mbar_wait_cluster(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    const uint32_t full_leader = mapa_shared(sm.full(s), 0);
+                    if (leader) mbar_arrive_expect_tx(sm.full(s), 2 * PAIR_STAGE_BYTES);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        tma_load_2d_pair(sm.a(s) + i * BOX_BYTES, &map_a, full_leader, m0 + i * 64, ks * 64);
+                        tma_load_2d_pair(sm.b(s) + i * BOX_BYTES, &map_b, full_leader, n0 + i * 64, ks * 64);
+                    }
+                    if (++s == PAIR_STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = idesc_bf16_f32(256, 256) | (1u << 15) | (1u << 16);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = first; t < num_tiles && ok; t += step) {
+                const PairTile tl = decode_pair_tile(a, t, m_tiles2);
+                if (tl.k1 <= tl.k0) continue;
+                const int buf = it & 1;
+                ok = mbar_wait_cluster(sm.misc(2 + buf), ((it >> 1) & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BN;
+                for (int ks = tl.k0; ks < tl.k1; ++ks) {
+                    ok = mbar_wait_cluster(sm.full(s), ph, status, ST_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16_pair(d, smem_desc_mn_sw128(sm.a(s) + k * 2048), smem_desc_mn_sw128(sm.b(s) + k * 2048),
+                                      idesc, (ks != tl.k0) || (k != 0));
+                    umma_commit_pair(sm.empty(s), 3);
+                    if (++s == PAIR_STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok) umma_commit_pair(sm.misc(buf), 3);
+                ++it;
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        const int cg = ew / 4;
+        int it = 0;
+        for (int t = first; t < num_tiles; t += step) {
+            const PairTile tl = decode_pair_tile(a, t, m_tiles2);
+            const int col0 = tl.nt * BN;
+            const int m = tl.mt2 * 256 + static_cast<int>(rank) * 128 + row;
+            const bool row_ok = m < a.c_rows;
+            __nv_bfloat16 *dst = a.c + (static_cast<size_t>(tl.e) * a.c_rows + (row_ok ? m : 0)) * a.ldc + col0;
+            if (tl.k1 <= tl.k0) {      // an expert without rows: its weight gradient is zero
+                if (row_ok)
+                    for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
+                        if (col0 + ch * 32 < a.c_cols)
+                            for (int j = 0; j < 4; ++j)
+                                reinterpret_cast<uint4 *>(dst + ch * 32)[j] = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const int buf = it & 1;
+            if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * BN;
+            for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
+                if (col0 + ch * 32 >= a.c_cols) break;
+                float v[32];
+                tmem_ld_32x32(v, tmem_addr(acc, lane_base, ch * 32));
+                tmem_ld_wait();
+                if (row_ok) store_chunk_bf16(dst + ch * 32, v);
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(mapa_shared(sm.misc(2 + buf), 0));
+            ++it;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // nobody frees TMEM or exits while the peer may still use this CTA's memory
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------
@@ -472,6 +651,43 @@ int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cu
     }
     moe_bwd_gemm_kernel<<<sm_count(), THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
     PMOE_CUDA_OK(cudaGetLastError());
+    return PMOE_OK;
+}
+
+// PMOE_BWD_PAIRS=0 / 1: CTA pairs never / always; unset (-1): when an expert has 256 routed rows or more on average
+// (below that the weight-gradient launches are bound by their stores, and the pairs measured slower)
+int pairs_mode() {
+    const char *v = getenv("PMOE_BWD_PAIRS");
+    return (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
+}
+
+int launch_wgrad_pair(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    PMOE_CUDA_OK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        PMOE_CUDA_OK(cudaFuncSetAttribute(moe_bwd_wgrad_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(PAIR_SMEM_BYTES)));
+        configured[dev] = true;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(2);
+    int max_clusters = 0;
+    PMOE_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, moe_bwd_wgrad_pair_kernel, &cfg));
+    if (max_clusters < 1) return set_error(PMOE_ERR_CUDA, "no CTA pair of the weight-gradient kernel fits on this device");
+    const long long tiles = static_cast<long long>(g.E) * ((g.c_rows + 255) / 256) * g.n_tiles;
+    cfg.gridDim = dim3(2 * static_cast<unsigned>(std::min<long long>(tiles, max_clusters)));
+    PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_bwd_wgrad_pair_kernel, ma, mb, g));
     return PMOE_OK;
 }
 
@@ -561,6 +777,8 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     const uint64_t R = static_cast<uint64_t>(sorted_num);
 
     const int mask = g_bwd_mask;
+    const int pm = pairs_mode();
+    const bool pairs = pm >= 0 ? pm == 1 : static_cast<long long>(T) * top_k >= 256ll * E;
     const int copy_grid = 8 * sm_count();
     if (mask & 1) {
         PMOE_CUDA_OK(cudaMemsetAsync(inv, 0xFF, static_cast<size_t>(T) * top_k * sizeof(int32_t), stream));
@@ -614,7 +832,7 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
         GArgs g = base;
         g.mode = MODE_WGRAD, g.m_tiles = (K + 127) / 128, g.n_tiles = (H + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w2), g.ldc = H, g.c_cols = H, g.c_rows = K;
-        if (int rc = launch_gemm(dos_mn, actw_mn, g, stream)) return rc;
+        if (int rc = (pairs ? launch_wgrad_pair : launch_gemm)(dos_mn, actw_mn, g, stream)) return rc;
     }
     if (mask & 16) {   // d_xs = d_gu . W1[e], written over dos (dead from here on)
         GArgs g = base;
@@ -626,7 +844,7 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
         GArgs g = base;
         g.mode = MODE_WGRAD, g.m_tiles = (N + 127) / 128, g.n_tiles = (K + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w1), g.ldc = K, g.c_cols = K, g.c_rows = N;
-        if (int rc = launch_gemm(dgu_mn, xs_mn, g, stream)) return rc;
+        if (int rc = (pairs ? launch_wgrad_pair : launch_gemm)(dgu_mn, xs_mn, g, stream)) return rc;
     }
     if (mask & 64) {
         combine_dx_kernel<<<copy_grid, 256, 0, stream>>>(dos, inv, top_k, T, K, static_cast<__nv_bfloat16 *>(d_x));
