@@ -59,6 +59,8 @@ struct GArgs {
     const int32_t *sorted_ids, *expert_ids, *npp;
     int sorted_num;
     const int32_t *eblk;          // MODE_WGRAD: first / one-past-last row block of every expert, [2 * E]
+    const int32_t *items;         // row-space modes: the row blocks of this launch (pair kernel: first block of each
+    const int32_t *item_count;    //   pair) and their number on the device; null = every live row block
     const float *topk_weights;
     int top_k, tokens, E;
     int ksteps;                   // modes 0-2: contraction length / 64
@@ -179,9 +181,15 @@ struct Tile {
     int mb, nt, e, mt, k0, k1;
 };
 
-__device__ __forceinline__ Tile decode_tile(const GArgs &a, int t, int m_blocks) {
+// row-space modes: the row blocks of this launch are either all live ones or those named by a.items
+__device__ __forceinline__ int num_row_items(const GArgs &a) {
+    return a.items ? *a.item_count : live_row_blocks(a.npp, a.sorted_num);
+}
+
+template <int MODE>
+__device__ __forceinline__ Tile decode_tile(const GArgs &a, int t, int m_items) {
     Tile tl;
-    if (a.mode == MODE_WGRAD) {
+    if (MODE == MODE_WGRAD) {
         const int per = a.m_tiles * a.n_tiles;
         tl.e = t / per;
         const int rem = t - tl.e * per;
@@ -191,11 +199,11 @@ __device__ __forceinline__ Tile decode_tile(const GArgs &a, int t, int m_blocks)
         tl.k0 = 2 * a.eblk[tl.e];              // k-step = 64-row chunk of the sorted row space
         tl.k1 = 2 * a.eblk[a.E + tl.e];
     } else {
-        const Coord c = tile_coord(t, m_blocks, a.n_tiles);
-        tl.mb = c.m_blk;
+        const Coord c = tile_coord(t, m_items, a.n_tiles);
+        tl.mb = a.items ? a.items[c.m_blk] : c.m_blk;
         tl.nt = c.n_tile;
         tl.mt = 0;
-        tl.e = max(0, min(a.E - 1, a.expert_ids[c.m_blk]));
+        tl.e = max(0, min(a.E - 1, a.expert_ids[tl.mb]));
         tl.k0 = 0;
         tl.k1 = a.ksteps;
     }
@@ -231,6 +239,73 @@ __device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16 *src, float 
     }
 }
 
+
+
+// Epilogue of one finished accumulator (128 rows x 256 columns at TMEM `acc`), shared by both GEMM kernels: thread
+// = row `row` of the accumulator, column chunks cg*4 .. cg*4+3 (32 columns each). Row-space modes: `mb` = row
+// block; MODE_WGRAD: `m` = row of the expert's gradient matrix.
+template <int MODE>
+__device__ __forceinline__ void drain_tile(const GArgs &a, uint32_t acc, uint32_t lane_base, int row, int cg, int mb,
+                                           int e, int m, int col0) {
+    if (MODE == MODE_NN_SWIGLU) {
+        const size_t row_g = static_cast<size_t>(mb) * BM + row;
+        const int pair = a.sorted_ids[row_g];
+        const bool valid = pair >= 0 && pair < a.tokens * a.top_k;
+        const float wt = valid ? a.topk_weights[pair] : 0.f;
+        float part = 0.f;
+        for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
+            const int h0 = col0 + ch * 32;
+            if (h0 >= a.H) break;
+            float c[32], g[32], u[32];
+            tmem_ld_32x32(c, tmem_addr(acc, lane_base, ch * 32));
+            load_chunk_bf16(a.gu + row_g * a.N + h0, g);
+            load_chunk_bf16(a.gu + row_g * a.N + a.H + h0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float s = 1.f / (1.f + __expf(-g[j]));
+                const float silu = g[j] * s;
+                const float act = silu * u[j];
+                const float d = wt * c[j];
+                part += c[j] * act;
+                c[j] = wt * act;                                   // -> actw
+                g[j] = d * u[j] * s * (1.f + g[j] * (1.f - s));    // -> d_gate
+                u[j] = d * silu;                                   // -> d_up
+            }
+            store_chunk_bf16(a.actw + row_g * a.H + h0, c);
+            store_chunk_bf16(a.dgu + row_g * a.N + h0, g);
+            store_chunk_bf16(a.dgu + row_g * a.N + a.H + h0, u);
+        }
+        if (a.dwt && valid) atomicAdd(a.dwt + pair, part);
+        return;
+    }
+    __nv_bfloat16 *dst;
+    bool row_ok = true;
+    if (MODE == MODE_WGRAD) {
+        row_ok = m < a.c_rows;
+        dst = a.c + (static_cast<size_t>(e) * a.c_rows + (row_ok ? m : 0)) * a.ldc + col0;
+    } else {
+        dst = a.c + (static_cast<size_t>(mb) * BM + row) * a.ldc + col0;
+    }
+    for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
+        if (col0 + ch * 32 >= a.c_cols) break;
+        float v[32];
+        tmem_ld_32x32(v, tmem_addr(acc, lane_base, ch * 32));
+        tmem_ld_wait();
+        if (row_ok) store_chunk_bf16(dst + ch * 32, v);
+    }
+}
+
+// MODE_WGRAD, an expert without rows: its weight gradient is zero (no accumulator involved)
+__device__ __forceinline__ void zero_tile(const GArgs &a, int cg, int e, int m, int col0) {
+    if (m >= a.c_rows) return;
+    __nv_bfloat16 *dst = a.c + (static_cast<size_t>(e) * a.c_rows + m) * a.ldc + col0;
+    for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
+        if (col0 + ch * 32 < a.c_cols)
+            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4 *>(dst + ch * 32)[j] = make_uint4(0, 0, 0, 0);
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GArgs a) {
@@ -261,10 +336,10 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
 
-    const int m_blocks = live_row_blocks(a.npp, a.sorted_num);
-    const int num_tiles = a.mode == MODE_WGRAD ? a.E * a.m_tiles * a.n_tiles : m_blocks * a.n_tiles;
-    const bool a_mn = a.mode == MODE_WGRAD;
-    const bool b_mn = a.mode != MODE_NT_STORE;
+    constexpr bool a_mn = MODE == MODE_WGRAD;
+    constexpr bool b_mn = MODE != MODE_NT_STORE;
+    const int m_items = a_mn ? 0 : num_row_items(a);
+    const int num_tiles = a_mn ? a.E * a.m_tiles * a.n_tiles : m_items * a.n_tiles;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -273,7 +348,7 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             long long issued = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const Tile tl = decode_tile(a, t, m_blocks);
+                const Tile tl = decode_tile<MODE>(a, t, m_items);
                 for (int ks = tl.k0; ks < tl.k1; ++ks) {
                     ok = mbar_wait(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
@@ -288,7 +363,7 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!b_mn) {
                         tma_load_2d(sm.b(s), &map_b, sm.full(s), ks * BK, tl.e * a.b_rows_per_expert + tl.nt * BN);
                     } else {
-                        const int krow = a.mode == MODE_WGRAD ? ks * 64 : tl.e * a.b_rows_per_expert + ks * 64;
+                        const int krow = a_mn ? ks * 64 : tl.e * a.b_rows_per_expert + ks * 64;
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             tma_load_2d(sm.b(s) + j * BOX_BYTES, &map_b, sm.full(s), tl.nt * BN + j * 64, krow);
@@ -315,13 +390,13 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = idesc_bf16_f32(BM, BN) | (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN) | (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
             int s = 0;
             uint32_t ph = 0;
             int it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const Tile tl = decode_tile(a, t, m_blocks);
+                const Tile tl = decode_tile<MODE>(a, t, m_items);
                 if (tl.k1 <= tl.k0) continue;
                 const int buf = it & 1;
                 ok = mbar_wait(sm.misc(2 + buf), ((it >> 1) & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
@@ -356,72 +431,17 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int cg = ew / 4;
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-            const Tile tl = decode_tile(a, t, m_blocks);
+            const Tile tl = decode_tile<MODE>(a, t, m_items);
             const int col0 = tl.nt * BN;
+            const int m = tl.mt * BM + row;
             if (tl.k1 <= tl.k0) {
-                // an expert without rows: its weight gradient is zero
-                const int m = tl.mt * BM + row;
-                if (m < a.c_rows) {
-                    __nv_bfloat16 *dst = a.c + (static_cast<size_t>(tl.e) * a.c_rows + m) * a.ldc + col0;
-                    for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
-                        if (col0 + ch * 32 < a.c_cols)
-                            for (int j = 0; j < 4; ++j)
-                                reinterpret_cast<uint4 *>(dst + ch * 32)[j] = make_uint4(0, 0, 0, 0);   // rare path
-                }
+                zero_tile(a, cg, tl.e, m, col0);
                 continue;
             }
             const int buf = it & 1;
             if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
             tc_fence_after();
-            const uint32_t acc = tmem_base + buf * BN;
-            if (a.mode == MODE_NN_SWIGLU) {
-                const size_t row_g = static_cast<size_t>(tl.mb) * BM + row;
-                const int pair = a.sorted_ids[row_g];
-                const bool valid = pair >= 0 && pair < a.tokens * a.top_k;
-                const float wt = valid ? a.topk_weights[pair] : 0.f;
-                float part = 0.f;
-                for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
-                    const int h0 = col0 + ch * 32;
-                    if (h0 >= a.H) break;
-                    float c[32], g[32], u[32];
-                    tmem_ld_32x32(c, tmem_addr(acc, lane_base, ch * 32));
-                    load_chunk_bf16(a.gu + row_g * a.N + h0, g);
-                    load_chunk_bf16(a.gu + row_g * a.N + a.H + h0, u);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float s = 1.f / (1.f + __expf(-g[j]));
-                        const float silu = g[j] * s;
-                        const float act = silu * u[j];
-                        const float d = wt * c[j];
-                        part += c[j] * act;
-                        c[j] = wt * act;                                   // -> actw
-                        g[j] = d * u[j] * s * (1.f + g[j] * (1.f - s));    // -> d_gate
-                        u[j] = d * silu;                                   // -> d_up
-                    }
-                    store_chunk_bf16(a.actw + row_g * a.H + h0, c);
-                    store_chunk_bf16(a.dgu + row_g * a.N + h0, g);
-                    store_chunk_bf16(a.dgu + row_g * a.N + a.H + h0, u);
-                }
-                if (a.dwt && valid) atomicAdd(a.dwt + pair, part);
-            } else {
-                __nv_bfloat16 *dst;
-                bool row_ok = true;
-                if (a.mode == MODE_WGRAD) {
-                    const int m = tl.mt * BM + row;
-                    row_ok = m < a.c_rows;
-                    dst = a.c + (static_cast<size_t>(tl.e) * a.c_rows + (row_ok ? m : 0)) * a.ldc + col0;
-                } else {
-                    dst = a.c + (static_cast<size_t>(tl.mb) * BM + row) * a.ldc + col0;
-                }
-                for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
-                    if (col0 + ch * 32 >= a.c_cols) break;
-                    float v[32];
-                    tmem_ld_32x32(v, tmem_addr(acc, lane_base, ch * 32));
-                    tmem_ld_wait();
-                    if (row_ok) store_chunk_bf16(dst + ch * 32, v);
-                }
-            }
+            drain_tile<MODE>(a, tmem_base + buf * BN, lane_base, row, cg, tl.mb, tl.e, m, col0);
             tc_fence_before();
             mbar_arrive(sm.misc(2 + buf));
             ++it;
@@ -434,11 +454,12 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------------
-// weight-gradient GEMM on CTA pairs (cluster of 2, tcgen05 cta_group::2, M = 256): the pair computes 256 rows of
-// one expert's gradient x 256 columns. Each CTA loads its own 128 M indices of A and its own 128 N indices of B
-// (two 64 x 64 boxes each: 32 KB per ring slot and CTA instead of 48 KB, six slots), the even CTA issues the MMAs
-// for both, each CTA drains the accumulator rows of its half. No multicast loads; ring slots and accumulators are
-// released to both CTAs by multicast tcgen05.commit.
+// The same GEMMs on CTA pairs (cluster of 2, tcgen05 cta_group::2, M = 256). Row-space modes: the pair takes two
+// row blocks of one expert (a.items lists the first block of every such pair; the odd last block of an expert goes
+// to the one-CTA kernel). MODE_WGRAD: 256 rows of the expert's gradient matrix. Each CTA loads its own 128 rows /
+// M indices of A and its own 128 of the tile's 256 N indices of B: 32 KB per ring slot and CTA instead of 48 KB
+// (six slots), the even CTA issues the MMAs for both, each CTA drains the accumulator rows of its half. No
+// multicast loads; ring slots and accumulators are released to both CTAs by multicast tcgen05.commit.
 //   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2] (even CTA; both CTAs' epilogue warps arrive there)
 // ---------------------------------------------------------------------------------------------
 constexpr uint32_t PAIR_STAGE_BYTES = 4 * BOX_BYTES;   // 32 KB
@@ -455,24 +476,35 @@ struct RingPair {
     __device__ __forceinline__ uint32_t tmem_slot() const { return bars + 8 * (2 * PAIR_STAGES + 4); }
 };
 
-struct PairTile {
-    int e, mt2, nt, k0, k1;
-};
-__device__ __forceinline__ PairTile decode_pair_tile(const GArgs &a, int t, int m_tiles2) {
-    PairTile tl;
-    const int per = m_tiles2 * a.n_tiles;
-    tl.e = t / per;
-    const int rem = t - tl.e * per;
-    tl.mt2 = rem % m_tiles2;
-    tl.nt = rem / m_tiles2;
-    tl.k0 = 2 * a.eblk[tl.e];
-    tl.k1 = 2 * a.eblk[a.E + tl.e];
+// tile of a pair: row-space modes mb = first row block of the pair; MODE_WGRAD mt = 256-row tile of the gradient
+template <int MODE>
+__device__ __forceinline__ Tile decode_pair_tile(const GArgs &a, int t, int m_items, int m_tiles2) {
+    Tile tl;
+    if (MODE == MODE_WGRAD) {
+        const int per = m_tiles2 * a.n_tiles;
+        tl.e = t / per;
+        const int rem = t - tl.e * per;
+        tl.mt = rem % m_tiles2;
+        tl.nt = rem / m_tiles2;
+        tl.mb = 0;
+        tl.k0 = 2 * a.eblk[tl.e];
+        tl.k1 = 2 * a.eblk[a.E + tl.e];
+    } else {
+        const Coord c = tile_coord(t, m_items, a.n_tiles);
+        tl.mb = a.items[c.m_blk];
+        tl.nt = c.n_tile;
+        tl.mt = 0;
+        tl.e = max(0, min(a.E - 1, a.expert_ids[tl.mb]));
+        tl.k0 = 0;
+        tl.k1 = a.ksteps;
+    }
     return tl;
 }
 
+template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
-moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                          const GArgs a) {
+moe_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GArgs a) {
     extern __shared__ uint8_t smem_raw[];
     RingPair sm;
     sm.ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -503,8 +535,11 @@ moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
 
+    constexpr bool wgrad = MODE == MODE_WGRAD;
+    constexpr bool b_mn = MODE != MODE_NT_STORE;
     const int m_tiles2 = (a.c_rows + 255) / 256;
-    const int num_tiles = a.E * m_tiles2 * a.n_tiles;
+    const int m_items = wgrad ? 0 : *a.item_count;
+    const int num_tiles = wgrad ? a.E * m_tiles2 * a.n_tiles : m_items * a.n_tiles;
     const int first = blockIdx.x >> 1, step = gridDim.x >> 1;   // this pair's tile sequence
 
     if (warp == 0) {
@@ -513,18 +548,29 @@ moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             uint32_t ph = 0;
             bool ok = true;
             for (int t = first; t < num_tiles && ok; t += step) {
-                const PairTile tl = decode_pair_tile(a, t, m_tiles2);
-                const int m0 = tl.mt2 * 256 + static_cast<int>(rank) * 128;
-                const int n0 = tl.nt * BN + static_cast<int>(rank) * 128;
+                const Tile tl = decode_pair_tile<MODE>(a, t, m_items, m_tiles2);
+                const int m0 = tl.mt * 256 + static_cast<int>(rank) * 128;      // wgrad: this CTA's M indices
+                const int blk = tl.mb + static_cast<int>(rank);                 // row space: this CTA's row block
+                const int n0 = tl.nt * BN + static_cast<int>(rank) * 128;       // this CTA's N indices of B
                 for (int ks = tl.k0; ks < tl.k1; ++ks) {
                     ok = mbar_wait_cluster(sm.empty(s), ph ^ 1, status, ST_TIMEOUT_EMPTY);
                     if (!ok) break;
                     const uint32_t full_leader = mapa_shared(sm.full(s), 0);
                     if (leader) mbar_arrive_expect_tx(sm.full(s), 2 * PAIR_STAGE_BYTES);
+                    if (wgrad) {
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        tma_load_2d_pair(sm.a(s) + i * BOX_BYTES, &map_a, full_leader, m0 + i * 64, ks * 64);
-                        tma_load_2d_pair(sm.b(s) + i * BOX_BYTES, &map_b, full_leader, n0 + i * 64, ks * 64);
+                        for (int i = 0; i < 2; ++i)
+                            tma_load_2d_pair(sm.a(s) + i * BOX_BYTES, &map_a, full_leader, m0 + i * 64, ks * 64);
+                    } else {
+                        tma_load_2d_pair(sm.a(s), &map_a, full_leader, ks * BK, blk * BM);
+                    }
+                    if (!b_mn) {
+                        tma_load_2d_pair(sm.b(s), &map_b, full_leader, ks * BK, tl.e * a.b_rows_per_expert + n0);
+                    } else {
+                        const int krow = wgrad ? ks * 64 : tl.e * a.b_rows_per_expert + ks * 64;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            tma_load_2d_pair(sm.b(s) + j * BOX_BYTES, &map_b, full_leader, n0 + j * 64, krow);
                     }
                     if (++s == PAIR_STAGES) {
                         s = 0;
@@ -536,13 +582,13 @@ moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0 && leader) {
-            constexpr uint32_t idesc = idesc_bf16_f32(256, 256) | (1u << 15) | (1u << 16);
+            constexpr uint32_t idesc = idesc_bf16_f32(256, 256) | (wgrad ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
             int s = 0;
             uint32_t ph = 0;
             int it = 0;
             bool ok = true;
             for (int t = first; t < num_tiles && ok; t += step) {
-                const PairTile tl = decode_pair_tile(a, t, m_tiles2);
+                const Tile tl = decode_pair_tile<MODE>(a, t, m_items, m_tiles2);
                 if (tl.k1 <= tl.k0) continue;
                 const int buf = it & 1;
                 ok = mbar_wait_cluster(sm.misc(2 + buf), ((it >> 1) & 1) ^ 1, status, ST_TIMEOUT_TMEM_EMPTY);
@@ -554,9 +600,11 @@ moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_f16_pair(d, smem_desc_mn_sw128(sm.a(s) + k * 2048), smem_desc_mn_sw128(sm.b(s) + k * 2048),
-                                      idesc, (ks != tl.k0) || (k != 0));
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = wgrad ? smem_desc_mn_sw128(sm.a(s) + k * 2048) : smem_desc_sw128(sm.a(s) + k * 32);
+                        const uint64_t bd = b_mn ? smem_desc_mn_sw128(sm.b(s) + k * 2048) : smem_desc_sw128(sm.b(s) + k * 32);
+                        umma_f16_pair(d, ad, bd, idesc, (ks != tl.k0) || (k != 0));
+                    }
                     umma_commit_pair(sm.empty(s), 3);
                     if (++s == PAIR_STAGES) {
                         s = 0;
@@ -575,30 +623,17 @@ moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         const int cg = ew / 4;
         int it = 0;
         for (int t = first; t < num_tiles; t += step) {
-            const PairTile tl = decode_pair_tile(a, t, m_tiles2);
+            const Tile tl = decode_pair_tile<MODE>(a, t, m_items, m_tiles2);
             const int col0 = tl.nt * BN;
-            const int m = tl.mt2 * 256 + static_cast<int>(rank) * 128 + row;
-            const bool row_ok = m < a.c_rows;
-            __nv_bfloat16 *dst = a.c + (static_cast<size_t>(tl.e) * a.c_rows + (row_ok ? m : 0)) * a.ldc + col0;
-            if (tl.k1 <= tl.k0) {      // an expert without rows: its weight gradient is zero
-                if (row_ok)
-                    for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
-                        if (col0 + ch * 32 < a.c_cols)
-                            for (int j = 0; j < 4; ++j)
-                                reinterpret_cast<uint4 *>(dst + ch * 32)[j] = make_uint4(0, 0, 0, 0);
+            const int m = tl.mt * 256 + static_cast<int>(rank) * 128 + row;
+            if (tl.k1 <= tl.k0) {
+                zero_tile(a, cg, tl.e, m, col0);
                 continue;
             }
             const int buf = it & 1;
             if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
             tc_fence_after();
-            const uint32_t acc = tmem_base + buf * BN;
-            for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
-                if (col0 + ch * 32 >= a.c_cols) break;
-                float v[32];
-                tmem_ld_32x32(v, tmem_addr(acc, lane_base, ch * 32));
-                tmem_ld_wait();
-                if (row_ok) store_chunk_bf16(dst + ch * 32, v);
-            }
+            drain_tile<MODE>(a, tmem_base + buf * BN, lane_base, row, cg, tl.mb + static_cast<int>(rank), tl.e, m, col0);
             tc_fence_before();
             mbar_arrive_cluster(mapa_shared(sm.misc(2 + buf), 0));
             ++it;
@@ -611,6 +646,34 @@ moe_bwd_wgrad_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
+// Work lists of the row-space GEMMs on CTA pairs, one CTA: for every expert its row blocks two by two (pair_list =
+// first block of each pair) and the odd last one (single_list); counts[0] = pairs, counts[1] = singles.
+__global__ void __launch_bounds__(1024)
+pair_items_kernel(const int32_t *__restrict__ eblk, int E, int32_t *__restrict__ pair_list,
+                  int32_t *__restrict__ single_list, int32_t *__restrict__ counts) {
+    __shared__ int sp[1024], ss[1024];
+    const int e = threadIdx.x;
+    const int b0 = e < E ? eblk[e] : 0;
+    const int nb = e < E ? max(0, eblk[E + e] - b0) : 0;
+    sp[e] = nb / 2;
+    ss[e] = nb & 1;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {      // inclusive scans of both counts
+        const int vp = e >= d ? sp[e - d] : 0, vs = e >= d ? ss[e - d] : 0;
+        __syncthreads();
+        sp[e] += vp;
+        ss[e] += vs;
+        __syncthreads();
+    }
+    const int poff = sp[e] - nb / 2, soff = ss[e] - (nb & 1);
+    for (int j = 0; j < nb / 2; ++j) pair_list[poff + j] = b0 + 2 * j;
+    if (nb & 1) single_list[soff] = b0 + nb - 1;
+    if (e == 1023) {
+        counts[0] = sp[e];
+        counts[1] = ss[e];
+    }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------
@@ -621,10 +684,10 @@ namespace {
 size_t align_up(size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); }
 
 struct BwdLayout {
-    size_t xs, dos, gu, dgu, actw, inv, eblk, total;
+    size_t xs, dos, gu, dgu, actw, inv, eblk, pair_list, single_list, counts, total;
 };
 
-// xs | dos (reused for d_xs once dW2 is done) | gu | d_gu | wt*act | pair -> row | expert block ranges
+// xs | dos (reused for d_xs once dW2 is done) | gu | d_gu | wt*act | pair -> row | expert block ranges | work lists
 BwdLayout plan_backward(int T, int K, int N, int E, int top_k, int sorted_num) {
     const size_t R = static_cast<size_t>(sorted_num);
     BwdLayout l{};
@@ -636,37 +699,52 @@ BwdLayout plan_backward(int T, int K, int N, int E, int top_k, int sorted_num) {
     l.actw = off, off = align_up(off + R * (N / 2) * 2);
     l.inv = off, off = align_up(off + static_cast<size_t>(T) * top_k * sizeof(int32_t));
     l.eblk = off, off = align_up(off + 2 * static_cast<size_t>(E) * sizeof(int32_t));
+    l.pair_list = off, off = align_up(off + (R / 256 + 1) * sizeof(int32_t));
+    l.single_list = off, off = align_up(off + static_cast<size_t>(E) * sizeof(int32_t));
+    l.counts = off, off = align_up(off + 2 * sizeof(int32_t));
     l.total = off;
     return l;
 }
 
-int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
+template <int MODE>
+int launch_gemm_mode(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
     static bool configured[64] = {false};
     int dev = 0;
     PMOE_CUDA_OK(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        PMOE_CUDA_OK(cudaFuncSetAttribute(moe_bwd_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        PMOE_CUDA_OK(cudaFuncSetAttribute(moe_bwd_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(SMEM_BYTES)));
         configured[dev] = true;
     }
-    moe_bwd_gemm_kernel<<<sm_count(), THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
+    moe_bwd_gemm_kernel<MODE><<<sm_count(), THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
     PMOE_CUDA_OK(cudaGetLastError());
     return PMOE_OK;
 }
 
-// PMOE_BWD_PAIRS=0 / 1: CTA pairs never / always; unset (-1): when an expert has 256 routed rows or more on average
-// (below that the weight-gradient launches are bound by their stores, and the pairs measured slower)
-int pairs_mode() {
-    const char *v = getenv("PMOE_BWD_PAIRS");
-    return (v && (v[0] == '0' || v[0] == '1')) ? v[0] - '0' : -1;
+int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
+    switch (g.mode) {
+        case MODE_NT_STORE: return launch_gemm_mode<MODE_NT_STORE>(ma, mb, g, stream);
+        case MODE_NN_SWIGLU: return launch_gemm_mode<MODE_NN_SWIGLU>(ma, mb, g, stream);
+        case MODE_NN_STORE: return launch_gemm_mode<MODE_NN_STORE>(ma, mb, g, stream);
+        default: return launch_gemm_mode<MODE_WGRAD>(ma, mb, g, stream);
+    }
 }
 
-int launch_wgrad_pair(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
+// PMOE_BWD_PAIRS: 0 = one-CTA kernel everywhere; 1 = weight-gradient GEMMs on CTA pairs; 2 = the row-space GEMMs as
+// well (measured: no gain, their odd-last-block launch eats it); unset (-1) = 1 when an expert has 256 routed rows or
+// more on average (below that the weight-gradient launches are bound by their stores and the pairs measured slower)
+int pairs_mode() {
+    const char *v = getenv("PMOE_BWD_PAIRS");
+    return (v && v[0] >= '0' && v[0] <= '2') ? v[0] - '0' : -1;
+}
+
+template <int MODE>
+int launch_pair_mode(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
     static bool configured[64] = {false};
     int dev = 0;
     PMOE_CUDA_OK(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        PMOE_CUDA_OK(cudaFuncSetAttribute(moe_bwd_wgrad_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        PMOE_CUDA_OK(cudaFuncSetAttribute(moe_bwd_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(PAIR_SMEM_BYTES)));
         configured[dev] = true;
     }
@@ -683,12 +761,23 @@ int launch_wgrad_pair(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs 
     cfg.numAttrs = 1;
     cfg.gridDim = dim3(2);
     int max_clusters = 0;
-    PMOE_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, moe_bwd_wgrad_pair_kernel, &cfg));
-    if (max_clusters < 1) return set_error(PMOE_ERR_CUDA, "no CTA pair of the weight-gradient kernel fits on this device");
-    const long long tiles = static_cast<long long>(g.E) * ((g.c_rows + 255) / 256) * g.n_tiles;
+    PMOE_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, moe_bwd_pair_kernel<MODE>, &cfg));
+    if (max_clusters < 1) return set_error(PMOE_ERR_CUDA, "no CTA pair of the backward GEMM kernel fits on this device");
+    // upper bound of the tile count known on the host (the row-space modes read theirs on the device)
+    const long long tiles = g.mode == MODE_WGRAD ? static_cast<long long>(g.E) * ((g.c_rows + 255) / 256) * g.n_tiles
+                                                 : static_cast<long long>(g.sorted_num / 256 + 1) * g.n_tiles;
     cfg.gridDim = dim3(2 * static_cast<unsigned>(std::min<long long>(tiles, max_clusters)));
-    PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_bwd_wgrad_pair_kernel, ma, mb, g));
+    PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_bwd_pair_kernel<MODE>, ma, mb, g));
     return PMOE_OK;
+}
+
+int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cudaStream_t stream) {
+    switch (g.mode) {
+        case MODE_NT_STORE: return launch_pair_mode<MODE_NT_STORE>(ma, mb, g, stream);
+        case MODE_NN_SWIGLU: return launch_pair_mode<MODE_NN_SWIGLU>(ma, mb, g, stream);
+        case MODE_NN_STORE: return launch_pair_mode<MODE_NN_STORE>(ma, mb, g, stream);
+        default: return launch_pair_mode<MODE_WGRAD>(ma, mb, g, stream);
+    }
 }
 
 int bf16_map(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char *what) {
@@ -743,6 +832,8 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
                  PMOE_ERR_BAD_ARG, "fused_moe_bf16_backward: null pointer");
     PMOE_REQUIRE(T >= 0 && K > 0 && N > 0 && num_experts > 0 && top_k > 0 && sorted_num >= 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16_backward: negative or zero size");
+    PMOE_REQUIRE(num_experts <= 1024, PMOE_ERR_UNSUPPORTED,
+                 "fused_moe_bf16_backward: at most 1024 experts (as moe_align), got %d", num_experts);
     PMOE_REQUIRE(K % 64 == 0 && N % 128 == 0, PMOE_ERR_UNSUPPORTED,
                  "fused_moe_bf16_backward: K must be a multiple of 64 and N of 128, got K=%d N=%d", K, N);
     PMOE_REQUIRE(sorted_num % 128 == 0, PMOE_ERR_BAD_ARG,
@@ -774,11 +865,15 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     auto *actw = reinterpret_cast<__nv_bfloat16 *>(ws + lay.actw);
     auto *inv = reinterpret_cast<int32_t *>(ws + lay.inv);
     auto *eblk = reinterpret_cast<int32_t *>(ws + lay.eblk);
+    auto *pair_list = reinterpret_cast<int32_t *>(ws + lay.pair_list);
+    auto *single_list = reinterpret_cast<int32_t *>(ws + lay.single_list);
+    auto *counts = reinterpret_cast<int32_t *>(ws + lay.counts);
     const uint64_t R = static_cast<uint64_t>(sorted_num);
 
     const int mask = g_bwd_mask;
     const int pm = pairs_mode();
-    const bool pairs = pm >= 0 ? pm == 1 : static_cast<long long>(T) * top_k >= 256ll * E;
+    const bool pairs = pm >= 0 ? pm >= 1 : static_cast<long long>(T) * top_k >= 256ll * E;   // weight gradients
+    const bool row_pairs = pm == 2;
     const int copy_grid = 8 * sm_count();
     if (mask & 1) {
         PMOE_CUDA_OK(cudaMemsetAsync(inv, 0xFF, static_cast<size_t>(T) * top_k * sizeof(int32_t), stream));
@@ -787,6 +882,10 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
         row_maps_kernel<<<small_grid, 256, 0, stream>>>(sorted_token_ids, expert_ids, num_tokens_post_padded,
                                                         sorted_num, top_k, T, E, inv, eblk);
         PMOE_CUDA_OK(cudaGetLastError());
+        if (row_pairs) {
+            pair_items_kernel<<<1, 1024, 0, stream>>>(eblk, E, pair_list, single_list, counts);
+            PMOE_CUDA_OK(cudaGetLastError());
+        }
         gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x),
                                                                 sorted_token_ids, num_tokens_post_padded, sorted_num,
                                                                 top_k, T, K, xs);
@@ -799,7 +898,7 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     if ((mask & 4) && d_topk_weights)
         PMOE_CUDA_OK(cudaMemsetAsync(d_topk_weights, 0, static_cast<size_t>(T) * top_k * sizeof(float), stream));
 
-    CUtensorMap xs_k, xs_mn, dos_k, dos_mn, dgu_k, dgu_mn, actw_mn, w1_k, w1_mn, w2_mn;
+    CUtensorMap xs_k, xs_mn, dos_k, dos_mn, dgu_k, dgu_mn, actw_mn, w1_k, w1_mn, w2_mn, w1_k128;
     if (int rc = bf16_map(&xs_k, xs, R, K, 128, "xs rows")) return rc;
     if (int rc = bf16_map(&xs_mn, xs, R, K, 64, "xs boxes")) return rc;
     if (int rc = bf16_map(&dos_k, dos, R, K, 128, "d_out rows")) return rc;
@@ -810,41 +909,51 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     if (int rc = bf16_map(&w1_k, w1, static_cast<uint64_t>(E) * N, K, 256, "w1 rows")) return rc;
     if (int rc = bf16_map(&w1_mn, w1, static_cast<uint64_t>(E) * N, K, 64, "w1 boxes")) return rc;
     if (int rc = bf16_map(&w2_mn, w2, static_cast<uint64_t>(E) * K, H, 64, "w2 boxes")) return rc;
+    if (int rc = bf16_map(&w1_k128, w1, static_cast<uint64_t>(E) * N, K, 128, "w1 half tiles")) return rc;
 
     GArgs base{};
     base.sorted_ids = sorted_token_ids, base.expert_ids = expert_ids, base.npp = num_tokens_post_padded;
     base.sorted_num = sorted_num, base.eblk = eblk, base.topk_weights = topk_weights;
     base.top_k = top_k, base.tokens = T, base.E = E, base.H = H, base.N = N;
+    // A row-space GEMM on CTA pairs is two launches: the pairs of row blocks, then the odd last blocks of the experts
+    // on the one-CTA kernel (tcgen05 does not allow cta_group::1 and ::2 in one kernel)
+    auto launch_rows = [&](const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mb_pair, GArgs g) -> int {
+        if (!row_pairs) return launch_gemm(ma, mb, g, stream);
+        g.items = pair_list, g.item_count = counts;
+        if (int rc = launch_pair(ma, mb_pair, g, stream)) return rc;
+        g.items = single_list, g.item_count = counts + 1;
+        return launch_gemm(ma, mb, g, stream);
+    };
 
     if (mask & 2) {   // gate | up pre-activations: gu = xs . W1[e]^T
         GArgs g = base;
         g.mode = MODE_NT_STORE, g.ksteps = K / 64, g.n_tiles = (N + 255) / 256, g.b_rows_per_expert = N;
         g.c = gu, g.ldc = N, g.c_cols = N;
-        if (int rc = launch_gemm(xs_k, w1_k, g, stream)) return rc;
+        if (int rc = launch_rows(xs_k, w1_k, w1_k128, g)) return rc;
     }
     if (mask & 4) {   // d_act = wt * (dos . W2[e]) -> d_gu, wt * act, d_wt
         GArgs g = base;
         g.mode = MODE_NN_SWIGLU, g.ksteps = K / 64, g.n_tiles = (H + 255) / 256, g.b_rows_per_expert = K;
         g.gu = gu, g.dgu = dgu, g.actw = actw, g.dwt = d_topk_weights;
-        if (int rc = launch_gemm(dos_k, w2_mn, g, stream)) return rc;
+        if (int rc = launch_rows(dos_k, w2_mn, w2_mn, g)) return rc;
     }
     if (mask & 8) {   // d_W2[e] [K, H] = dos_e^T . (wt * act)_e
         GArgs g = base;
         g.mode = MODE_WGRAD, g.m_tiles = (K + 127) / 128, g.n_tiles = (H + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w2), g.ldc = H, g.c_cols = H, g.c_rows = K;
-        if (int rc = (pairs ? launch_wgrad_pair : launch_gemm)(dos_mn, actw_mn, g, stream)) return rc;
+        if (int rc = (pairs ? launch_pair : launch_gemm)(dos_mn, actw_mn, g, stream)) return rc;
     }
     if (mask & 16) {   // d_xs = d_gu . W1[e], written over dos (dead from here on)
         GArgs g = base;
         g.mode = MODE_NN_STORE, g.ksteps = N / 64, g.n_tiles = (K + 255) / 256, g.b_rows_per_expert = N;
         g.c = dos, g.ldc = K, g.c_cols = K;
-        if (int rc = launch_gemm(dgu_k, w1_mn, g, stream)) return rc;
+        if (int rc = launch_rows(dgu_k, w1_mn, w1_mn, g)) return rc;
     }
     if (mask & 32) {   // d_W1[e] [N, K] = d_gu_e^T . xs_e
         GArgs g = base;
         g.mode = MODE_WGRAD, g.m_tiles = (N + 127) / 128, g.n_tiles = (K + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w1), g.ldc = K, g.c_cols = K, g.c_rows = N;
-        if (int rc = (pairs ? launch_wgrad_pair : launch_gemm)(dgu_mn, xs_mn, g, stream)) return rc;
+        if (int rc = (pairs ? launch_pair : launch_gemm)(dgu_mn, xs_mn, g, stream)) return rc;
     }
     if (mask & 64) {
         combine_dx_kernel<<<copy_grid, 256, 0, stream>>>(dos, inv, top_k, T, K, static_cast<__nv_bfloat16 *>(d_x));

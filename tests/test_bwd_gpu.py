@@ -47,6 +47,18 @@ def test_vs_autograd_of_fp32_oracle(T, K, E, N, k):
     check(run_backward(x, w1, w2, ids, wts, d_out), refs)
 
 
+@pytest.mark.parametrize("pairs", ["0", "1", "2"])
+def test_cta_pair_settings_agree_with_the_oracle(pairs, monkeypatch):
+    # PMOE_BWD_PAIRS: 0 one-CTA kernel everywhere, 1 weight gradients on CTA pairs, 2 row-space GEMMs as well
+    # (pairs of row blocks of one expert + the odd last blocks on the one-CTA kernel)
+    monkeypatch.setenv("PMOE_BWD_PAIRS", pairs)
+    T, K, E, N, k = 700, 384, 5, 768, 3       # 420 rows per expert: 3-4 row blocks each, odd and even counts
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=21)
+    d_out = torch.randn(T, K, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+    refs = O.moe_backward_ref_fp32(x, w1, w2, ids, wts, d_out)
+    check(run_backward(x, w1, w2, ids, wts, d_out), refs)
+
+
 def test_experts_without_rows_get_zero_weight_gradients():
     T, K, E, N, k = 8, 256, 16, 256, 2
     x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=3)
