@@ -82,22 +82,33 @@ struct GArgs {
 // ---------------------------------------------------------------------------------------------
 // row-space helpers (HBM-bound)
 // ---------------------------------------------------------------------------------------------
-// dst[r] = src[token(r)] for the live rows, zeros for padding rows; 16 bytes per thread and step
+// xs[r] = x[token(r)] and dos[r] = d_out[token(r)] for the live rows, zeros for padding rows. One warp per row,
+// 16 bytes per lane and step, both tensors in one pass over the routing table.
 __global__ void __launch_bounds__(256)
-gather_token_rows_kernel(const __nv_bfloat16 *__restrict__ src, const int32_t *__restrict__ sorted_ids,
-                         const int32_t *__restrict__ npp, int sorted_num, int top_k, int tokens, int K,
-                         __nv_bfloat16 *__restrict__ dst) {
+gather_token_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ d_out,
+                         const int32_t *__restrict__ sorted_ids, const int32_t *__restrict__ npp, int sorted_num,
+                         int top_k, int tokens, int K, __nv_bfloat16 *__restrict__ xs, __nv_bfloat16 *__restrict__ dos) {
     const int rows = live_row_blocks(npp, sorted_num) * BM;
     const int vec_per_row = K / 8;
-    const long long total = static_cast<long long>(rows) * vec_per_row;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int r = static_cast<int>(i / vec_per_row), v = static_cast<int>(i - static_cast<long long>(r) * vec_per_row);
+    const int lane = threadIdx.x & 31;
+    for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8) {
         const int pair = sorted_ids[r];
         const int tok = pair >= 0 ? pair / top_k : tokens;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (tok < tokens) val = __ldg(reinterpret_cast<const uint4 *>(src + static_cast<size_t>(tok) * K) + v);
-        reinterpret_cast<uint4 *>(dst + static_cast<size_t>(r) * K)[v] = val;
+        const bool live = tok < tokens;
+        const uint4 *s1 = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(live ? tok : 0) * K);
+        const uint4 *s2 = reinterpret_cast<const uint4 *>(d_out + static_cast<size_t>(live ? tok : 0) * K);
+        uint4 *d1 = reinterpret_cast<uint4 *>(xs + static_cast<size_t>(r) * K);
+        uint4 *d2 = reinterpret_cast<uint4 *>(dos + static_cast<size_t>(r) * K);
+#pragma unroll 4
+        for (int v = lane; v < vec_per_row; v += 32) {
+            uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+            if (live) {
+                a = __ldg(s1 + v);
+                b = __ldg(s2 + v);
+            }
+            d1[v] = a;
+            d2[v] = b;
+        }
     }
 }
 
@@ -886,13 +897,9 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
             pair_items_kernel<<<1, 1024, 0, stream>>>(eblk, E, pair_list, single_list, counts);
             PMOE_CUDA_OK(cudaGetLastError());
         }
-        gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x),
-                                                                sorted_token_ids, num_tokens_post_padded, sorted_num,
-                                                                top_k, T, K, xs);
-        PMOE_CUDA_OK(cudaGetLastError());
-        gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(d_out),
-                                                                sorted_token_ids, num_tokens_post_padded, sorted_num,
-                                                                top_k, T, K, dos);
+        gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(d_out), sorted_token_ids,
+            num_tokens_post_padded, sorted_num, top_k, T, K, xs, dos);
         PMOE_CUDA_OK(cudaGetLastError());
     }
     if ((mask & 4) && d_topk_weights)
