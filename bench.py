@@ -709,13 +709,23 @@ def sweep_backward_entry(name, tokens, device, peaks):
         steps[label] = time_calls(call, reps, flush_buf)
     lib.pmoe_debug_set_backward_mask(127)
     call()
+    # the same with the gate/up pre-activations kept by the forward call (no recompute GEMM): forward with and without
+    # keeping them (one-CTA kernels, bpc = 1, both), then the backward pass fed with them
+    out = torch.empty(T, K, dtype=torch.bfloat16, device=device)
+    fwd_plain = time_calls(lambda: capi.fused_moe_bf16(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k), reps, flush_buf)
+    fwd_keep = time_calls(lambda: capi.fused_moe_bf16_keep(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k), reps, flush_buf)
+    _, gate_up = capi.fused_moe_bf16_keep(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k)
+    ms_kept = time_calls(lambda: capi.fused_moe_bf16_backward(c["x"], c["w1"], c["w2"], d_out, s, e, n, c["wts"], k,
+                                                              workspace=ws, gate_up=gate_up), reps, flush_buf)
     torch.cuda.synchronize()
     assert capi.device_status() == 0, "a kernel recorded an error status"
     ach = flops / (ms * 1e-3) / 1e12
-    del c, ws, d_out, flush_buf
+    kept = {"backward_ms": ms_kept, "forward_ms": fwd_keep, "forward_ms_without_keeping": fwd_plain,
+            "tflops_over_2_thirds_of_flops": (6.0 * T * k * K * N) / (ms_kept * 1e-3) / 1e12}
+    del c, ws, d_out, flush_buf, gate_up, out
     torch.cuda.empty_cache()
     return {"config": name, "tokens": T, "op": "backward", "dtype": "bf16", "ms_per_step": ms, "value": ach,
-            "unit": "TFLOP/s",
+            "unit": "TFLOP/s", "with_kept_pre_activations": kept,
             "roofline": {"kernel": "moe_bwd_gemm_kernel (5 launches)", "bound": "tensor", "achieved": ach,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
                          "peak_source": peaks["source"] + " (burst cuBLAS bf16)", "traffic": None,

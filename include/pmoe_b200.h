@@ -203,7 +203,7 @@ int pmoe_quantize_mx(const void *x /* bf16[src_rows, K] */, const int32_t *row_i
  * w1 [E, N, K], w2 [E, K, N/2]; d_out bf16[T, K] is the gradient of `out`. Writes (does not accumulate into)
  *   d_x  bf16[T, K]        d_w1 bf16[E, N, K]        d_w2 bf16[E, K, N/2]   (experts without rows get zeros)
  *   d_topk_weights fp32[T, top_k], or NULL to skip it (entries of routes to ids outside [0, E) stay 0)
- * The gate/up pre-activations are recomputed from x (nothing is kept from the forward call), products accumulate
+ * The gate/up pre-activations are recomputed from x unless `gate_up` is given (see below); products accumulate
  * in fp32 and every intermediate is rounded to bf16 once. K % 64 == 0, N % 128 == 0, sorted_num % 128 == 0,
  * tensors 16-byte aligned (d_w1, d_w2: 32), workspace 1024-byte aligned with pmoe_fused_moe_bf16_backward_workspace_bytes() bytes.
  * Asynchronous on `stream`; bounded waits and status reporting as for the forward kernels. */
@@ -212,8 +212,19 @@ int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, 
                                  const int32_t *sorted_token_ids, const int32_t *expert_ids,
                                  const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k, int T,
                                  int K, int N, int num_experts, int sorted_num, void *d_x, void *d_w1, void *d_w2,
-                                 float *d_topk_weights, void *workspace, size_t workspace_bytes,
-                                 pmoe_stream_t stream);
+                                 float *d_topk_weights, const void *gate_up, void *workspace,
+                                 size_t workspace_bytes, pmoe_stream_t stream);
+/* Forward call that keeps what the backward pass would otherwise recompute: pmoe_fused_moe_bf16_ws with the knobs
+ * fixed (block_m 128, bpc 1, split pipeline) whose gate/up kernel also stores its pre-activations (bf16, as rounded
+ * from the fp32 accumulators) into gate_up bf16[sorted_num, N] (32-byte aligned; row r = row r of sorted_token_ids,
+ * columns [0, N/2) gate, [N/2, N) up; rows of padding hold finite values nobody uses). Passing that buffer as
+ * `gate_up` to pmoe_fused_moe_bf16_backward skips its recompute GEMM (a quarter of the step on wide layers); NULL
+ * there means recompute. No counterpart in the reference. */
+int pmoe_fused_moe_bf16_keep_ws(const void *x, const void *w, const void *w2, void *out,
+                                const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k, int M,
+                                int K, int N, int num_experts, int sorted_num, void *gate_up, void *workspace,
+                                size_t workspace_bytes, pmoe_stream_t stream);
 /* Measurement hook: which steps of the backward pass run. Bits: 1 row maps + row gathers, 2 gate/up recompute,
  * 4 d_act + SwiGLU derivative, 8 d_w2, 16 d_xs, 32 d_w1, 64 d_x combine; 127 = all (default). Returns the old mask.
  * With bits missing the outputs are incomplete. */

@@ -121,39 +121,55 @@ def pack_scales_blocked(scales: torch.Tensor) -> torch.Tensor:
     return tiles.reshape(*lead, -1).view(torch.float8_e8m0fnu)
 
 
-def fused_moe_bf16_backward(x, w, w2, d_out, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, top_k):
-    """Gradients of ``fused_moe_bf16`` (bpc = 1 routing tensors): ``(d_x, d_w, d_w2, d_topk_weights)``. The reference
-    is forward-only (README.md:17); the checker is autograd through the fp32 test oracle (test/test.py:13-48)."""
+def fused_moe_bf16_backward(x, w, w2, d_out, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, top_k,
+                            gate_up=None):
+    """Gradients of ``fused_moe_bf16`` (bpc = 1 routing tensors): ``(d_x, d_w, d_w2, d_topk_weights)``. ``gate_up`` is
+    the tensor ``fused_moe_bf16_keep`` returned for the same inputs; without it the pre-activations are recomputed.
+    The reference is forward-only (README.md:17); the checker is autograd through the fp32 test oracle
+    (test/test.py:13-48)."""
     return torch.ops.prime_moe.fused_moe_bf16_backward(x, w, w2, d_out.contiguous(), sorted_token_ids, expert_ids,
-                                                       num_tokens_post_padded, topk_weights, top_k)
+                                                       num_tokens_post_padded, topk_weights, top_k, gate_up)
+
+
+def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k):
+    """``fused_moe_bf16`` (split pipeline, bpc = 1) writing ``out`` and returning the gate/up pre-activations
+    ``[sorted_num, N]`` its gate/up kernel saw, for ``fused_moe_bf16_backward(..., gate_up=...)``."""
+    return torch.ops.prime_moe.fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                                   topk_weights, out, top_k)
 
 
 class _MoEFFN(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, w2, topk_ids, topk_weights):
+    def forward(ctx, x, w, w2, topk_ids, topk_weights, recompute):
         num_experts, top_k = w.shape[0], topk_ids.shape[1]
         sorted_ids, expert_ids, npp = torch.ops.prime_moe.moe_align(topk_ids, num_experts, 128, 1)
         wts = topk_weights.detach().float().contiguous()
         out = torch.empty_like(x)
-        torch.ops.prime_moe.fused_moe_bf16(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k, 128, 64, 4, 4, 1, 1, True)
-        ctx.save_for_backward(x, w, w2, sorted_ids, expert_ids, npp, wts)
+        gate_up = None
+        if recompute:
+            torch.ops.prime_moe.fused_moe_bf16(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k, 128, 64, 4, 4, 1, 1,
+                                               True)
+        else:
+            gate_up = fused_moe_bf16_keep(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k)
+        ctx.save_for_backward(x, w, w2, sorted_ids, expert_ids, npp, wts, gate_up)
         ctx.top_k = top_k
         ctx.weights_dtype = topk_weights.dtype
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        x, w, w2, sorted_ids, expert_ids, npp, wts = ctx.saved_tensors
-        d_x, d_w, d_w2, d_wt = fused_moe_bf16_backward(x, w, w2, d_out, sorted_ids, expert_ids, npp, wts, ctx.top_k)
-        return d_x, d_w, d_w2, None, d_wt.to(ctx.weights_dtype)
+        x, w, w2, sorted_ids, expert_ids, npp, wts, gate_up = ctx.saved_tensors
+        d_x, d_w, d_w2, d_wt = fused_moe_bf16_backward(x, w, w2, d_out, sorted_ids, expert_ids, npp, wts, ctx.top_k, gate_up)
+        return d_x, d_w, d_w2, None, d_wt.to(ctx.weights_dtype), None
 
 
-def moe_ffn(x, w, w2, topk_ids, topk_weights):
+def moe_ffn(x, w, w2, topk_ids, topk_weights, recompute=False):
     """Differentiable bf16 MoE FFN layer: ``moe_align`` + ``fused_moe_bf16`` forward, ``fused_moe_bf16_backward`` for the
-    gradients of ``x``, ``w``, ``w2`` and ``topk_weights`` (only the routed rows' inputs are kept for the backward
-    pass; the gate/up pre-activations are recomputed)."""
-    return _MoEFFN.apply(x, w, w2, topk_ids, topk_weights)
+    gradients of ``x``, ``w``, ``w2`` and ``topk_weights``. The forward call keeps the gate/up pre-activations
+    (``sorted_num * N`` bf16) for the backward pass; ``recompute=True`` keeps nothing and recomputes them there (one
+    more GEMM of the gate/up size)."""
+    return _MoEFFN.apply(x, w, w2, topk_ids, topk_weights, recompute)
 
 
 __all__ = ["fused_moe_bf16", "fused_moe_mxfp8", "moe_align", "pack_scales_blocked", "route_topk", "route_topk_align", "quantize_mx",
-           "fused_moe_bf16_backward", "moe_ffn", "BLOCK"]
+           "fused_moe_bf16_backward", "fused_moe_bf16_keep", "moe_ffn", "BLOCK"]

@@ -54,7 +54,8 @@ SIGNATURES = {
     "pmoe_route_topk_align": (_i, [_vp, _i, _i, _i, _i, _i] + [_vp] * 5 + [_i] * 4 + [_vp, _sz, _vp]),
     "pmoe_quantize_mx": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "pmoe_fused_moe_bf16_backward_workspace_bytes": (_sz, [_i] * 6),
-    "pmoe_fused_moe_bf16_backward": (_i, [_vp] * 8 + [_i] * 6 + [_vp] * 5 + [_sz, _vp]),
+    "pmoe_fused_moe_bf16_backward": (_i, [_vp] * 8 + [_i] * 6 + [_vp] * 6 + [_sz, _vp]),
+    "pmoe_fused_moe_bf16_keep_ws": (_i, [_vp] * 8 + [_i] * 6 + [_vp, _vp, _sz, _vp]),
     "pmoe_debug_set_backward_mask": (_i, [_i]),
     "pmoe_debug_set_wait_ns": (_i, [C.c_ulonglong]),
     "pmoe_debug_wait_probe": (_i, [_vp]),
@@ -158,8 +159,24 @@ def fused_moe_mxfp8(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, e
     return out
 
 
+def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k):
+    """``fused_moe_bf16`` (split pipeline, bpc = 1) that also returns the gate/up pre-activations
+    ``[sorted_num, N]`` for ``fused_moe_bf16_backward(..., gate_up=...)``."""
+    M, K = x.shape
+    E, N, _ = w.shape
+    R = sorted_token_ids.numel()
+    gate_up = torch.empty(R, N, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        workspace = _workspace(lib().pmoe_fused_moe_bf16_workspace_bytes(M, K, N, R, 1), x.device)
+        _check(lib().pmoe_fused_moe_bf16_keep_ws(
+            _p(x), _p(w), _p(w2), _p(out), _p(sorted_token_ids), _p(expert_ids), _p(num_tokens_post_padded),
+            _p(topk_weights), top_k, M, K, N, E, R, _p(gate_up), _p(workspace),
+            workspace.numel() * workspace.element_size(), _stream()))
+    return out, gate_up
+
+
 def fused_moe_bf16_backward(x, w, w2, d_out, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights,
-                            top_k, need_weight_grad=True, workspace=None):
+                            top_k, need_weight_grad=True, workspace=None, gate_up=None):
     """Gradients of ``fused_moe_bf16`` for ``d_out`` [T, K]: ``(d_x [T, K], d_w [E, N, K], d_w2 [E, K, N/2],
     d_topk_weights fp32 [T, top_k] | None)``, the routing tensors being those of the forward call (block_m = 128)."""
     T, K = x.shape
@@ -176,7 +193,7 @@ def fused_moe_bf16_backward(x, w, w2, d_out, sorted_token_ids, expert_ids, num_t
         _check(lib().pmoe_fused_moe_bf16_backward(
             _p(x), _p(w), _p(w2), _p(d_out), _p(sorted_token_ids), _p(expert_ids), _p(num_tokens_post_padded),
             _p(topk_weights), top_k, T, K, N, E, sorted_token_ids.numel(), _p(d_x), _p(d_w), _p(d_w2), _p(d_wt),
-            _p(workspace), workspace.numel() * workspace.element_size(), _stream()))
+            _p(gate_up), _p(workspace), workspace.numel() * workspace.element_size(), _stream()))
     return d_x, d_w, d_w2, d_wt
 
 

@@ -42,9 +42,12 @@ int scratch_free(void *ptr, cudaStream_t stream);
 //   out_rows   device uint64[M]: row i of `out` lives at this address (possibly in another GPU's memory mapped
 //              into this process); the down kernels add their results there with plain vector reductions and the
 //              library does not zero anything (bf16 split pipeline only)
+//   gu_out     device bf16[sorted_num, N]: the gate/up kernel also stores its pre-activations there (kept for the
+//              backward pass; bf16 split pipeline with bpc = 1 only)
 struct CallExtras {
     const int32_t *live_rows = nullptr;
     const unsigned long long *out_rows = nullptr;
+    void *gu_out = nullptr;
 };
 CallExtras &call_extras();
 

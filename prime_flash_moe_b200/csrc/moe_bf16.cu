@@ -92,6 +92,8 @@ struct Args {
     int down_ksplit; // one-CTA down kernel: split the k-range of its tiles when there are fewer tiles than CTAs
     int short_boxes; // one-CTA split kernels: row blocks with <= SHORT_ROWS routed rows move only those rows of
                      // the A operand and of the activation tile (the rest of a 128-row block is padding)
+    __nv_bfloat16 *gu_out;   // optional [sorted_num, N]: the one-CTA gate/up kernels also store the gate | up
+                             // pre-activations (bf16) for a later backward pass
 };
 
 constexpr int SHORT_ROWS = 32;
@@ -214,12 +216,26 @@ __device__ __forceinline__ void drain_fills(const Smem &sm, int stages, long lon
 
 // SwiGLU epilogue for one 32-column chunk `c` (0..3) of a 128x128 activation tile: thread = row.
 // Writes bf16 into the 128-byte-swizzled tile at `act` (two 16 KB halves of 64 columns).
+template <bool kKeep = false>
 __device__ __forceinline__ void swiglu_chunk_to_smem(uint32_t tmem_acc, uint32_t lane_base, int row, int c,
-                                                     uint32_t act) {
+                                                     uint32_t act, __nv_bfloat16 *gu_row = nullptr, int H = 0) {
     float g[32], u[32];
     tmem_ld_32x32(g, tmem_addr(tmem_acc, lane_base, c * 32));
     tmem_ld_32x32(u, tmem_addr(tmem_acc, lane_base, 128 + c * 32));
     tmem_ld_wait();
+    if (kKeep && gu_row) {   // keep the pre-activations: gate columns at gu_row, up columns H further (256-bit stores)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            uint32_t wg[8], wu[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                wg[q] = pack_bf16x2(g[16 * j + 2 * q], g[16 * j + 2 * q + 1]);
+                wu[q] = pack_bf16x2(u[16 * j + 2 * q], u[16 * j + 2 * q + 1]);
+            }
+            st_global_v8(gu_row + c * 32 + 16 * j, wg);
+            st_global_v8(gu_row + H + c * 32 + 16 * j, wu);
+        }
+    }
     const uint32_t row_addr = act + (c >> 1) * (ACT_TILE_BYTES / 2) + row * 128;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -340,6 +356,7 @@ gather_rows_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restric
 // up kernel (split pipeline, first launch)
 //   misc barriers: 0,1 tmem_full[2] | 2,3 tmem_empty[2] | 4 staged | 5 stage_free
 // ---------------------------------------------------------------------------------------------
+template <bool kKeep>
 __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                    const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_x_short,
@@ -540,8 +557,10 @@ moe_up_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             if (!mbar_wait(sm.misc(5), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;  // staging tile free
             tc_fence_after();
             const uint32_t acc = tmem_base + buf * 256;
+            __nv_bfloat16 *gu_row =
+                kKeep ? a.gu_out + (static_cast<size_t>(mb) * BM + row) * a.N + c.n_tile * 128 : nullptr;
             for (int ch = cg * (4 / ncg); ch < (cg + 1) * (4 / ncg); ++ch)
-                swiglu_chunk_to_smem(acc, lane_base, row, ch, sm.act);
+                swiglu_chunk_to_smem<kKeep>(acc, lane_base, row, ch, sm.act, gu_row, a.H);
             tc_fence_before();
             mbar_arrive(sm.misc(2 + buf));  // accumulator drained
             fence_proxy_async_smem();
@@ -622,6 +641,7 @@ __device__ __forceinline__ int tile_passes(const Args &a, int q, int m_blocks, P
     return 2;
 }
 
+template <bool kKeep>
 __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_up_dual_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
                         const __grid_constant__ CUtensorMap map_act, const Args a) {
@@ -854,8 +874,11 @@ moe_up_dual_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t acc = tmem_base + h * 256;
+                    __nv_bfloat16 *gu_row =
+                        kKeep ? a.gu_out + (static_cast<size_t>(ps[pi].blk[h]) * BM + row) * a.N + c.n_tile * 128
+                              : nullptr;
                     for (int ch = cg * (4 / ncg); ch < (cg + 1) * (4 / ncg); ++ch)
-                        swiglu_chunk_to_smem(acc, lane_base, row, ch, sm.act);
+                        swiglu_chunk_to_smem<kKeep>(acc, lane_base, row, ch, sm.act, gu_row, a.H);
                     tc_fence_before();
                     mbar_arrive(sm.misc(2 + h));   // accumulator drained
                     fence_proxy_async_smem();
@@ -1584,6 +1607,9 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
     a.live_rows = extras.live_rows;
     a.out_rows = extras.out_rows;
     PMOE_REQUIRE(!extras.out_rows || p.split, PMOE_ERR_UNSUPPORTED, "fused_moe_bf16: out_rows requires split=True");
+    a.gu_out = static_cast<__nv_bfloat16 *>(extras.gu_out);
+    PMOE_REQUIRE(!extras.gu_out || (p.split && p.bpc == 1), PMOE_ERR_UNSUPPORTED,
+                 "fused_moe_bf16: keeping the gate/up pre-activations requires split=True and bpc=1");
     const int bulk = down_bulk_reduce_mode();   // -1 auto: on when the down GEMM's K extent (H) is short
     // rows addressed through out_rows may live in a peer's memory: plain vector reductions only there
     const bool bulk_reduce = extras.out_rows ? false : (bulk < 0 ? (H <= 1024) : bulk != 0);
@@ -1682,7 +1708,8 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
         if (int rc = make_tmap_2d(&map_x_short, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ws_base + lay.x_sorted,
                                   p.sorted_num, p.K, SHORT_ROWS, BK, CU_TENSOR_MAP_SWIZZLE_128B, "x_sorted (short box)"))
             return rc;
-    a.short_boxes = short_boxes_mode();
+    // with gu_out every row of a block is stored, so every row of the A tile must hold real data
+    a.short_boxes = extras.gu_out ? 0 : short_boxes_mode();
     if (p.bpc == 2) {
         // two-CTA pipeline: always fed from the row-gathered copy; B tiles are loaded as 128-row halves
         CUtensorMap map_w2h;
@@ -1754,7 +1781,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
             if (tails && !(phases & 8)) {   // plain launch: starts when the pair kernel (which zeroes `out`) has finished
                 Args tu = ta;
                 tu.use_pdl = 0;
-                if (int rc = launch_single(moe_up_bf16_kernel, tu, (max_blocks / 2) * (H / 128),
+                if (int rc = launch_single(moe_up_bf16_kernel<false>, tu, (max_blocks / 2) * (H / 128),
                                            smem_bytes(tu.stages, ACT_TILE_BYTES), map_x, map_w1, map_act, map_x_short,
                                            map_act_short))
                     return rc;
@@ -1797,7 +1824,8 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
         // LSU mode: eight gather warps (four per row block) beside four epilogue warps, else four for both blocks
         const int threads = 64 + 32 * a.epi_warps + (a_mode == 2 ? (a.epi_warps == 4 ? 2 : 1) * GATHER_THREADS : 0);
         const size_t smem = smem_bytes_dual(up.stages);
-        if (int rc = set_smem(moe_up_dual_bf16_kernel, smem)) return rc;
+        auto dual_kernel = a.gu_out ? moe_up_dual_bf16_kernel<true> : moe_up_dual_bf16_kernel<false>;
+        if (int rc = set_smem(dual_kernel, smem)) return rc;
         const int tiles = ((max_blocks + 1) / 2) * (H / 128);
         up.use_pdl = (pdl_enabled() && pregather && (phases & 1)) ? 1 : 0;
         cudaLaunchConfig_t cfg = {};
@@ -1810,7 +1838,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = up.use_pdl ? 1 : 0;
-        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_dual_bf16_kernel, map_x, map_w1, map_act, up));
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, dual_kernel, map_x, map_w1, map_act, up));
     } else if (phases & 2) {
         Args up = a;
         up.zero_out = extras.out_rows ? 0 : 1;
@@ -1818,7 +1846,8 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
         up.x = static_cast<const __nv_bfloat16 *>(p.x);
         const int threads = 64 + 32 * a.epi_warps + (a_mode == 2 ? GATHER_THREADS : 0);
         const size_t smem = smem_bytes(up.stages, ACT_TILE_BYTES);
-        if (int rc = set_smem(moe_up_bf16_kernel, smem)) return rc;
+        auto up_kernel = a.gu_out ? moe_up_bf16_kernel<true> : moe_up_bf16_kernel<false>;
+        if (int rc = set_smem(up_kernel, smem)) return rc;
         const int tiles = max_blocks * (H / 128);
         up.use_pdl = (pdl_enabled() && pregather && (phases & 1)) ? 1 : 0;
         cudaLaunchConfig_t cfg = {};
@@ -1831,7 +1860,7 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = up.use_pdl ? 1 : 0;
-        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_up_bf16_kernel, map_x, map_w1, map_act, map_x_short, map_act_short, up));
+        PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, up_kernel, map_x, map_w1, map_act, map_x_short, map_act_short, up));
     }
     if (phases & 4) {
         Args dn = a;
@@ -1930,6 +1959,22 @@ extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2,
     const int rc = run(p, raw ? ws : nullptr, need, stream);
     if (raw)
         if (int rc2 = scratch_free(raw, stream)) return rc2;
+    return rc;
+}
+
+extern "C" int pmoe_fused_moe_bf16_keep_ws(const void *x, const void *w, const void *w2, void *out,
+                                           const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                           const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
+                                           int M, int K, int N, int num_experts, int sorted_num, void *gate_up,
+                                           void *workspace, size_t workspace_bytes, pmoe_stream_t stream) {
+    PMOE_REQUIRE(gate_up != nullptr && (reinterpret_cast<uintptr_t>(gate_up) & 31) == 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_keep: gate_up must be a 32-byte aligned device buffer of sorted_num * N bf16");
+    pmoe::CallExtras &extras = pmoe::call_extras();
+    extras.gu_out = gate_up;
+    const int rc = pmoe_fused_moe_bf16_ws(x, w, w2, out, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                          topk_weights, top_k, M, K, N, num_experts, sorted_num, 128, 64, 4, 4, 1, 1, 1,
+                                          workspace, workspace_bytes, stream);
+    extras = pmoe::CallExtras{};
     return rc;
 }
 

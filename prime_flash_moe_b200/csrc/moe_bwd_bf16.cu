@@ -835,7 +835,8 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
                                             const int32_t *num_tokens_post_padded, const float *topk_weights,
                                             int top_k, int T, int K, int N, int num_experts, int sorted_num,
                                             void *d_x, void *d_w1, void *d_w2, float *d_topk_weights,
-                                            void *workspace, size_t workspace_bytes, pmoe_stream_t stream_) {
+                                            const void *gate_up, void *workspace, size_t workspace_bytes,
+                                            pmoe_stream_t stream_) {
     using namespace pmoe;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     PMOE_REQUIRE(x && w1 && w2 && d_out && sorted_token_ids && expert_ids && num_tokens_post_padded && topk_weights &&
@@ -871,7 +872,11 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     auto *xs = reinterpret_cast<__nv_bfloat16 *>(ws + lay.xs);
     auto *dos = reinterpret_cast<__nv_bfloat16 *>(ws + lay.dos);
-    auto *gu = reinterpret_cast<__nv_bfloat16 *>(ws + lay.gu);
+    // the pre-activations kept by the forward call (pmoe_fused_moe_bf16_keep_ws), or recomputed into the workspace
+    PMOE_REQUIRE((reinterpret_cast<uintptr_t>(gate_up) & 31) == 0, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_backward: gate_up must be 32-byte aligned");
+    auto *gu = gate_up ? const_cast<__nv_bfloat16 *>(static_cast<const __nv_bfloat16 *>(gate_up))
+                       : reinterpret_cast<__nv_bfloat16 *>(ws + lay.gu);
     auto *dgu = reinterpret_cast<__nv_bfloat16 *>(ws + lay.dgu);
     auto *actw = reinterpret_cast<__nv_bfloat16 *>(ws + lay.actw);
     auto *inv = reinterpret_cast<int32_t *>(ws + lay.inv);
@@ -932,7 +937,7 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
         return launch_gemm(ma, mb, g, stream);
     };
 
-    if (mask & 2) {   // gate | up pre-activations: gu = xs . W1[e]^T
+    if ((mask & 2) && !gate_up) {   // gate | up pre-activations: gu = xs . W1[e]^T
         GArgs g = base;
         g.mode = MODE_NT_STORE, g.ksteps = K / 64, g.n_tiles = (N + 255) / 256, g.b_rows_per_expert = N;
         g.c = gu, g.ldc = N, g.c_cols = N;

@@ -303,10 +303,17 @@ std::tuple<torch::Tensor, torch::Tensor> quantize_mx(const torch::Tensor &x,
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> fused_moe_bf16_backward(
     const torch::Tensor &x, const torch::Tensor &w, const torch::Tensor &w2, const torch::Tensor &d_out,
     const torch::Tensor &sorted_token_ids, const torch::Tensor &expert_ids, const torch::Tensor &num_tokens_post_padded,
-    const torch::Tensor &topk_weights, int64_t top_k) {
+    const torch::Tensor &topk_weights, int64_t top_k, const std::optional<torch::Tensor> &gate_up) {
     at::cuda::OptionalCUDAGuard guard{device_of(x)};
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w2.dim() == 3, "x must be [T, K], w [E, N, K], w2 [E, K, N/2]");
+    const void *gu = nullptr;
+    if (gate_up.has_value()) {
+        TORCH_CHECK(gate_up->is_cuda() && gate_up->is_contiguous() && gate_up->dtype() == torch::kBFloat16 &&
+                        gate_up->numel() == sorted_token_ids.numel() * w.size(1),
+                    "gate_up must be the contiguous bf16 [sorted_num, N] tensor of fused_moe_bf16_keep");
+        gu = gate_up->const_data_ptr();
+    }
     for (const torch::Tensor *t : {&x, &w, &w2, &d_out})
         TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->dtype() == torch::kBFloat16,
                     "x, w, w2 and d_out must be contiguous bf16 CUDA tensors");
@@ -333,17 +340,57 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> fused_moe
         static_cast<const int32_t *>(num_tokens_post_padded.const_data_ptr()),
         static_cast<const float *>(topk_weights.const_data_ptr()), static_cast<int>(top_k), static_cast<int>(T),
         static_cast<int>(K), static_cast<int>(N), static_cast<int>(E), static_cast<int>(sorted_token_ids.numel()),
-        d_x.data_ptr(), d_w.data_ptr(), d_w2.data_ptr(), static_cast<float *>(d_wt.data_ptr()), ws_ptr, need, stream));
+        d_x.data_ptr(), d_w.data_ptr(), d_w2.data_ptr(), static_cast<float *>(d_wt.data_ptr()), gu, ws_ptr, need,
+        stream));
     return {d_x, d_w, d_w2, d_wt};
+}
+
+// forward call that keeps the gate/up pre-activations for the backward pass (pmoe_fused_moe_bf16_keep_ws):
+// writes `out`, returns gate_up bf16 [sorted_num, N]
+torch::Tensor fused_moe_bf16_keep(const torch::Tensor &x, const torch::Tensor &w, const torch::Tensor &w2,
+                                  const torch::Tensor &sorted_token_ids, const torch::Tensor &expert_ids,
+                                  const torch::Tensor &num_tokens_post_padded, const torch::Tensor &topk_weights,
+                                  torch::Tensor &out, int64_t top_k) {
+    at::cuda::OptionalCUDAGuard guard{device_of(x)};
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w2.dim() == 3, "x must be [T, K], w [E, N, K], w2 [E, K, N/2]");
+    for (const torch::Tensor *t : {&x, &w, &w2, static_cast<const torch::Tensor *>(&out)})
+        TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->dtype() == torch::kBFloat16,
+                    "x, w, w2 and out must be contiguous bf16 CUDA tensors");
+    for (const torch::Tensor *t : {&sorted_token_ids, &expert_ids, &num_tokens_post_padded})
+        TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->dtype() == torch::kInt32,
+                    "the routing tensors must be contiguous int32 CUDA tensors");
+    TORCH_CHECK(topk_weights.is_cuda() && topk_weights.is_contiguous() && topk_weights.dtype() == torch::kFloat32,
+                "topk_weights must be a contiguous fp32 CUDA tensor");
+    const int64_t T = x.size(0), K = x.size(1), E = w.size(0), N = w.size(1), R = sorted_token_ids.numel();
+    TORCH_CHECK(w.size(2) == K && w2.size(0) == E && w2.size(1) == K && w2.size(2) * 2 == N, "weight shapes do not match");
+    TORCH_CHECK(out.sizes() == x.sizes(), "out must have the shape of x");
+    torch::Tensor gate_up = torch::empty({R, N}, x.options());
+    const size_t need = pmoe_fused_moe_bf16_workspace_bytes(static_cast<int>(T), static_cast<int>(K), static_cast<int>(N),
+                                                            static_cast<int>(R), 1);
+    torch::Tensor ws = torch::empty({static_cast<int64_t>(need) + 1024}, x.options().dtype(torch::kUInt8));
+    void *ws_ptr = reinterpret_cast<void *>((reinterpret_cast<uintptr_t>(ws.data_ptr()) + 1023) & ~static_cast<uintptr_t>(1023));
+    check_status(pmoe_fused_moe_bf16_keep_ws(
+        x.const_data_ptr(), w.const_data_ptr(), w2.const_data_ptr(), out.data_ptr(),
+        static_cast<const int32_t *>(sorted_token_ids.const_data_ptr()),
+        static_cast<const int32_t *>(expert_ids.const_data_ptr()),
+        static_cast<const int32_t *>(num_tokens_post_padded.const_data_ptr()),
+        static_cast<const float *>(topk_weights.const_data_ptr()), static_cast<int>(top_k), static_cast<int>(T),
+        static_cast<int>(K), static_cast<int>(N), static_cast<int>(E), static_cast<int>(R), gate_up.data_ptr(), ws_ptr,
+        need, stream));
+    return gate_up;
 }
 
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(prime_moe, m) {
     m.def("fused_moe_bf16_backward(Tensor x, Tensor w, Tensor w2, Tensor d_out, Tensor sorted_token_ids, "
-          "Tensor expert_ids, Tensor num_tokens_post_padded, Tensor topk_weights, int top_k) -> "
+          "Tensor expert_ids, Tensor num_tokens_post_padded, Tensor topk_weights, int top_k, Tensor? gate_up=None) -> "
           "(Tensor, Tensor, Tensor, Tensor)");
     m.impl("fused_moe_bf16_backward", torch::kCUDA, &fused_moe_bf16_backward);
+    m.def("fused_moe_bf16_keep(Tensor x, Tensor w, Tensor w2, Tensor sorted_token_ids, Tensor expert_ids, "
+          "Tensor num_tokens_post_padded, Tensor topk_weights, Tensor(a!) out, int top_k) -> Tensor");
+    m.impl("fused_moe_bf16_keep", torch::kCUDA, &fused_moe_bf16_keep);
     m.def("route_topk(Tensor logits, int top_k, bool renormalize=True) -> (Tensor, Tensor)");
     m.impl("route_topk", torch::kCUDA, &route_topk);
     m.def("route_topk_align(Tensor logits, int top_k, bool renormalize=True, int block_m=128, int bpc=1) -> "
