@@ -106,6 +106,33 @@ def test_bf16_ws_entry_point_rejects_a_short_workspace(lib):
     assert rc == 1 and str(need).encode() in lib.pmoe_last_error()
 
 
+def test_backward_argument_errors_and_workspace_plan(lib):
+    """The backward entry point validates before it touches the device; its workspace plan covers the row-space
+    buffers (xs, d_out rows, gate|up, d_gate|d_up, weighted activation) and grows with every dimension."""
+    buf = (C.c_char * 8192)()
+    p = (C.addressof(buf) + 1023) & ~1023
+    common = (p, p, p, p, p, p, p, p)
+    assert lib.pmoe_fused_moe_bf16_backward(*common, 2, 8, 96, 512, 4, 512, p, p, p, None, None, p, 1 << 30, None) == 2
+    assert b"multiple of 64" in lib.pmoe_last_error()
+    assert lib.pmoe_fused_moe_bf16_backward(*common, 2, 8, 256, 512, 4, 500, p, p, p, None, None, p, 1 << 30, None) == 1
+    assert b"sorted_num" in lib.pmoe_last_error()
+    assert lib.pmoe_fused_moe_bf16_backward(*common, 2, 8, 256, 512, 2000, 512, p, p, p, None, None, p, 1 << 30,
+                                            None) == 2
+    assert b"1024 experts" in lib.pmoe_last_error()
+    assert lib.pmoe_fused_moe_bf16_backward(None, p, p, p, p, p, p, p, 2, 8, 256, 512, 4, 512, p, p, p, None, None, p,
+                                            1 << 30, None) == 1
+    need = lib.pmoe_fused_moe_bf16_backward_workspace_bytes(8, 256, 512, 4, 2, 512)
+    rows = 512 * (2 * 256 + 2 * 512 + 256) * 2                      # bf16 row-space buffers
+    assert need >= rows and need % 1024 == 0
+    assert lib.pmoe_fused_moe_bf16_backward(*common, 2, 8, 256, 512, 4, 512, p, p, p, None, None, p, need - 1, None) == 1
+    assert str(need).encode() in lib.pmoe_last_error()
+    assert lib.pmoe_fused_moe_bf16_backward_workspace_bytes(8, 256, 512, 4, 2, 1024) > need
+    assert lib.pmoe_fused_moe_bf16_backward_workspace_bytes(8, 512, 512, 4, 2, 512) > need
+    assert lib.pmoe_fused_moe_bf16_keep_ws(*common, 2, 8, 256, 512, 4, 512, None, p, 1 << 30, None) == 1
+    assert b"gate_up" in lib.pmoe_last_error()
+    assert lib.pmoe_debug_set_backward_mask(127) == 127
+
+
 def test_wait_limit_argument_range(lib):
     assert lib.pmoe_debug_set_wait_ns(10) == 1                   # below 1 microsecond
     assert lib.pmoe_debug_set_wait_ns(10 ** 12) == 1             # above 60 seconds
