@@ -316,3 +316,22 @@ def moe_backward_ref_fp32(x, w1, w2, topk_ids, topk_weights, d_out):
     out = moe_ref_fp32(leaves[0], leaves[1], leaves[2], topk_ids, leaves[3])
     out.backward(d_out.float())
     return tuple(t.grad if t.grad is not None else torch.zeros_like(t) for t in leaves)
+
+
+def moe_backward_expert_slice_ref(x_e, d_out_e, wt_e, w1_gate_rows, w1_up_rows, w2_cols):
+    """Weight gradients of ONE expert restricted to a slice ``hs`` of its hidden columns, in fp32, from the rows routed
+    to it: ``x_e`` [n, K], ``d_out_e`` [n, K] (gradient of the output rows of those tokens), ``wt_e`` [n] routing
+    weights, ``w1_gate_rows`` = W1[e][hs], ``w1_up_rows`` = W1[e][H + hs] (both [h, K]), ``w2_cols`` = W2[e][:, hs]
+    ([K, h]). Returns ``(d_W1[e][hs], d_W1[e][H + hs], d_W2[e][:, hs])``. Same contraction as
+    ``moe_backward_ref_fp32`` (the test suite checks one against the other); exists so that full-size layers can be
+    checked a slice at a time."""
+    x_e, d_out_e, wt_e = x_e.float(), d_out_e.float(), wt_e.float()
+    g = x_e @ w1_gate_rows.float().t()
+    u = x_e @ w1_up_rows.float().t()
+    s = torch.sigmoid(g)
+    act = g * s * u
+    c = d_out_e @ w2_cols.float()
+    d_act = c * wt_e[:, None]
+    d_gate = d_act * u * s * (1 + g * (1 - s))
+    d_up = d_act * g * s
+    return d_gate.t() @ x_e, d_up.t() @ x_e, d_out_e.t() @ (act * wt_e[:, None])

@@ -178,3 +178,61 @@ def test_c4_zipf_shape(dtype):
         ref = oracle_rows(toks, xq, w1q, w2q, ids, wts, scales=(xs, w1s, w2s))
     assert torch.isfinite(out.float()).all()
     assert O.max_rel_to_peak(out[toks].cpu(), ref) <= TOL
+
+
+def backward_rows_oracle(tokens, x, w1, w2, ids, wts, d_out):
+    """Autograd-through-the-fp32-oracle gradients d_x[t], d_topk_weights[t] for `tokens` (each depends on its own
+    token and the weights of the experts it routes to only)."""
+    dx, dwt = [], []
+    for t in tokens:
+        e = ids[t].long()
+        local = torch.arange(e.numel(), dtype=torch.int32).view(1, -1)
+        g = O.moe_backward_ref_fp32(x[t:t + 1].cpu(), w1[e.to(DEV)].cpu(), w2[e.to(DEV)].cpu(), local, wts[t:t + 1],
+                                    d_out[t:t + 1].cpu())
+        dx.append(g[0])
+        dwt.append(g[3])
+    return torch.cat(dx), torch.cat(dwt)
+
+
+@pytest.mark.parametrize("name,T,K,E,N,k,kept", [
+    ("c1", 4096, 4096, 8, 28672, 2, False),        # weight gradients on CTA pairs, pre-activations recomputed
+    ("c1", 4096, 4096, 8, 28672, 2, True),         # ... kept by the forward call
+    ("c2", 8192, 2048, 128, 1536, 8, False),
+])
+def test_backward_full_size(name, T, K, E, N, k, kept):
+    """The backward pass on benchmark layers at full size: d_x and d_topk_weights of sampled tokens against autograd
+    through the fp32 oracle, weight gradients of sampled experts on a slice of 256 hidden columns against the
+    slice-wise restatement (oracle.moe_backward_expert_slice_ref), linearity in d_out over the whole tensors."""
+    from prime_flash_moe_b200 import capi
+    H = N // 2
+    x, w1, w2, ids, wts = device_case(T, K, E, N, k, seed=41)
+    d_out = torch.randn(T, K, device=DEV, generator=torch.Generator(device=DEV).manual_seed(42)).to(torch.bfloat16)
+    s, e, n = capi.moe_align(ids.to(DEV), E, 128, 1)
+    dwts = wts.to(DEV)
+    gate_up = None
+    if kept:
+        _, gate_up = capi.fused_moe_bf16_keep(x, w1, w2, s, e, n, dwts, torch.empty_like(x), k)
+    d_x, d_w1, d_w2, d_wt = capi.fused_moe_bf16_backward(x, w1, w2, d_out, s, e, n, dwts, k, gate_up=gate_up)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    for g in (d_x, d_w1, d_w2, d_wt):
+        assert torch.isfinite(g.float()).all()
+    toks = spread(T, 12)
+    ref_dx, ref_dwt = backward_rows_oracle(toks, x, w1, w2, ids, wts, d_out)
+    assert O.max_rel_to_peak(d_x[toks].cpu(), ref_dx) <= TOL
+    assert O.max_rel_to_peak(d_wt[toks].cpu(), ref_dwt) <= TOL
+    for ex, h0 in ((0, 0), (E - 1, H - 256)):
+        tok, route = torch.nonzero(ids == ex, as_tuple=True)
+        hs = slice(h0, h0 + 256)
+        want = O.moe_backward_expert_slice_ref(x[tok.to(DEV)].cpu(), d_out[tok.to(DEV)].cpu(), wts[tok, route],
+                                               w1[ex, hs].cpu(), w1[ex, H + h0:H + h0 + 256].cpu(), w2[ex][:, hs].cpu())
+        got = (d_w1[ex, hs], d_w1[ex, H + h0:H + h0 + 256], d_w2[ex][:, hs])
+        for g, w in zip(got, want):
+            assert O.max_rel_to_peak(g.cpu(), w) <= TOL
+    # linearity: doubling d_out doubles every gradient (exact in bf16 up to the order of the fp32 atomics of d_wt)
+    twice = capi.fused_moe_bf16_backward(x, w1, w2, (d_out.float() * 2).to(torch.bfloat16), s, e, n, dwts, k,
+                                         gate_up=gate_up)
+    torch.cuda.synchronize()
+    for g, g2 in zip((d_x, d_w1, d_w2), twice[:3]):
+        assert torch.equal((g.float() * 2).to(torch.bfloat16), g2)
+    assert O.max_rel_to_peak(twice[3].cpu(), d_wt.cpu() * 2) <= 1e-5
