@@ -148,6 +148,38 @@ class LocalExperts:
         return None if out_rows is not None else out
 
 
+    # ---- training: forward that keeps what the backward pass needs, and the backward pass (bf16 experts only) ----
+    def parameters(self):
+        return (self.w1, self.w2)
+
+    def forward_keep(self, rows: torch.Tensor, local_ids: torch.Tensor, weights: torch.Tensor):
+        """``(y, saved)``: the weighted partial sums as ``__call__`` returns them and what ``backward`` needs (the
+        received rows, their routing tables and the gate/up pre-activations the gate/up kernel stored)."""
+        if self.w1_scales is not None:
+            raise RuntimeError("the backward pass exists for bf16 experts only")
+        ops = torch.ops.prime_moe
+        R, K = rows.shape
+        top_k = local_ids.shape[1]
+        out = torch.empty(R, K, dtype=torch.bfloat16, device=rows.device)
+        if R == 0:
+            return out, None
+        s, e, n = ops.moe_align(local_ids.contiguous(), self.num_local, 128, 1)
+        w = weights.reshape(-1).contiguous()
+        gate_up = ops.fused_moe_bf16_keep(rows, self.w1, self.w2, s, e, n, w, out, top_k)
+        return out, (rows, s, e, n, w, gate_up, top_k)
+
+    def backward(self, saved, d_y: torch.Tensor):
+        """``(d_rows [R, K] bf16, d_weights [R, top_k] fp32, (d_w1, d_w2))`` for the gradient ``d_y`` of ``y``."""
+        if saved is None:
+            top_k = 1
+            return (d_y.new_empty(0, d_y.shape[1]), torch.empty(0, top_k, dtype=torch.float32, device=d_y.device),
+                    (torch.zeros_like(self.w1), torch.zeros_like(self.w2)))
+        rows, s, e, n, w, gate_up, top_k = saved
+        d_rows, d_w1, d_w2, d_wt = torch.ops.prime_moe.fused_moe_bf16_backward(
+            rows, self.w1, self.w2, d_y.contiguous(), s, e, n, w, top_k, gate_up)
+        return d_rows, d_wt, (d_w1, d_w2)
+
+
 class _DeviceBytes:
     """``nbytes`` of device memory at ``ptr`` for ``torch.as_tensor`` (zero-copy view through the CUDA array interface)."""
 
@@ -378,14 +410,85 @@ class ExpertParallelMoE:
              else self.experts(rows, local_ids, weights))
         if self.world > 1:
             y = _all_to_all_rows(y, recv, send, self.group)
-        # combine at the source: out[t] = sum of the partial sums of the token's visits
-        if y.is_cuda:
-            return torch.ops.prime_moe.ep_combine(y.contiguous(), plan.slot_of)
-        slot = plan.slot_of.to(torch.int64)                      # CPU ranks (gloo tests of the host logic)
-        part = torch.cat([y.float(), torch.zeros(1, K)])[torch.where(slot >= 0, slot, torch.full_like(slot, y.shape[0]))]
-        return part.sum(1).to(torch.bfloat16)
+        return _combine_visits(y, plan.slot_of)
 
     __call__ = forward
+
+    def forward_train(self, x, topk_ids, topk_weights):
+        """The layer as a differentiable function (bf16 experts, NCCL exchange): gradients flow to ``x``,
+        ``topk_weights`` and the tensors of ``experts.parameters()``. The backward pass sends the output gradients
+        of the visits along the forward dispatch, runs ``experts.backward`` on the rank that owns the experts, and
+        returns the row gradients along the forward return (no counterpart in the reference)."""
+        return _ExpertParallelTrain.apply(self, x, topk_ids, topk_weights, *self.experts.parameters())
+
+
+def _combine_visits(y: torch.Tensor, slot_of: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum of the rows of the token's visits (bf16, fp32 sum)."""
+    if y.is_cuda:
+        return torch.ops.prime_moe.ep_combine(y.contiguous(), slot_of)
+    slot = slot_of.to(torch.int64)                               # CPU ranks (gloo tests of the host logic)
+    K = y.shape[1]
+    part = torch.cat([y.float(), torch.zeros(1, K)])[torch.where(slot >= 0, slot, torch.full_like(slot, y.shape[0]))]
+    return part.sum(1).to(torch.bfloat16)
+
+
+class _ExpertParallelTrain(torch.autograd.Function):
+    """Forward and backward pass of ``ExpertParallelMoE.forward_train`` (NCCL / gloo exchange)."""
+
+    @staticmethod
+    def forward(ctx, layer, x, topk_ids, topk_weights, *params):
+        top_k = topk_ids.shape[1]
+        plan = make_dispatch_plan(topk_ids, topk_weights.detach(), layer.num_experts, layer.world)
+        if layer.world > 1:
+            recv_counts = torch.empty_like(plan.counts)
+            dist.all_to_all_single(recv_counts, plan.counts, group=layer.group)
+            send, recv = plan.counts.tolist(), recv_counts.tolist()
+        else:
+            send = recv = plan.counts.tolist()
+        V = sum(send)
+        tokens = plan.visit_token[:V].long()
+        rows, meta = x.detach()[tokens], plan.visit_meta[:V]
+        if layer.world > 1:
+            rows = _all_to_all_rows(rows, send, recv, layer.group)
+            meta = _all_to_all_rows(meta, send, recv, layer.group)
+        layer._sent_rows, layer._recv_rows = V, rows.shape[0]
+        local_ids = meta[:, :top_k].contiguous()
+        weights = meta[:, top_k:].contiguous().view(torch.float32)
+        y, saved = layer.experts.forward_keep(rows, local_ids, weights)
+        if layer.world > 1:
+            y = _all_to_all_rows(y, recv, send, layer.group)
+        ctx.layer, ctx.saved, ctx.plan, ctx.send, ctx.recv, ctx.tokens = layer, saved, plan, send, recv, tokens
+        ctx.ids, ctx.weights_meta = topk_ids, (topk_weights.shape, topk_weights.dtype)
+        return _combine_visits(y, plan.slot_of)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        layer, plan, send, recv = ctx.layer, ctx.plan, ctx.send, ctx.recv
+        top_k = ctx.ids.shape[1]
+        d_y = d_out.contiguous()[ctx.tokens]                   # out[t] is the plain sum of its visits' rows
+        if layer.world > 1:
+            d_y = _all_to_all_rows(d_y, send, recv, layer.group)
+        d_rows, d_wt, param_grads = layer.experts.backward(ctx.saved, d_y)
+        d_rows = d_rows.to(torch.bfloat16)
+        d_wt = d_wt.float().reshape(-1, top_k)
+        if layer.world > 1:
+            d_rows = _all_to_all_rows(d_rows, recv, send, layer.group)
+            d_wt = _all_to_all_rows(d_wt.contiguous(), recv, send, layer.group)
+        d_x = _combine_visits(d_rows, plan.slot_of)
+        # routing weight (t, j) was used by the visit of token t to the rank that owns expert ids[t, j]
+        per = layer.num_experts // layer.world
+        ids = ctx.ids.to(torch.int64)
+        valid = (ids >= 0) & (ids < layer.num_experts)
+        dest = torch.where(valid, torch.div(ids, per, rounding_mode="floor"), torch.zeros_like(ids))
+        slot = plan.slot_of.to(torch.int64).gather(1, dest)
+        ok = valid & (slot >= 0)
+        col = torch.arange(top_k, device=ids.device).expand_as(slot)
+        if d_wt.shape[0] == 0:
+            d_weights = torch.zeros(ids.shape, dtype=torch.float32, device=ids.device)
+        else:
+            d_weights = torch.where(ok, d_wt[slot.clamp_min(0), col], torch.zeros((), device=ids.device))
+        shape, dtype = ctx.weights_meta
+        return (None, d_x.to(d_out.dtype), None, d_weights.reshape(shape).to(dtype)) + tuple(param_grads)
 
 
 def shard_experts(t: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
