@@ -71,10 +71,11 @@ def parse_args():
                          "default when the expert count divides), 'replica' runs N independent copies")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="headline workload only")
-    ap.add_argument("--op", default="moe", choices=["moe", "moe_align", "pre", "backward"],
+    ap.add_argument("--op", default="moe", choices=["moe", "moe_align", "pre", "backward", "train"],
                     help="'moe_align' times the routing kernels alone on the routing table of --config (GB/s line); "
                          "'pre' times the router and the MX activation quantiser alone at the c3 shapes; 'backward' times the "
-                         "bf16 backward pass and each of its steps on --config")
+                         "bf16 backward pass and each of its steps on --config; 'train' times forward + backward of the bf16 "
+                         "layer (expert-parallel under torchrun)")
     ap.add_argument("--ep-combine", default="auto", choices=["auto", "nccl", "peer"],
                     help="expert-parallel combine: NCCL all-to-all, or this library's kernel storing into the source "
                          "rank's buffer over NVLink (auto = peer when every rank can map its peers)")
@@ -1239,6 +1240,66 @@ def run_backward_only(args):
     print(json.dumps(e))
 
 
+def run_train_only(args):
+    """`--op train`: one training step of the bf16 layer on --config - forward that keeps the gate/up
+    pre-activations + backward (9·T·k·K·N FLOPs per rank). One GPU: the autograd layer `moe_ffn`; under torchrun: the
+    expert-parallel layer's `forward_train` (E / N experts and T tokens per rank, NCCL exchange). Timed with CUDA
+    events over --steps steps after --warmup, max over ranks; one JSON line from rank 0."""
+    import torch
+    world, rank, local = dist_setup(args)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    sys.path.insert(0, str(ROOT))
+    import prime_flash_moe_b200 as P
+    from prime_flash_moe_b200 import capi, ep
+    T, K, E, N, k, routing = CONFIGS[args.config]
+    if args.tokens:
+        T = args.tokens
+    assert E % world == 0, "the experts must divide over the ranks"
+    per = E // world
+    g = torch.Generator(device=device).manual_seed(7000 + rank)
+    x = torch.randn(T, K, device=device, generator=g).to(torch.bfloat16).requires_grad_(True)
+    d_out = torch.randn(T, K, device=device, generator=g).to(torch.bfloat16)
+    gw = torch.Generator(device=device).manual_seed(7100 + rank)          # this rank's experts only
+    w1 = (torch.randn(per, N, K, device=device, generator=gw, dtype=torch.bfloat16) * K ** -0.5).requires_grad_(True)
+    w2 = (torch.randn(per, K, N // 2, device=device, generator=gw, dtype=torch.bfloat16) * (N // 2) ** -0.5).requires_grad_(True)
+    from oracle import moe_oracle as O
+    ids, wts = O.make_routing(T, E, k, 7200 + rank, routing)
+    ids, wts = ids.to(device), wts.to(device).requires_grad_(True)
+    if world > 1:
+        layer = ep.ExpertParallelMoE(E, ep.LocalExperts(w1, w2), combine="nccl")
+        fwd = lambda: layer.forward_train(x, ids, wts)
+    else:
+        fwd = lambda: P.moe_ffn(x, w1, w2, ids, wts)
+
+    def step():
+        for t in (x, w1, w2, wts):
+            t.grad = None
+        fwd().backward(d_out)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier_sync(world)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    barrier_sync(world)
+    ms = max_over_ranks(a.elapsed_time(b) / args.steps, world, device)
+    assert capi.device_status() == 0, "a kernel recorded an error status"
+    if rank == 0:
+        flops = 9.0 * T * k * K * N * world
+        print(json.dumps({"metric": "moe_ffn_train_step_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+                          "impl": "ours", "tokens_per_s": T * world / (ms * 1e-3),
+                          "config": {"workload": args.config, "tokens_per_rank": T, "experts_per_rank": per,
+                                     "parallelism": f"ep{world}" if world > 1 else "single",
+                                     "exchange": "nccl all-to-all" if world > 1 else None,
+                                     "flops": "forward 3·T·k·K·N + backward 6·T·k·K·N (pre-activations kept)"}}))
+
+
 def main():
     args = parse_args()
     if args.bpc == 0:
@@ -1254,6 +1315,8 @@ def main():
         run_pre_only(args)
     elif args.op == "backward":
         run_backward_only(args)
+    elif args.op == "train":
+        run_train_only(args)
     elif args.impl == "cpu":
         run_cpu_arm(args)
     else:
