@@ -718,12 +718,19 @@ def sweep_backward_entry(name, tokens, device, peaks):
     _, gate_up = capi.fused_moe_bf16_keep(c["x"], c["w1"], c["w2"], s, e, n, c["wts"], out, k)
     ms_kept = time_calls(lambda: capi.fused_moe_bf16_backward(c["x"], c["w1"], c["w2"], d_out, s, e, n, c["wts"], k,
                                                               workspace=ws, gate_up=gate_up), reps, flush_buf)
+    # ... and with the weight gradients added into fp32 tensors (a trainer's main gradients) by the wgrad epilogue
+    main_grads = (torch.zeros(E, N, K, dtype=torch.float32, device=device),
+                  torch.zeros(E, K, N // 2, dtype=torch.float32, device=device))
+    ms_acc = time_calls(lambda: capi.fused_moe_bf16_backward(c["x"], c["w1"], c["w2"], d_out, s, e, n, c["wts"], k,
+                                                             workspace=ws, gate_up=gate_up, d_w=main_grads,
+                                                             accumulate=True), reps, flush_buf)
     torch.cuda.synchronize()
     assert capi.device_status() == 0, "a kernel recorded an error status"
     ach = flops / (ms * 1e-3) / 1e12
     kept = {"backward_ms": ms_kept, "forward_ms": fwd_keep, "forward_ms_without_keeping": fwd_plain,
-            "tflops_over_2_thirds_of_flops": (6.0 * T * k * K * N) / (ms_kept * 1e-3) / 1e12}
-    del c, ws, d_out, flush_buf, gate_up, out
+            "tflops_over_2_thirds_of_flops": (6.0 * T * k * K * N) / (ms_kept * 1e-3) / 1e12,
+            "backward_ms_accumulating_into_fp32_weight_gradients": ms_acc}
+    del c, ws, d_out, flush_buf, gate_up, out, main_grads
     torch.cuda.empty_cache()
     return {"config": name, "tokens": T, "op": "backward", "dtype": "bf16", "ms_per_step": ms, "value": ach,
             "unit": "TFLOP/s", "with_kept_pre_activations": kept,

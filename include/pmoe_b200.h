@@ -214,6 +214,17 @@ int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, 
                                  int K, int N, int num_experts, int sorted_num, void *d_x, void *d_w1, void *d_w2,
                                  float *d_topk_weights, const void *gate_up, void *workspace,
                                  size_t workspace_bytes, pmoe_stream_t stream);
+/* The same with a choice of how the weight gradients are delivered: dw_dtype PMOE_DTYPE_BF16 or PMOE_DTYPE_F32 (d_w1,
+ * d_w2 are then fp32 tensors of the same shapes), accumulate_dw != 0 adds to what d_w1 / d_w2 hold instead of
+ * overwriting it (a trainer's fp32 main gradients over several micro-batches: the read-modify-write happens in the
+ * weight-gradient kernel's epilogue, every element owned by one thread, no atomics, and the separate bf16 gradient
+ * tensor with its add pass disappears). Experts without rows are left alone when accumulating. */
+int pmoe_fused_moe_bf16_backward_ex(const void *x, const void *w1, const void *w2, const void *d_out,
+                                    const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                    const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k, int T,
+                                    int K, int N, int num_experts, int sorted_num, void *d_x, void *d_w1, void *d_w2,
+                                    float *d_topk_weights, const void *gate_up, int dw_dtype, int accumulate_dw,
+                                    void *workspace, size_t workspace_bytes, pmoe_stream_t stream);
 /* Forward call that keeps what the backward pass would otherwise recompute: pmoe_fused_moe_bf16_ws with the knobs
  * fixed (block_m 128, bpc 1, split pipeline) whose gate/up kernel also stores its pre-activations (bf16, as rounded
  * from the fp32 accumulators) into gate_up bf16[sorted_num, N] (32-byte aligned; row r = row r of sorted_token_ids,

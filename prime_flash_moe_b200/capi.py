@@ -55,6 +55,7 @@ SIGNATURES = {
     "pmoe_quantize_mx": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "pmoe_fused_moe_bf16_backward_workspace_bytes": (_sz, [_i] * 6),
     "pmoe_fused_moe_bf16_backward": (_i, [_vp] * 8 + [_i] * 6 + [_vp] * 6 + [_sz, _vp]),
+    "pmoe_fused_moe_bf16_backward_ex": (_i, [_vp] * 8 + [_i] * 6 + [_vp] * 5 + [_i, _i, _vp, _sz, _vp]),
     "pmoe_fused_moe_bf16_keep_ws": (_i, [_vp] * 8 + [_i] * 6 + [_vp, _vp, _sz, _vp]),
     "pmoe_debug_set_backward_mask": (_i, [_i]),
     "pmoe_debug_set_wait_ns": (_i, [C.c_ulonglong]),
@@ -176,25 +177,34 @@ def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_
 
 
 def fused_moe_bf16_backward(x, w, w2, d_out, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights,
-                            top_k, need_weight_grad=True, workspace=None, gate_up=None):
+                            top_k, need_weight_grad=True, workspace=None, gate_up=None, d_w=None, accumulate=False):
     """Gradients of ``fused_moe_bf16`` for ``d_out`` [T, K]: ``(d_x [T, K], d_w [E, N, K], d_w2 [E, K, N/2],
-    d_topk_weights fp32 [T, top_k] | None)``, the routing tensors being those of the forward call (block_m = 128)."""
+    d_topk_weights fp32 [T, top_k] | None)``, the routing tensors being those of the forward call (block_m = 128).
+    ``d_w=(d_w, d_w2)``: bf16 or fp32 tensors to write the weight gradients into, or - with ``accumulate`` - to add
+    them to."""
     T, K = x.shape
     E, N, _ = w.shape
     assert d_out.shape == x.shape and d_out.dtype == torch.bfloat16 and d_out.is_contiguous()
     d_x = torch.empty_like(x)
-    d_w = torch.empty_like(w)
-    d_w2 = torch.empty_like(w2)
+    if d_w is None:
+        assert not accumulate
+        d_w1, d_w2 = torch.empty_like(w), torch.empty_like(w2)
+    else:
+        d_w1, d_w2 = d_w
+        assert d_w1.shape == w.shape and d_w2.shape == w2.shape and d_w1.dtype == d_w2.dtype
+        assert d_w1.is_contiguous() and d_w2.is_contiguous()
+    dw_dtype = {torch.float32: 0, torch.bfloat16: 1}[d_w1.dtype]
     d_wt = torch.empty(T, top_k, dtype=torch.float32, device=x.device) if need_weight_grad else None
     with torch.cuda.device(x.device):
         if workspace is None:
             workspace = _workspace(lib().pmoe_fused_moe_bf16_backward_workspace_bytes(
                 T, K, N, E, top_k, sorted_token_ids.numel()), x.device)
-        _check(lib().pmoe_fused_moe_bf16_backward(
+        _check(lib().pmoe_fused_moe_bf16_backward_ex(
             _p(x), _p(w), _p(w2), _p(d_out), _p(sorted_token_ids), _p(expert_ids), _p(num_tokens_post_padded),
-            _p(topk_weights), top_k, T, K, N, E, sorted_token_ids.numel(), _p(d_x), _p(d_w), _p(d_w2), _p(d_wt),
-            _p(gate_up), _p(workspace), workspace.numel() * workspace.element_size(), _stream()))
-    return d_x, d_w, d_w2, d_wt
+            _p(topk_weights), top_k, T, K, N, E, sorted_token_ids.numel(), _p(d_x), _p(d_w1), _p(d_w2), _p(d_wt),
+            _p(gate_up), dw_dtype, int(accumulate), _p(workspace), workspace.numel() * workspace.element_size(),
+            _stream()))
+    return d_x, d_w1, d_w2, d_wt
 
 
 def route_topk(logits: torch.Tensor, top_k: int, renormalize: bool = True):

@@ -52,7 +52,9 @@ enum : int {
     MODE_NN_SWIGLU = 1,    // C[R, h] = A[R, k] . B[e][k, h]            B N-major          SwiGLU backward epilogue
     MODE_NN_STORE = 2,     // C[R, n] = A[R, k] . B[e][k, n]            B N-major          plain bf16 store
     MODE_WGRAD = 3,        // C[e][m, n] = sum over the expert's rows A[r, m] . B[r, n]    both M/N-major
+    MODE_WGRAD_X = 4,      // the same with an fp32 and / or accumulated gradient (C = or += per GArgs::c_f32, accumulate)
 };
+__host__ __device__ constexpr bool is_wgrad(int mode) { return mode >= MODE_WGRAD; }
 
 struct GArgs {
     int mode;
@@ -71,6 +73,8 @@ struct GArgs {
     long long ldc;
     int c_cols;                   // live columns of C
     int c_rows;                   // MODE_WGRAD: rows of one expert's C
+    float *c_f32;                 // MODE_WGRAD_X: fp32 gradient (then `c` is unused), else null
+    int accumulate;               // MODE_WGRAD_X: add to the gradient already there instead of overwriting it
     // MODE_NN_SWIGLU
     const __nv_bfloat16 *gu;      // [R, N] gate | up pre-activations
     __nv_bfloat16 *dgu;           // [R, N]
@@ -200,7 +204,7 @@ __device__ __forceinline__ int num_row_items(const GArgs &a) {
 template <int MODE>
 __device__ __forceinline__ Tile decode_tile(const GArgs &a, int t, int m_items) {
     Tile tl;
-    if (MODE == MODE_WGRAD) {
+    if (is_wgrad(MODE)) {
         const int per = a.m_tiles * a.n_tiles;
         tl.e = t / per;
         const int rem = t - tl.e * per;
@@ -290,6 +294,46 @@ __device__ __forceinline__ void drain_tile(const GArgs &a, uint32_t acc, uint32_
         if (a.dwt && valid) atomicAdd(a.dwt + pair, part);
         return;
     }
+    if (MODE == MODE_WGRAD_X) {
+        // fp32 and / or accumulated weight gradient: a lane owns 32 consecutive columns of its row per chunk
+        if (m >= a.c_rows) return;
+        const size_t off = (static_cast<size_t>(e) * a.c_rows + m) * a.ldc + col0;
+        for (int ch = cg * 4; ch < cg * 4 + 4; ++ch) {
+            if (col0 + ch * 32 >= a.c_cols) break;
+            float v[32], old[32];
+            tmem_ld_32x32(v, tmem_addr(acc, lane_base, ch * 32));
+            if (a.accumulate) {
+                if (a.c_f32) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t w[8];
+                        ld_global_v8(a.c_f32 + off + ch * 32 + 8 * j, w);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) old[8 * j + q] = __uint_as_float(w[q]);
+                    }
+                } else {
+                    load_chunk_bf16(a.c + off + ch * 32, old);
+                }
+            }
+            tmem_ld_wait();
+            if (a.accumulate) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += old[j];
+            }
+            if (a.c_f32) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) w[q] = __float_as_uint(v[8 * j + q]);
+                    st_global_v8(a.c_f32 + off + ch * 32 + 8 * j, w);
+                }
+            } else {
+                store_chunk_bf16(a.c + off + ch * 32, v);
+            }
+        }
+        return;
+    }
     __nv_bfloat16 *dst;
     bool row_ok = true;
     if (MODE == MODE_WGRAD) {
@@ -309,7 +353,14 @@ __device__ __forceinline__ void drain_tile(const GArgs &a, uint32_t acc, uint32_
 
 // MODE_WGRAD, an expert without rows: its weight gradient is zero (no accumulator involved)
 __device__ __forceinline__ void zero_tile(const GArgs &a, int cg, int e, int m, int col0) {
-    if (m >= a.c_rows) return;
+    if (m >= a.c_rows || a.accumulate) return;      // nothing to add
+    if (a.c_f32) {
+        float *dst32 = a.c_f32 + (static_cast<size_t>(e) * a.c_rows + m) * a.ldc + col0;
+        for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
+            if (col0 + ch * 32 < a.c_cols)
+                for (int j = 0; j < 8; ++j) reinterpret_cast<uint4 *>(dst32 + ch * 32)[j] = make_uint4(0, 0, 0, 0);
+        return;
+    }
     __nv_bfloat16 *dst = a.c + (static_cast<size_t>(e) * a.c_rows + m) * a.ldc + col0;
     for (int ch = cg * 4; ch < cg * 4 + 4; ++ch)
         if (col0 + ch * 32 < a.c_cols)
@@ -347,7 +398,7 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
 
-    constexpr bool a_mn = MODE == MODE_WGRAD;
+    constexpr bool a_mn = is_wgrad(MODE);
     constexpr bool b_mn = MODE != MODE_NT_STORE;
     const int m_items = a_mn ? 0 : num_row_items(a);
     const int num_tiles = a_mn ? a.E * a.m_tiles * a.n_tiles : m_items * a.n_tiles;
@@ -491,7 +542,7 @@ struct RingPair {
 template <int MODE>
 __device__ __forceinline__ Tile decode_pair_tile(const GArgs &a, int t, int m_items, int m_tiles2) {
     Tile tl;
-    if (MODE == MODE_WGRAD) {
+    if (is_wgrad(MODE)) {
         const int per = m_tiles2 * a.n_tiles;
         tl.e = t / per;
         const int rem = t - tl.e * per;
@@ -546,7 +597,7 @@ moe_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(sm.tmem_slot()));
 
-    constexpr bool wgrad = MODE == MODE_WGRAD;
+    constexpr bool wgrad = is_wgrad(MODE);
     constexpr bool b_mn = MODE != MODE_NT_STORE;
     const int m_tiles2 = (a.c_rows + 255) / 256;
     const int m_items = wgrad ? 0 : *a.item_count;
@@ -737,7 +788,8 @@ int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cu
         case MODE_NT_STORE: return launch_gemm_mode<MODE_NT_STORE>(ma, mb, g, stream);
         case MODE_NN_SWIGLU: return launch_gemm_mode<MODE_NN_SWIGLU>(ma, mb, g, stream);
         case MODE_NN_STORE: return launch_gemm_mode<MODE_NN_STORE>(ma, mb, g, stream);
-        default: return launch_gemm_mode<MODE_WGRAD>(ma, mb, g, stream);
+        case MODE_WGRAD: return launch_gemm_mode<MODE_WGRAD>(ma, mb, g, stream);
+        default: return launch_gemm_mode<MODE_WGRAD_X>(ma, mb, g, stream);
     }
 }
 
@@ -775,7 +827,7 @@ int launch_pair_mode(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &
     PMOE_CUDA_OK(cudaOccupancyMaxActiveClusters(&max_clusters, moe_bwd_pair_kernel<MODE>, &cfg));
     if (max_clusters < 1) return set_error(PMOE_ERR_CUDA, "no CTA pair of the backward GEMM kernel fits on this device");
     // upper bound of the tile count known on the host (the row-space modes read theirs on the device)
-    const long long tiles = g.mode == MODE_WGRAD ? static_cast<long long>(g.E) * ((g.c_rows + 255) / 256) * g.n_tiles
+    const long long tiles = is_wgrad(g.mode) ? static_cast<long long>(g.E) * ((g.c_rows + 255) / 256) * g.n_tiles
                                                  : static_cast<long long>(g.sorted_num / 256 + 1) * g.n_tiles;
     cfg.gridDim = dim3(2 * static_cast<unsigned>(std::min<long long>(tiles, max_clusters)));
     PMOE_CUDA_OK(cudaLaunchKernelEx(&cfg, moe_bwd_pair_kernel<MODE>, ma, mb, g));
@@ -787,7 +839,8 @@ int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const GArgs &g, cu
         case MODE_NT_STORE: return launch_pair_mode<MODE_NT_STORE>(ma, mb, g, stream);
         case MODE_NN_SWIGLU: return launch_pair_mode<MODE_NN_SWIGLU>(ma, mb, g, stream);
         case MODE_NN_STORE: return launch_pair_mode<MODE_NN_STORE>(ma, mb, g, stream);
-        default: return launch_pair_mode<MODE_WGRAD>(ma, mb, g, stream);
+        case MODE_WGRAD: return launch_pair_mode<MODE_WGRAD>(ma, mb, g, stream);
+        default: return launch_pair_mode<MODE_WGRAD_X>(ma, mb, g, stream);
     }
 }
 
@@ -830,15 +883,18 @@ extern "C" size_t pmoe_fused_moe_bf16_backward_workspace_bytes(int T, int K, int
     return pmoe::plan_backward(T, K, N, num_experts, top_k, sorted_num).total;
 }
 
-extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, const void *d_out,
-                                            const int32_t *sorted_token_ids, const int32_t *expert_ids,
-                                            const int32_t *num_tokens_post_padded, const float *topk_weights,
-                                            int top_k, int T, int K, int N, int num_experts, int sorted_num,
-                                            void *d_x, void *d_w1, void *d_w2, float *d_topk_weights,
-                                            const void *gate_up, void *workspace, size_t workspace_bytes,
-                                            pmoe_stream_t stream_) {
+extern "C" int pmoe_fused_moe_bf16_backward_ex(const void *x, const void *w1, const void *w2, const void *d_out,
+                                               const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                               const int32_t *num_tokens_post_padded, const float *topk_weights,
+                                               int top_k, int T, int K, int N, int num_experts, int sorted_num,
+                                               void *d_x, void *d_w1, void *d_w2, float *d_topk_weights,
+                                               const void *gate_up, int dw_dtype, int accumulate_dw, void *workspace,
+                                               size_t workspace_bytes, pmoe_stream_t stream_) {
     using namespace pmoe;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PMOE_REQUIRE(dw_dtype == PMOE_DTYPE_BF16 || dw_dtype == PMOE_DTYPE_F32, PMOE_ERR_BAD_ARG,
+                 "fused_moe_bf16_backward: dw_dtype must be PMOE_DTYPE_BF16 or PMOE_DTYPE_F32");
+    const bool dw_f32 = dw_dtype == PMOE_DTYPE_F32, dw_extended = dw_f32 || accumulate_dw != 0;
     PMOE_REQUIRE(x && w1 && w2 && d_out && sorted_token_ids && expert_ids && num_tokens_post_padded && topk_weights &&
                      d_x && d_w1 && d_w2,
                  PMOE_ERR_BAD_ARG, "fused_moe_bf16_backward: null pointer");
@@ -858,10 +914,13 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     PMOE_REQUIRE(((reinterpret_cast<uintptr_t>(d_w1) | reinterpret_cast<uintptr_t>(d_w2)) & 31) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16_backward: d_w1 and d_w2 must be 32-byte aligned (256-bit stores)");
     const int H = N / 2, E = num_experts;
-    const size_t w1_bytes = static_cast<size_t>(E) * N * K * 2, w2_bytes = static_cast<size_t>(E) * K * H * 2;
+    const size_t w_elem = dw_f32 ? 4 : 2;
+    const size_t w1_bytes = static_cast<size_t>(E) * N * K * w_elem, w2_bytes = static_cast<size_t>(E) * K * H * w_elem;
     if (T == 0 || sorted_num == 0) {   // no routed row: every gradient is zero
-        PMOE_CUDA_OK(cudaMemsetAsync(d_w1, 0, w1_bytes, stream));
-        PMOE_CUDA_OK(cudaMemsetAsync(d_w2, 0, w2_bytes, stream));
+        if (!accumulate_dw) {
+            PMOE_CUDA_OK(cudaMemsetAsync(d_w1, 0, w1_bytes, stream));
+            PMOE_CUDA_OK(cudaMemsetAsync(d_w2, 0, w2_bytes, stream));
+        }
         return PMOE_OK;
     }
     const BwdLayout lay = plan_backward(T, K, N, E, top_k, sorted_num);
@@ -951,8 +1010,9 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     }
     if (mask & 8) {   // d_W2[e] [K, H] = dos_e^T . (wt * act)_e
         GArgs g = base;
-        g.mode = MODE_WGRAD, g.m_tiles = (K + 127) / 128, g.n_tiles = (H + 255) / 256;
+        g.mode = dw_extended ? MODE_WGRAD_X : MODE_WGRAD, g.m_tiles = (K + 127) / 128, g.n_tiles = (H + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w2), g.ldc = H, g.c_cols = H, g.c_rows = K;
+        g.c_f32 = dw_f32 ? static_cast<float *>(d_w2) : nullptr, g.accumulate = accumulate_dw ? 1 : 0;
         if (int rc = (pairs ? launch_pair : launch_gemm)(dos_mn, actw_mn, g, stream)) return rc;
     }
     if (mask & 16) {   // d_xs = d_gu . W1[e], written over dos (dead from here on)
@@ -963,8 +1023,9 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
     }
     if (mask & 32) {   // d_W1[e] [N, K] = d_gu_e^T . xs_e
         GArgs g = base;
-        g.mode = MODE_WGRAD, g.m_tiles = (N + 127) / 128, g.n_tiles = (K + 255) / 256;
+        g.mode = dw_extended ? MODE_WGRAD_X : MODE_WGRAD, g.m_tiles = (N + 127) / 128, g.n_tiles = (K + 255) / 256;
         g.c = static_cast<__nv_bfloat16 *>(d_w1), g.ldc = K, g.c_cols = K, g.c_rows = N;
+        g.c_f32 = dw_f32 ? static_cast<float *>(d_w1) : nullptr, g.accumulate = accumulate_dw ? 1 : 0;
         if (int rc = (pairs ? launch_pair : launch_gemm)(dgu_mn, xs_mn, g, stream)) return rc;
     }
     if (mask & 64) {
@@ -972,4 +1033,16 @@ extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const
         PMOE_CUDA_OK(cudaGetLastError());
     }
     return PMOE_OK;
+}
+
+extern "C" int pmoe_fused_moe_bf16_backward(const void *x, const void *w1, const void *w2, const void *d_out,
+                                            const int32_t *sorted_token_ids, const int32_t *expert_ids,
+                                            const int32_t *num_tokens_post_padded, const float *topk_weights,
+                                            int top_k, int T, int K, int N, int num_experts, int sorted_num,
+                                            void *d_x, void *d_w1, void *d_w2, float *d_topk_weights,
+                                            const void *gate_up, void *workspace, size_t workspace_bytes,
+                                            pmoe_stream_t stream) {
+    return pmoe_fused_moe_bf16_backward_ex(x, w1, w2, d_out, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                           topk_weights, top_k, T, K, N, num_experts, sorted_num, d_x, d_w1, d_w2,
+                                           d_topk_weights, gate_up, PMOE_DTYPE_BF16, 0, workspace, workspace_bytes, stream);
 }

@@ -59,6 +59,40 @@ def test_cta_pair_settings_agree_with_the_oracle(pairs, monkeypatch):
     check(run_backward(x, w1, w2, ids, wts, d_out), refs)
 
 
+@pytest.mark.parametrize("pairs", ["0", "1"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_weight_gradients_in_fp32_and_accumulated(dtype, pairs, monkeypatch):
+    """pmoe_fused_moe_bf16_backward_ex: fp32 weight gradients (tighter against the oracle than bf16 ones), and
+    accumulation into what the tensors hold - two calls on a preset tensor give preset + 2 x gradient; experts
+    without rows keep the preset."""
+    from prime_flash_moe_b200 import capi
+    monkeypatch.setenv("PMOE_BWD_PAIRS", pairs)
+    T, K, E, N, k = 600, 384, 6, 512, 2
+    x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=31)
+    ids = (ids % 5).to(torch.int32)                       # expert 5 gets no rows
+    ids[:, 1] = (ids[:, 0] + 1) % 5
+    d_out = torch.randn(T, K, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    refs = O.moe_backward_ref_fp32(x, w1, w2, ids, wts, d_out)
+    s, e, n = capi.moe_align(ids.to(DEV), E, 128, 1)
+    args = (x.to(DEV), w1.to(DEV), w2.to(DEV), d_out.to(DEV), s, e, n, wts.to(DEV), k)
+    plain = (torch.empty(E, N, K, dtype=dtype, device=DEV), torch.empty(E, K, N // 2, dtype=dtype, device=DEV))
+    capi.fused_moe_bf16_backward(*args, d_w=plain)
+    torch.cuda.synchronize()
+    tol = 6e-3 if dtype == torch.float32 else TOL         # what is left is the bf16 rounding of d_gu / act
+    assert O.max_rel_to_peak(plain[0].cpu(), refs[1]) <= tol and O.max_rel_to_peak(plain[1].cpu(), refs[2]) <= tol
+    assert float(plain[0][5].float().abs().max()) == 0.0 and float(plain[1][5].float().abs().max()) == 0.0
+    acc = (torch.full((E, N, K), 0.5, dtype=dtype, device=DEV), torch.full((E, K, N // 2), -0.25, dtype=dtype, device=DEV))
+    for _ in range(2):
+        capi.fused_moe_bf16_backward(*args, d_w=acc, accumulate=True)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    for got, base, ref, preset in ((acc[0], plain[0], refs[1], 0.5), (acc[1], plain[1], refs[2], -0.25)):
+        want = preset + 2 * base.float()
+        scale = float(ref.abs().max())
+        assert float((got.float() - want).abs().max()) <= (1e-5 if dtype == torch.float32 else 2e-2) * max(scale, 1.0)
+        assert float((got[5].float() - preset).abs().max()) == 0.0
+
+
 def test_experts_without_rows_get_zero_weight_gradients():
     T, K, E, N, k = 8, 256, 16, 256, 2
     x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=3)
