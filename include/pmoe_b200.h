@@ -199,7 +199,8 @@ int pmoe_quantize_mx(const void *x /* bf16[src_rows, K] */, const int32_t *row_i
 
 /* ---------------------------------------------------------------------------------------------
  * Backward pass of pmoe_fused_moe_bf16 (no counterpart in the reference, which is forward-only, README.md:17).
- * Same routing tensors as the forward call (moe_align output with block_m = 128, pad_to = 128) and the same x,
+ * Same routing tensors as the forward call (moe_align output with block_m = 128; bpc 1 or 2 - 128-row blocks without
+ * any routed row, which bpc = 2 tables contain, are skipped) and the same x,
  * w1 [E, N, K], w2 [E, K, N/2]; d_out bf16[T, K] is the gradient of `out`. Writes (does not accumulate into)
  *   d_x  bf16[T, K]        d_w1 bf16[E, N, K]        d_w2 bf16[E, K, N/2]   (experts without rows get zeros)
  *   d_topk_weights fp32[T, top_k], or NULL to skip it (entries of routes to ids outside [0, E) stay 0)
@@ -226,16 +227,17 @@ int pmoe_fused_moe_bf16_backward_ex(const void *x, const void *w1, const void *w
                                     float *d_topk_weights, const void *gate_up, int dw_dtype, int accumulate_dw,
                                     void *workspace, size_t workspace_bytes, pmoe_stream_t stream);
 /* Forward call that keeps what the backward pass would otherwise recompute: pmoe_fused_moe_bf16_ws with the knobs
- * fixed (block_m 128, bpc 1, split pipeline) whose gate/up kernel also stores its pre-activations (bf16, as rounded
+ * fixed (block_m 128, split pipeline; bpc 1 or 2 as moe_align was run) whose gate/up kernel also stores its pre-activations (bf16, as rounded
  * from the fp32 accumulators) into gate_up bf16[sorted_num, N] (32-byte aligned; row r = row r of sorted_token_ids,
- * columns [0, N/2) gate, [N/2, N) up; rows of padding hold finite values nobody uses). Passing that buffer as
+ * columns [0, N/2) gate, [N/2, N) up; rows of padding hold values nobody uses, 128-row blocks without any routed
+ * row may stay unwritten). Passing that buffer as
  * `gate_up` to pmoe_fused_moe_bf16_backward skips its recompute GEMM (a quarter of the step on wide layers); NULL
  * there means recompute. No counterpart in the reference. */
 int pmoe_fused_moe_bf16_keep_ws(const void *x, const void *w, const void *w2, void *out,
                                 const int32_t *sorted_token_ids, const int32_t *expert_ids,
                                 const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k, int M,
-                                int K, int N, int num_experts, int sorted_num, void *gate_up, void *workspace,
-                                size_t workspace_bytes, pmoe_stream_t stream);
+                                int K, int N, int num_experts, int sorted_num, int bpc, void *gate_up,
+                                void *workspace, size_t workspace_bytes, pmoe_stream_t stream);
 /* Measurement hook: which steps of the backward pass run. Bits: 1 row maps + row gathers, 2 gate/up recompute,
  * 4 d_act + SwiGLU derivative, 8 d_w2, 16 d_xs, 32 d_w1, 64 d_x combine; 127 = all (default). Returns the old mask.
  * With bits missing the outputs are incomplete. */

@@ -131,26 +131,28 @@ def fused_moe_bf16_backward(x, w, w2, d_out, sorted_token_ids, expert_ids, num_t
                                                        num_tokens_post_padded, topk_weights, top_k, gate_up)
 
 
-def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k):
-    """``fused_moe_bf16`` (split pipeline, bpc = 1) writing ``out`` and returning the gate/up pre-activations
-    ``[sorted_num, N]`` its gate/up kernel saw, for ``fused_moe_bf16_backward(..., gate_up=...)``."""
+def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k,
+                        bpc=1):
+    """``fused_moe_bf16`` (split pipeline; ``bpc`` as ``moe_align`` was run) writing ``out`` and returning the gate/up
+    pre-activations ``[sorted_num, N]`` its gate/up kernel saw, for ``fused_moe_bf16_backward(..., gate_up=...)``."""
     return torch.ops.prime_moe.fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded,
-                                                   topk_weights, out, top_k)
+                                                   topk_weights, out, top_k, bpc)
 
 
 class _MoEFFN(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, w2, topk_ids, topk_weights, recompute):
         num_experts, top_k = w.shape[0], topk_ids.shape[1]
-        sorted_ids, expert_ids, npp = torch.ops.prime_moe.moe_align(topk_ids, num_experts, 128, 1)
+        bpc = 2 if w.shape[1] >= 8192 else 1        # CTA pairs pay off on wide layers (as in bench.py)
+        sorted_ids, expert_ids, npp = torch.ops.prime_moe.moe_align(topk_ids, num_experts, 128, bpc)
         wts = topk_weights.detach().float().contiguous()
         out = torch.empty_like(x)
         gate_up = None
         if recompute:
-            torch.ops.prime_moe.fused_moe_bf16(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k, 128, 64, 4, 4, 1, 1,
-                                               True)
+            torch.ops.prime_moe.fused_moe_bf16(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k, 128, 64, 4, 4, bpc,
+                                               1, True)
         else:
-            gate_up = fused_moe_bf16_keep(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k)
+            gate_up = fused_moe_bf16_keep(x, w, w2, sorted_ids, expert_ids, npp, wts, out, top_k, bpc)
         ctx.save_for_backward(x, w, w2, sorted_ids, expert_ids, npp, wts, gate_up)
         ctx.top_k = top_k
         ctx.weights_dtype = topk_weights.dtype

@@ -56,7 +56,7 @@ SIGNATURES = {
     "pmoe_fused_moe_bf16_backward_workspace_bytes": (_sz, [_i] * 6),
     "pmoe_fused_moe_bf16_backward": (_i, [_vp] * 8 + [_i] * 6 + [_vp] * 6 + [_sz, _vp]),
     "pmoe_fused_moe_bf16_backward_ex": (_i, [_vp] * 8 + [_i] * 6 + [_vp] * 5 + [_i, _i, _vp, _sz, _vp]),
-    "pmoe_fused_moe_bf16_keep_ws": (_i, [_vp] * 8 + [_i] * 6 + [_vp, _vp, _sz, _vp]),
+    "pmoe_fused_moe_bf16_keep_ws": (_i, [_vp] * 8 + [_i] * 7 + [_vp, _vp, _sz, _vp]),
     "pmoe_debug_set_backward_mask": (_i, [_i]),
     "pmoe_debug_set_wait_ns": (_i, [C.c_ulonglong]),
     "pmoe_debug_wait_probe": (_i, [_vp]),
@@ -160,8 +160,9 @@ def fused_moe_mxfp8(x, x_scales, w, w_scales, w2, w2_scales, sorted_token_ids, e
     return out
 
 
-def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k):
-    """``fused_moe_bf16`` (split pipeline, bpc = 1) that also returns the gate/up pre-activations
+def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_padded, topk_weights, out, top_k,
+                        bpc=1):
+    """``fused_moe_bf16`` (split pipeline; ``bpc`` as ``moe_align`` was run) that also returns the gate/up pre-activations
     ``[sorted_num, N]`` for ``fused_moe_bf16_backward(..., gate_up=...)``."""
     M, K = x.shape
     E, N, _ = w.shape
@@ -171,7 +172,7 @@ def fused_moe_bf16_keep(x, w, w2, sorted_token_ids, expert_ids, num_tokens_post_
         workspace = _workspace(lib().pmoe_fused_moe_bf16_workspace_bytes(M, K, N, R, 1), x.device)
         _check(lib().pmoe_fused_moe_bf16_keep_ws(
             _p(x), _p(w), _p(w2), _p(out), _p(sorted_token_ids), _p(expert_ids), _p(num_tokens_post_padded),
-            _p(topk_weights), top_k, M, K, N, E, R, _p(gate_up), _p(workspace),
+            _p(topk_weights), top_k, M, K, N, E, R, bpc, _p(gate_up), _p(workspace),
             workspace.numel() * workspace.element_size(), _stream()))
     return out, gate_up
 

@@ -1304,7 +1304,7 @@ size_t smem_bytes_pair(int stages, uint32_t extra) {
     return 1024 + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + extra + BAR_BYTES;
 }
 
-template <bool kUp>
+template <bool kUp, bool kKeep = false>
 __global__ void __launch_bounds__(MAX_THREADS, 1)
 moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_act, const Args a) {
@@ -1440,8 +1440,10 @@ moe_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 if (!mbar_wait(sm.misc(buf), (it >> 1) & 1, status, ST_TIMEOUT_TMEM_FULL)) break;
                 if (!mbar_wait(sm.misc(5), (it & 1) ^ 1, status, ST_TIMEOUT_ACT)) break;
                 tc_fence_after();
+                __nv_bfloat16 *gu_row =
+                    kKeep ? a.gu_out + (static_cast<size_t>(blk) * BM + row) * a.N + c.n_tile * 128 : nullptr;
                 for (int ch = cg * (4 / ncg); ch < (cg + 1) * (4 / ncg); ++ch)
-                    swiglu_chunk_to_smem(acc, lane_base, row, ch, sm.act);
+                    swiglu_chunk_to_smem<kKeep>(acc, lane_base, row, ch, sm.act, gu_row, a.H);
                 tc_fence_before();
                 mbar_arrive_cluster(empty_leader);
                 fence_proxy_async_smem();
@@ -1608,8 +1610,8 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
     a.out_rows = extras.out_rows;
     PMOE_REQUIRE(!extras.out_rows || p.split, PMOE_ERR_UNSUPPORTED, "fused_moe_bf16: out_rows requires split=True");
     a.gu_out = static_cast<__nv_bfloat16 *>(extras.gu_out);
-    PMOE_REQUIRE(!extras.gu_out || (p.split && p.bpc == 1), PMOE_ERR_UNSUPPORTED,
-                 "fused_moe_bf16: keeping the gate/up pre-activations requires split=True and bpc=1");
+    PMOE_REQUIRE(!extras.gu_out || p.split, PMOE_ERR_UNSUPPORTED,
+                 "fused_moe_bf16: keeping the gate/up pre-activations requires split=True");
     const int bulk = down_bulk_reduce_mode();   // -1 auto: on when the down GEMM's K extent (H) is short
     // rows addressed through out_rows may live in a peer's memory: plain vector reductions only there
     const bool bulk_reduce = extras.out_rows ? false : (bulk < 0 ? (H <= 1024) : bulk != 0);
@@ -1775,15 +1777,20 @@ int run(const Problem &p, void *workspace, size_t workspace_bytes, cudaStream_t 
             Args up = pa;
             up.zero_out = extras.out_rows ? 0 : 1;
             up.use_pdl = (pdl_enabled() && (phases & 1)) ? 1 : 0;
-            if (int rc = launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up, (max_blocks / 2) * (H / 128),
-                                     ACT_TILE_BYTES, up.use_pdl ? 2 : 1))
+            if (int rc = a.gu_out ? launch_pair(moe_pair_bf16_kernel<true, true>, map_x, map_w1, up,
+                                                (max_blocks / 2) * (H / 128), ACT_TILE_BYTES, up.use_pdl ? 2 : 1)
+                                  : launch_pair(moe_pair_bf16_kernel<true>, map_x, map_w1, up,
+                                                (max_blocks / 2) * (H / 128), ACT_TILE_BYTES, up.use_pdl ? 2 : 1))
                 return rc;
             if (tails && !(phases & 8)) {   // plain launch: starts when the pair kernel (which zeroes `out`) has finished
                 Args tu = ta;
                 tu.use_pdl = 0;
-                if (int rc = launch_single(moe_up_bf16_kernel<false>, tu, (max_blocks / 2) * (H / 128),
-                                           smem_bytes(tu.stages, ACT_TILE_BYTES), map_x, map_w1, map_act, map_x_short,
-                                           map_act_short))
+                if (int rc = a.gu_out ? launch_single(moe_up_bf16_kernel<true>, tu, (max_blocks / 2) * (H / 128),
+                                                      smem_bytes(tu.stages, ACT_TILE_BYTES), map_x, map_w1, map_act,
+                                                      map_x_short, map_act_short)
+                                      : launch_single(moe_up_bf16_kernel<false>, tu, (max_blocks / 2) * (H / 128),
+                                                      smem_bytes(tu.stages, ACT_TILE_BYTES), map_x, map_w1, map_act,
+                                                      map_x_short, map_act_short))
                     return rc;
             }
         }
@@ -1965,14 +1972,15 @@ extern "C" int pmoe_fused_moe_bf16(const void *x, const void *w, const void *w2,
 extern "C" int pmoe_fused_moe_bf16_keep_ws(const void *x, const void *w, const void *w2, void *out,
                                            const int32_t *sorted_token_ids, const int32_t *expert_ids,
                                            const int32_t *num_tokens_post_padded, const float *topk_weights, int top_k,
-                                           int M, int K, int N, int num_experts, int sorted_num, void *gate_up,
-                                           void *workspace, size_t workspace_bytes, pmoe_stream_t stream) {
+                                           int M, int K, int N, int num_experts, int sorted_num, int bpc,
+                                           void *gate_up, void *workspace, size_t workspace_bytes,
+                                           pmoe_stream_t stream) {
     PMOE_REQUIRE(gate_up != nullptr && (reinterpret_cast<uintptr_t>(gate_up) & 31) == 0, PMOE_ERR_BAD_ARG,
                  "fused_moe_bf16_keep: gate_up must be a 32-byte aligned device buffer of sorted_num * N bf16");
     pmoe::CallExtras &extras = pmoe::call_extras();
     extras.gu_out = gate_up;
     const int rc = pmoe_fused_moe_bf16_ws(x, w, w2, out, sorted_token_ids, expert_ids, num_tokens_post_padded,
-                                          topk_weights, top_k, M, K, N, num_experts, sorted_num, 128, 64, 4, 4, 1, 1, 1,
+                                          topk_weights, top_k, M, K, N, num_experts, sorted_num, 128, 64, 4, 4, bpc, 1, 1,
                                           workspace, workspace_bytes, stream);
     extras = pmoe::CallExtras{};
     return rc;

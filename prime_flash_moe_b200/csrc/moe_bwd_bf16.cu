@@ -116,8 +116,8 @@ gather_token_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
     }
 }
 
-// inv[pair] = sorted row of the pair (inv is preset to -1); eblk[e] / eblk[E + e] = block range of expert e
-// (preset to 0)
+// inv[pair] = sorted row of the pair (inv is preset to -1); eblk[e] / eblk[E + e] = range of the blocks of expert e
+// that hold routed rows (preset to 0)
 __global__ void __launch_bounds__(256)
 row_maps_kernel(const int32_t *__restrict__ sorted_ids, const int32_t *__restrict__ expert_ids,
                 const int32_t *__restrict__ npp, int sorted_num, int top_k, int tokens, int E,
@@ -128,10 +128,13 @@ row_maps_kernel(const int32_t *__restrict__ sorted_ids, const int32_t *__restric
         const int pair = sorted_ids[r];
         if (pair >= 0 && pair < tokens * top_k) inv[pair] = r;
         if ((r & (BM - 1)) == 0) {
+            // routed rows come first in an expert's segment, so a block is live iff its first row is; routing
+            // tables padded to 256 rows (bpc = 2) can end an expert with one block without any routed row
             const int b = r / BM, e = expert_ids[b];
-            if (e >= 0 && e < E) {
+            if (e >= 0 && e < E && pair >= 0) {
                 if (b == 0 || expert_ids[b - 1] != e) eblk[e] = b;
-                if (b == blocks - 1 || expert_ids[b + 1] != e) eblk[E + e] = b + 1;
+                const bool more = b + 1 < blocks && expert_ids[b + 1] == e && sorted_ids[(b + 1) * BM] >= 0;
+                if (!more) eblk[E + e] = b + 1;
             }
         }
     }
@@ -220,7 +223,7 @@ __device__ __forceinline__ Tile decode_tile(const GArgs &a, int t, int m_items) 
         tl.mt = 0;
         tl.e = max(0, min(a.E - 1, a.expert_ids[tl.mb]));
         tl.k0 = 0;
-        tl.k1 = a.ksteps;
+        tl.k1 = a.sorted_ids[tl.mb * BM] >= 0 ? a.ksteps : 0;    // a block without routed rows is skipped altogether
     }
     return tl;
 }
@@ -497,7 +500,7 @@ moe_bwd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int col0 = tl.nt * BN;
             const int m = tl.mt * BM + row;
             if (tl.k1 <= tl.k0) {
-                zero_tile(a, cg, tl.e, m, col0);
+                if (a_mn) zero_tile(a, cg, tl.e, m, col0);
                 continue;
             }
             const int buf = it & 1;
@@ -689,7 +692,7 @@ moe_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int col0 = tl.nt * BN;
             const int m = tl.mt * 256 + static_cast<int>(rank) * 128 + row;
             if (tl.k1 <= tl.k0) {
-                zero_tile(a, cg, tl.e, m, col0);
+                if (wgrad) zero_tile(a, cg, tl.e, m, col0);
                 continue;
             }
             const int buf = it & 1;
@@ -706,6 +709,29 @@ moe_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     cluster_sync_all();      // nobody frees TMEM or exits while the peer may still use this CTA's memory
     if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
+// The row blocks that hold routed rows, in order, one CTA: live_list[0 .. *live_count). The row-space GEMMs walk this
+// list, so that blocks without routed rows (routing tables padded to 256 rows) cost no tile slot in the static
+// schedule.
+__global__ void __launch_bounds__(1024)
+live_items_kernel(const int32_t *__restrict__ eblk, int E, int32_t *__restrict__ live_list,
+                  int32_t *__restrict__ live_count) {
+    __shared__ int sn[1024];
+    const int e = threadIdx.x;
+    const int b0 = e < E ? eblk[e] : 0;
+    const int nb = e < E ? max(0, eblk[E + e] - b0) : 0;
+    sn[e] = nb;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {
+        const int v = e >= d ? sn[e - d] : 0;
+        __syncthreads();
+        sn[e] += v;
+        __syncthreads();
+    }
+    const int off = sn[e] - nb;
+    for (int j = 0; j < nb; ++j) live_list[off + j] = b0 + j;
+    if (e == 1023) *live_count = sn[e];
 }
 
 // Work lists of the row-space GEMMs on CTA pairs, one CTA: for every expert its row blocks two by two (pair_list =
@@ -746,7 +772,7 @@ namespace {
 size_t align_up(size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); }
 
 struct BwdLayout {
-    size_t xs, dos, gu, dgu, actw, inv, eblk, pair_list, single_list, counts, total;
+    size_t xs, dos, gu, dgu, actw, inv, eblk, pair_list, single_list, counts, live_list, total;
 };
 
 // xs | dos (reused for d_xs once dW2 is done) | gu | d_gu | wt*act | pair -> row | expert block ranges | work lists
@@ -763,7 +789,8 @@ BwdLayout plan_backward(int T, int K, int N, int E, int top_k, int sorted_num) {
     l.eblk = off, off = align_up(off + 2 * static_cast<size_t>(E) * sizeof(int32_t));
     l.pair_list = off, off = align_up(off + (R / 256 + 1) * sizeof(int32_t));
     l.single_list = off, off = align_up(off + static_cast<size_t>(E) * sizeof(int32_t));
-    l.counts = off, off = align_up(off + 2 * sizeof(int32_t));
+    l.counts = off, off = align_up(off + 3 * sizeof(int32_t));            // pairs, singles, live blocks
+    l.live_list = off, off = align_up(off + (R / 128 + 1) * sizeof(int32_t));
     l.total = off;
     return l;
 }
@@ -943,6 +970,7 @@ extern "C" int pmoe_fused_moe_bf16_backward_ex(const void *x, const void *w1, co
     auto *pair_list = reinterpret_cast<int32_t *>(ws + lay.pair_list);
     auto *single_list = reinterpret_cast<int32_t *>(ws + lay.single_list);
     auto *counts = reinterpret_cast<int32_t *>(ws + lay.counts);
+    auto *live_list = reinterpret_cast<int32_t *>(ws + lay.live_list);
     const uint64_t R = static_cast<uint64_t>(sorted_num);
 
     const int mask = g_bwd_mask;
@@ -956,6 +984,8 @@ extern "C" int pmoe_fused_moe_bf16_backward_ex(const void *x, const void *w1, co
         const int small_grid = std::max(1, std::min(sorted_num / 256 + 1, 8 * sm_count()));
         row_maps_kernel<<<small_grid, 256, 0, stream>>>(sorted_token_ids, expert_ids, num_tokens_post_padded,
                                                         sorted_num, top_k, T, E, inv, eblk);
+        PMOE_CUDA_OK(cudaGetLastError());
+        live_items_kernel<<<1, 1024, 0, stream>>>(eblk, E, live_list, counts + 2);
         PMOE_CUDA_OK(cudaGetLastError());
         if (row_pairs) {
             pair_items_kernel<<<1, 1024, 0, stream>>>(eblk, E, pair_list, single_list, counts);
@@ -989,7 +1019,10 @@ extern "C" int pmoe_fused_moe_bf16_backward_ex(const void *x, const void *w1, co
     // A row-space GEMM on CTA pairs is two launches: the pairs of row blocks, then the odd last blocks of the experts
     // on the one-CTA kernel (tcgen05 does not allow cta_group::1 and ::2 in one kernel)
     auto launch_rows = [&](const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mb_pair, GArgs g) -> int {
-        if (!row_pairs) return launch_gemm(ma, mb, g, stream);
+        if (!row_pairs) {
+            g.items = live_list, g.item_count = counts + 2;
+            return launch_gemm(ma, mb, g, stream);
+        }
         g.items = pair_list, g.item_count = counts;
         if (int rc = launch_pair(ma, mb_pair, g, stream)) return rc;
         g.items = single_list, g.item_count = counts + 1;

@@ -350,7 +350,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> fused_moe
 torch::Tensor fused_moe_bf16_keep(const torch::Tensor &x, const torch::Tensor &w, const torch::Tensor &w2,
                                   const torch::Tensor &sorted_token_ids, const torch::Tensor &expert_ids,
                                   const torch::Tensor &num_tokens_post_padded, const torch::Tensor &topk_weights,
-                                  torch::Tensor &out, int64_t top_k) {
+                                  torch::Tensor &out, int64_t top_k, int64_t bpc) {
     at::cuda::OptionalCUDAGuard guard{device_of(x)};
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
     TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w2.dim() == 3, "x must be [T, K], w [E, N, K], w2 [E, K, N/2]");
@@ -376,8 +376,8 @@ torch::Tensor fused_moe_bf16_keep(const torch::Tensor &x, const torch::Tensor &w
         static_cast<const int32_t *>(expert_ids.const_data_ptr()),
         static_cast<const int32_t *>(num_tokens_post_padded.const_data_ptr()),
         static_cast<const float *>(topk_weights.const_data_ptr()), static_cast<int>(top_k), static_cast<int>(T),
-        static_cast<int>(K), static_cast<int>(N), static_cast<int>(E), static_cast<int>(R), gate_up.data_ptr(), ws_ptr,
-        need, stream));
+        static_cast<int>(K), static_cast<int>(N), static_cast<int>(E), static_cast<int>(R), static_cast<int>(bpc),
+        gate_up.data_ptr(), ws_ptr, need, stream));
     return gate_up;
 }
 
@@ -389,7 +389,7 @@ TORCH_LIBRARY_FRAGMENT(prime_moe, m) {
           "(Tensor, Tensor, Tensor, Tensor)");
     m.impl("fused_moe_bf16_backward", torch::kCUDA, &fused_moe_bf16_backward);
     m.def("fused_moe_bf16_keep(Tensor x, Tensor w, Tensor w2, Tensor sorted_token_ids, Tensor expert_ids, "
-          "Tensor num_tokens_post_padded, Tensor topk_weights, Tensor(a!) out, int top_k) -> Tensor");
+          "Tensor num_tokens_post_padded, Tensor topk_weights, Tensor(a!) out, int top_k, int bpc=1) -> Tensor");
     m.impl("fused_moe_bf16_keep", torch::kCUDA, &fused_moe_bf16_keep);
     m.def("route_topk(Tensor logits, int top_k, bool renormalize=True) -> (Tensor, Tensor)");
     m.impl("route_topk", torch::kCUDA, &route_topk);

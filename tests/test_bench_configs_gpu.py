@@ -197,6 +197,7 @@ def backward_rows_oracle(tokens, x, w1, w2, ids, wts, d_out):
 @pytest.mark.parametrize("name,T,K,E,N,k,kept", [
     ("c1", 4096, 4096, 8, 28672, 2, False),        # weight gradients on CTA pairs, pre-activations recomputed
     ("c1", 4096, 4096, 8, 28672, 2, True),         # ... kept by the forward call
+    ("c1", 4096, 4096, 8, 28672, 2, 2),            # ... kept by the CTA-pair forward (routing tables padded to 256 rows)
     ("c2", 8192, 2048, 128, 1536, 8, False),
 ])
 def test_backward_full_size(name, T, K, E, N, k, kept):
@@ -207,11 +208,12 @@ def test_backward_full_size(name, T, K, E, N, k, kept):
     H = N // 2
     x, w1, w2, ids, wts = device_case(T, K, E, N, k, seed=41)
     d_out = torch.randn(T, K, device=DEV, generator=torch.Generator(device=DEV).manual_seed(42)).to(torch.bfloat16)
-    s, e, n = capi.moe_align(ids.to(DEV), E, 128, 1)
+    bpc = 2 if kept == 2 else 1
+    s, e, n = capi.moe_align(ids.to(DEV), E, 128, bpc)
     dwts = wts.to(DEV)
     gate_up = None
     if kept:
-        _, gate_up = capi.fused_moe_bf16_keep(x, w1, w2, s, e, n, dwts, torch.empty_like(x), k)
+        _, gate_up = capi.fused_moe_bf16_keep(x, w1, w2, s, e, n, dwts, torch.empty_like(x), k, bpc=bpc)
     d_x, d_w1, d_w2, d_wt = capi.fused_moe_bf16_backward(x, w1, w2, d_out, s, e, n, dwts, k, gate_up=gate_up)
     torch.cuda.synchronize()
     assert capi.device_status() == 0

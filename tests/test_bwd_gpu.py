@@ -136,19 +136,21 @@ def test_argument_checks():
                                      workspace=small[(-small.data_ptr()) % 1024:][:1024])
 
 
+@pytest.mark.parametrize("bpc", [1, 2])
 @pytest.mark.parametrize("T,K,E,N,k", [(64, 512, 4, 512, 2), (256, 4096, 8, 512, 4), (2100, 256, 2, 768, 1)])
-def test_kept_pre_activations(T, K, E, N, k):
+def test_kept_pre_activations(T, K, E, N, k, bpc):
     """The forward call that keeps gate | up: same `out` as the plain call, the kept rows equal xs @ W1[e]^T, and the
     backward pass fed with them matches the oracle (the last shape has > 1024 rows per expert: the two-block
-    gate/up kernel)."""
+    gate/up kernel). bpc = 2: routing tables padded to 256 rows, CTA-pair gate/up kernel + single-block tails, and
+    a backward pass that skips the blocks without routed rows."""
     from prime_flash_moe_b200 import capi
     x, w1, w2, ids, wts = O.make_case(T, K, E, N, k, seed=T + 3)
     d_out = torch.randn(T, K, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
-    s, e, n = capi.moe_align(ids.to(DEV), E, 128, 1)
+    s, e, n = capi.moe_align(ids.to(DEV), E, 128, bpc)
     dx, dw1, dw2, dwts = x.to(DEV), w1.to(DEV), w2.to(DEV), wts.to(DEV)
     plain = torch.empty(T, K, dtype=torch.bfloat16, device=DEV)
-    capi.fused_moe_bf16(dx, dw1, dw2, s, e, n, dwts, plain, k)
-    out, gate_up = capi.fused_moe_bf16_keep(dx, dw1, dw2, s, e, n, dwts, torch.empty_like(plain), k)
+    capi.fused_moe_bf16(dx, dw1, dw2, s, e, n, dwts, plain, k, bpc=bpc)
+    out, gate_up = capi.fused_moe_bf16_keep(dx, dw1, dw2, s, e, n, dwts, torch.empty_like(plain), k, bpc=bpc)
     torch.cuda.synchronize()
     assert O.max_rel_to_peak(out.cpu(), plain.cpu()) <= 1e-2     # bf16 reductions into `out` come in any order
     rows = s.cpu().long()
@@ -156,7 +158,7 @@ def test_kept_pre_activations(T, K, E, N, k):
     expert = e.cpu().long()[live // 128]
     want = torch.einsum("rk,rnk->rn", x.float()[rows[live] // k], w1.float()[expert])
     assert O.max_rel_to_peak(gate_up.cpu()[live], want) <= 1e-2
-    assert torch.isfinite(gate_up[: int(n.item())].float()).all()
+    assert torch.isfinite(gate_up[torch.nonzero(s >= 0).flatten()].float()).all()
     grads = capi.fused_moe_bf16_backward(dx, dw1, dw2, d_out.to(DEV), s, e, n, dwts, k, gate_up=gate_up)
     torch.cuda.synchronize()
     assert capi.device_status() == 0

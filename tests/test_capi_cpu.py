@@ -128,7 +128,7 @@ def test_backward_argument_errors_and_workspace_plan(lib):
     assert str(need).encode() in lib.pmoe_last_error()
     assert lib.pmoe_fused_moe_bf16_backward_workspace_bytes(8, 256, 512, 4, 2, 1024) > need
     assert lib.pmoe_fused_moe_bf16_backward_workspace_bytes(8, 512, 512, 4, 2, 512) > need
-    assert lib.pmoe_fused_moe_bf16_keep_ws(*common, 2, 8, 256, 512, 4, 512, None, p, 1 << 30, None) == 1
+    assert lib.pmoe_fused_moe_bf16_keep_ws(*common, 2, 8, 256, 512, 4, 512, 1, None, p, 1 << 30, None) == 1
     assert b"gate_up" in lib.pmoe_last_error()
     assert lib.pmoe_debug_set_backward_mask(127) == 127
 
