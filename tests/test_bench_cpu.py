@@ -41,6 +41,15 @@ def test_sweep_covers_the_benchmark_configurations():
     assert ("c3", "mxfp8") in names and ("c4", "bf16") in names and ("c4", "mxfp8") in names and ("c0", "bf16") in names
     assert {t for c, t, _ in b.SWEEP if c == "c2"} == {16, 128, 8192}
     assert b.SWEEP_ALIGN == ["c4", "c3"]
+    assert ("c1", 0) in b.SWEEP_BACKWARD and ("c2", 8192) in b.SWEEP_BACKWARD        # backward pass beside the forward sweep
+    assert sum(bit for _, bit in b.BACKWARD_STEPS) == 127                              # every step of the mask, once
+
+
+def test_operations_the_bench_can_time(monkeypatch):
+    b = _bench()
+    for op in ("moe", "moe_align", "pre", "backward", "train"):
+        monkeypatch.setattr("sys.argv", ["bench.py", "--op", op])
+        assert b.parse_args().op == op
 
 
 def test_sweep_summary_is_one_string_per_entry():
