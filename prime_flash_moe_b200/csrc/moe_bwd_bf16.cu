@@ -87,31 +87,44 @@ struct GArgs {
 // row-space helpers (HBM-bound)
 // ---------------------------------------------------------------------------------------------
 // xs[r] = x[token(r)] and dos[r] = d_out[token(r)] for the live rows, zeros for padding rows. One warp per row,
-// 16 bytes per lane and step, both tensors in one pass over the routing table.
+// both tensors in one pass over the routing table; kWide: 32 bytes per lane and access (x and d_out 32-byte
+// aligned), else 16.
+template <bool kWide>
 __global__ void __launch_bounds__(256)
 gather_token_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ d_out,
                          const int32_t *__restrict__ sorted_ids, const int32_t *__restrict__ npp, int sorted_num,
                          int top_k, int tokens, int K, __nv_bfloat16 *__restrict__ xs, __nv_bfloat16 *__restrict__ dos) {
     const int rows = live_row_blocks(npp, sorted_num) * BM;
-    const int vec_per_row = K / 8;
     const int lane = threadIdx.x & 31;
+    constexpr int kElems = kWide ? 16 : 8;        // bf16 per lane and access
+    const int vec_per_row = K / kElems;
     for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8) {
         const int pair = sorted_ids[r];
         const int tok = pair >= 0 ? pair / top_k : tokens;
         const bool live = tok < tokens;
-        const uint4 *s1 = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(live ? tok : 0) * K);
-        const uint4 *s2 = reinterpret_cast<const uint4 *>(d_out + static_cast<size_t>(live ? tok : 0) * K);
-        uint4 *d1 = reinterpret_cast<uint4 *>(xs + static_cast<size_t>(r) * K);
-        uint4 *d2 = reinterpret_cast<uint4 *>(dos + static_cast<size_t>(r) * K);
+        const __nv_bfloat16 *s1 = x + static_cast<size_t>(live ? tok : 0) * K;
+        const __nv_bfloat16 *s2 = d_out + static_cast<size_t>(live ? tok : 0) * K;
+        __nv_bfloat16 *d1 = xs + static_cast<size_t>(r) * K;
+        __nv_bfloat16 *d2 = dos + static_cast<size_t>(r) * K;
 #pragma unroll 4
         for (int v = lane; v < vec_per_row; v += 32) {
-            uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-            if (live) {
-                a = __ldg(s1 + v);
-                b = __ldg(s2 + v);
+            if (kWide) {
+                uint32_t a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (live) {
+                    ld_global_v8(s1 + v * 16, a);
+                    ld_global_v8(s2 + v * 16, b);
+                }
+                st_global_v8(d1 + v * 16, a);
+                st_global_v8(d2 + v * 16, b);
+            } else {
+                uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+                if (live) {
+                    a = __ldg(reinterpret_cast<const uint4 *>(s1) + v);
+                    b = __ldg(reinterpret_cast<const uint4 *>(s2) + v);
+                }
+                reinterpret_cast<uint4 *>(d1)[v] = a;
+                reinterpret_cast<uint4 *>(d2)[v] = b;
             }
-            d1[v] = a;
-            d2[v] = b;
         }
     }
 }
@@ -991,7 +1004,8 @@ extern "C" int pmoe_fused_moe_bf16_backward_ex(const void *x, const void *w1, co
             pair_items_kernel<<<1, 1024, 0, stream>>>(eblk, E, pair_list, single_list, counts);
             PMOE_CUDA_OK(cudaGetLastError());
         }
-        gather_token_rows_kernel<<<copy_grid, 256, 0, stream>>>(
+        const bool wide = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(d_out)) & 31) == 0;
+        (wide ? gather_token_rows_kernel<true> : gather_token_rows_kernel<false>)<<<copy_grid, 256, 0, stream>>>(
             static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(d_out), sorted_token_ids,
             num_tokens_post_padded, sorted_num, top_k, T, K, xs, dos);
         PMOE_CUDA_OK(cudaGetLastError());
